@@ -1,0 +1,159 @@
+"""ctypes binding of libgnn_b200.so (C ABI declared in include/gnn_b200.h).
+
+The library is built ahead of time by ``ae_mlsys_gnn_b200.build``; there is no
+fallback: if it cannot be loaded, importing an operator raises.  PyTorch is used
+only to own device memory and streams — tensors cross the boundary as raw
+pointers plus sizes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+from . import build as _build
+
+_I64 = C.c_int64
+_INT = C.c_int
+_F32 = C.c_float
+_PTR = C.c_void_p
+_SZ = C.c_size_t
+_SZP = C.POINTER(C.c_size_t)
+
+# name -> argument types (return type is int unless listed in _RESTYPES)
+PROTOTYPES = {
+    "gnn_abi_version": [],
+    "gnn_last_error_string": [],
+    "gnn_csr2csc_workspace_bytes": [_I64, _SZP],
+    "gnn_csr2csc": [_PTR, _PTR, _I64, _I64, _I64, _PTR, _PTR, _PTR, _PTR, _SZ, _PTR],
+    "gnn_gat_fwd_workspace_bytes": [_I64, _INT, _INT, _SZP],
+    "gnn_gat_fwd": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _INT, _INT, _F32,
+                    _PTR, _PTR, _PTR, _PTR, _SZ, _PTR],
+    "gnn_gat_bwd_workspace_bytes": [_I64, _I64, _INT, _INT, _SZP],
+    "gnn_gat_bwd": [_PTR, _PTR, _PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR,
+                    _INT, _INT, _F32, _PTR, _PTR, _PTR, _PTR, _SZ, _PTR],
+    "gnn_gat_bwd_row_workspace_bytes": [_I64, _INT, _INT, _SZP],
+    "gnn_gat_bwd_row": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR,
+                        _INT, _INT, _F32, _PTR, _PTR, _PTR, _SZ, _PTR],
+    "gnn_gat_bwd_col_workspace_bytes": [_I64, _INT, _INT, _SZP],
+    "gnn_gat_bwd_col": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _PTR, _INT, _INT, _F32,
+                        _PTR, _PTR, _PTR, _SZ, _PTR],
+    "gnn_gat_edge_alpha": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _PTR, _INT, _F32,
+                           _PTR, _PTR, _PTR],
+    "gnn_edgeconv_fwd": [_INT, _PTR, _PTR, _PTR, _I64, _INT, _PTR, _PTR, _PTR],
+    "gnn_edgeconv_bwd": [_PTR, _PTR, _I64, _I64, _INT, _PTR, _PTR],
+    "gnn_gmm_fwd_workspace_bytes": [_I64, _INT, _INT, _SZP],
+    "gnn_gmm_fwd": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _PTR, _PTR, _INT, _INT, _INT,
+                    _PTR, _PTR, _SZ, _PTR],
+    "gnn_gaussian_fwd": [_PTR, _PTR, _PTR, _I64, _INT, _INT, _PTR, _PTR],
+    "gnn_gaussian_bwd_workspace_bytes": [_I64, _INT, _INT, _SZP],
+    "gnn_gaussian_bwd": [_PTR, _PTR, _PTR, _PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR,
+                         _PTR, _SZ, _PTR],
+    "gnn_mhspmm_workspace_bytes": [_I64, _INT, _INT, _SZP],
+    "gnn_mhspmm": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _INT, _INT, _PTR, _PTR, _SZ, _PTR],
+    "gnn_mhsddmm": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _INT, _INT, _PTR, _PTR],
+    "gnn_sddmm_coo": [_PTR, _PTR, _I64, _PTR, _PTR, _INT, _PTR, _PTR],
+    "gnn_mhtranspose": [_PTR, _PTR, _I64, _INT, _PTR, _PTR],
+    "gnn_u_add_v_fwd": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _INT, _PTR, _PTR],
+    "gnn_u_add_v_bwd": [_PTR, _PTR, _I64, _I64, _I64, _PTR, _INT, _PTR, _PTR, _PTR],
+    "gnn_edge_softmax_fwd": [_PTR, _I64, _I64, _PTR, _INT, _PTR, _PTR],
+    "gnn_edge_softmax_bwd": [_PTR, _I64, _I64, _PTR, _PTR, _INT, _PTR, _PTR],
+}
+_RESTYPES = {"gnn_last_error_string": C.c_char_p}
+
+_lib = None
+
+
+class GnnError(RuntimeError):
+    """A negative return code from libgnn_b200.so."""
+
+
+def library_path() -> str:
+    return _build.LIB
+
+
+def lib() -> C.CDLL:
+    """Loads (building first if the sources are newer) and returns the library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB
+    if os.environ.get("GNN_B200_NO_BUILD", "0") != "1" and _build.needs_build():
+        path = _build.build()
+    if not os.path.exists(path):
+        raise ImportError(
+            f"{path} is missing: run `python -m ae_mlsys_gnn_b200.build` (nvcc, sm_100a). "
+            "There is no CPU or PyTorch fallback for these operators.")
+    handle = C.CDLL(path)
+    for name, args in PROTOTYPES.items():
+        fn = getattr(handle, name)  # AttributeError if the symbol is not exported
+        fn.argtypes = args
+        fn.restype = _RESTYPES.get(name, C.c_int)
+    if handle.gnn_abi_version() != 1:
+        raise ImportError("libgnn_b200.so ABI version mismatch; rebuild the library")
+    _lib = handle
+    return _lib
+
+
+def last_error() -> str:
+    msg = lib().gnn_last_error_string()
+    return msg.decode() if msg else ""
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise GnnError(f"{what} failed with code {rc}: {last_error()}")
+
+
+def call(name: str, *args) -> None:
+    check(getattr(lib(), name)(*args), name)
+
+
+def workspace_bytes(name: str, *args) -> int:
+    out = C.c_size_t(0)
+    check(getattr(lib(), name)(*args, C.byref(out)), name)
+    return int(out.value)
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def require(t: torch.Tensor, dtype: torch.dtype, name: str, ndim: int | None = None,
+            device: torch.device | None = None) -> torch.Tensor:
+    """Argument validation that the reference does with C asserts
+    (src/fused_gat/fused_gat_SM.cpp:22-36): CUDA device, dtype, contiguity."""
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (no CPU path exists)")
+    if device is not None and t.device != device:
+        raise ValueError(f"{name} is on {t.device}, expected {device}")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise ValueError(f"{name} must have {ndim} dims, got shape {tuple(t.shape)}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return t
+
+
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """A per-(device, stream) scratch buffer that only grows; contents are undefined."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = None
+        _workspaces.pop(key, None)
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf

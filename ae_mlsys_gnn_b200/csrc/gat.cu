@@ -1,0 +1,303 @@
+// C-ABI entry points of the fused GAT forward / backward.
+#include "../../include/gnn_b200.h"
+#include "gat_bwd.cuh"
+
+using namespace gnn;
+
+namespace {
+
+struct HeadPlan {
+  bool fused;   // all heads in one launch
+  bool vec;     // 128-bit row accesses
+  int HP;       // padded head count of the launch
+  int slab;     // columns per launch in the per-head fallback
+};
+
+// Decides how (H, F) maps onto the instantiated tiles.
+bool plan_heads(int H, int F, bool aligned, bool need_full_head, HeadPlan* pl) {
+  const bool vec = aligned && (F % 4 == 0);
+  const int cap = max_tile_width(vec);
+  if (H <= 8 && (int64_t)H * F <= cap) {
+    pl->fused = true; pl->vec = vec; pl->HP = next_pow2(H); pl->slab = H * F;
+    return true;
+  }
+  if (need_full_head && F > cap) return false;
+  pl->fused = false; pl->vec = vec; pl->HP = 1; pl->slab = F < cap ? F : cap;
+  return true;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+int bad(const char* msg) {
+  set_last_error(msg);
+  return GNN_ERR_INVALID_ARG;
+}
+
+}  // namespace
+
+extern "C" int gnn_gat_fwd_workspace_bytes(int64_t nnz, int H, int F, size_t* bytes) {
+  if (!bytes || nnz < 0 || H <= 0 || F <= 0) return bad("gnn_gat_fwd_workspace_bytes: bad argument");
+  HeadPlan pl;
+  plan_heads(H, F, true, false, &pl);
+  const size_t a = wgather_scratch_floats(nnz, pl.HP, pl.slab);
+  HeadPlan ps;
+  plan_heads(H, F, false, false, &ps);
+  const size_t b = wgather_scratch_floats(nnz, ps.HP, ps.slab);
+  *bytes = (a > b ? a : b) * sizeof(float) + 256;
+  return GNN_OK;
+}
+
+extern "C" int gnn_gat_fwd(const int* row_ptr, const int* col_ind, int64_t n_rows,
+                           int64_t nnz, const float* attn_row, const float* attn_col,
+                           const float* in_feat, int H, int F, float negative_slope,
+                           float* out, float* edge_max, float* edge_sum,
+                           void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  if (n_rows < 0 || nnz < 0 || H <= 0 || F <= 0) return bad("gnn_gat_fwd: negative size");
+  if (n_rows > INT32_MAX - 1 || nnz > INT32_MAX - 4096) return bad("gnn_gat_fwd: size exceeds int32 indexing");
+  if (n_rows == 0) return GNN_OK;
+  if (!row_ptr || (!col_ind && nnz) || !attn_row || !attn_col || !in_feat || !out || !edge_max || !edge_sum)
+    return bad("gnn_gat_fwd: null pointer");
+  const int64_t HF = (int64_t)H * F;
+  const bool aligned = aligned16(in_feat) && aligned16(out) && HF % 4 == 0;
+  HeadPlan pl;
+  if (!plan_heads(H, F, aligned, false, &pl)) {
+    set_last_error("gnn_gat_fwd: unsupported shape");
+    return GNN_ERR_UNSUPPORTED;
+  }
+  size_t need = 0;
+  gnn_gat_fwd_workspace_bytes(nnz, H, F, &need);
+  if (nnz > 0 && (!workspace || workspace_bytes < need)) {
+    set_last_error("gnn_gat_fwd: workspace too small");
+    return GNN_ERR_WORKSPACE;
+  }
+  float* scratch = (float*)align_up((uintptr_t)workspace, 256);
+
+  const int chunk = pick_chunk(nnz);
+  ChunkGeom g{row_ptr, col_ind, (int)n_rows, (int)nnz, chunk, num_chunks_for(nnz, chunk)};
+  const int nh = pl.fused ? 1 : H;
+  for (int h = 0; h < nh; ++h) {
+    const int Hh = pl.fused ? H : 1;
+    for (int f0 = 0; f0 < (pl.fused ? 1 : F); f0 += pl.slab) {
+      const int w = pl.fused ? (int)HF : (F - f0 < pl.slab ? F - f0 : pl.slab);
+      const int64_t off = pl.fused ? 0 : (int64_t)h * F + f0;
+      WGatherParams p;
+      p.g = g;
+      p.feat = in_feat + off; p.ld_feat = HF;
+      p.out = out + off; p.ld_out = HF;
+      p.H = Hh; p.F = pl.fused ? F : w; p.width = w;
+      p.scratch = scratch;
+      p.aux_off = round_up4(w);
+      p.slot_stride = p.aux_off + round_up4(2 * pl.HP);
+      bool ok = dispatch_tile(pl.HP, w, pl.vec, [&](auto hp, auto q, auto v) {
+        constexpr int HP = decltype(hp)::value;
+        GatSoftmaxPolicy<HP> pol;
+        pol.attn_seg = attn_row + (pl.fused ? 0 : h);
+        pol.attn_idx = attn_col + (pl.fused ? 0 : h);
+        pol.ld_attn = H;
+        pol.slope = negative_slope;
+        pol.seg_max = edge_max + (pl.fused ? 0 : h);
+        pol.seg_sum = edge_sum + (pl.fused ? 0 : h);
+        launch_wgather<GatSoftmaxPolicy, HP, decltype(q)::value, decltype(v)::value>(p, pol, stream);
+      });
+      if (!ok) {
+        set_last_error("gnn_gat_fwd: no tile for this shape");
+        return GNN_ERR_UNSUPPORTED;
+      }
+    }
+  }
+  return check_launch("gnn_gat_fwd");
+}
+
+// ---------------------------------------------------------------------------
+
+namespace {
+
+size_t bwd_scratch_floats(int64_t nnz, int HP, int width) {
+  const size_t col = wgather_scratch_floats(nnz, HP, width);
+  const int chunk = pick_chunk(nnz);
+  const size_t row = (size_t)num_chunks_for(nnz, chunk) * 2 * 4 * HP;
+  return col > row ? col : row;
+}
+
+template <int HP, int Q, bool VEC>
+void launch_row(const GatBwdRowParams& p, cudaStream_t stream) {
+  if (p.g.num_chunks > 0) {
+    const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
+    gat_bwd_row_kernel<HP, Q, VEC><<<blocks, kThreadsPerCta, 0, stream>>>(p);
+  }
+  const int nbound = p.g.num_chunks > 1 ? p.g.num_chunks - 1 : 0;
+  const int bblocks = (nbound + kWarpsPerCta - 1) / kWarpsPerCta;
+  const int sblocks = (p.g.nseg + kThreadsPerCta - 1) / kThreadsPerCta;
+  if (bblocks + sblocks > 0)
+    gat_bwd_row_fixup_kernel<HP><<<bblocks + sblocks, kThreadsPerCta, 0, stream>>>(p, bblocks);
+}
+
+template <int HP, int Q, bool VEC>
+void launch_col(const GatBwdColParams& p, cudaStream_t stream) {
+  if (p.g.num_chunks > 0) {
+    const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
+    gat_bwd_col_kernel<HP, Q, VEC><<<blocks, kThreadsPerCta, 0, stream>>>(p);
+  }
+  const int nbound = p.g.num_chunks > 1 ? p.g.num_chunks - 1 : 0;
+  const int bblocks = (nbound + kWarpsPerCta - 1) / kWarpsPerCta;
+  const int sblocks = (p.g.nseg + kThreadsPerCta - 1) / kThreadsPerCta;
+  if (bblocks + sblocks > 0)
+    gat_bwd_col_fixup_kernel<HP, Q, VEC><<<bblocks + sblocks, kThreadsPerCta, 0, stream>>>(p, bblocks);
+}
+
+}  // namespace
+
+extern "C" int gnn_gat_bwd_row_workspace_bytes(int64_t nnz, int H, int F, size_t* bytes) {
+  if (!bytes || nnz < 0 || H <= 0 || F <= 0) return bad("gnn_gat_bwd_row_workspace_bytes: bad argument");
+  HeadPlan pl;
+  if (!plan_heads(H, F, true, true, &pl)) plan_heads(H, 1, false, true, &pl);
+  const int chunk = pick_chunk(nnz);
+  *bytes = (size_t)num_chunks_for(nnz, chunk) * 2 * 4 * 8 * sizeof(float) + 256;
+  return GNN_OK;
+}
+
+extern "C" int gnn_gat_bwd_col_workspace_bytes(int64_t nnz, int H, int F, size_t* bytes) {
+  if (!bytes || nnz < 0 || H <= 0 || F <= 0) return bad("gnn_gat_bwd_col_workspace_bytes: bad argument");
+  HeadPlan pl, ps;
+  size_t a = 0, b = 0;
+  if (plan_heads(H, F, true, true, &pl)) a = wgather_scratch_floats(nnz, pl.HP, pl.slab);
+  if (plan_heads(H, F, false, true, &ps)) b = wgather_scratch_floats(nnz, ps.HP, ps.slab);
+  *bytes = (a > b ? a : b) * sizeof(float) + 256;
+  return GNN_OK;
+}
+
+extern "C" int gnn_gat_bwd_row(const int* row_ptr, const int* col_ind, int64_t n_rows,
+                               int64_t nnz, const float* edge_max, const float* edge_sum,
+                               const float* in_feat, const float* attn_row,
+                               const float* attn_col, const float* grad_out, int H, int F,
+                               float negative_slope, float* grad_attn_row, float* rowpack,
+                               void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  if (n_rows < 0 || nnz < 0 || H <= 0 || F <= 0) return bad("gnn_gat_bwd_row: negative size");
+  if (n_rows > INT32_MAX - 1 || nnz > INT32_MAX - 4096) return bad("gnn_gat_bwd_row: size exceeds int32 indexing");
+  if (n_rows == 0) return GNN_OK;
+  if (!row_ptr || (!col_ind && nnz) || !edge_max || !edge_sum || !in_feat || !attn_row ||
+      !attn_col || !grad_out || !grad_attn_row || !rowpack)
+    return bad("gnn_gat_bwd_row: null pointer");
+  const int64_t HF = (int64_t)H * F;
+  const bool aligned = aligned16(in_feat) && aligned16(grad_out) && HF % 4 == 0;
+  HeadPlan pl;
+  if (!plan_heads(H, F, aligned, true, &pl)) {
+    set_last_error("gnn_gat_bwd_row: per-head width beyond the largest tile");
+    return GNN_ERR_UNSUPPORTED;
+  }
+  if (!pl.fused) {
+    set_last_error("gnn_gat_bwd_row: H > 8 or H*F beyond the largest tile is not supported");
+    return GNN_ERR_UNSUPPORTED;
+  }
+  size_t need = 0;
+  gnn_gat_bwd_row_workspace_bytes(nnz, H, F, &need);
+  if (nnz > 0 && (!workspace || workspace_bytes < need)) {
+    set_last_error("gnn_gat_bwd_row: workspace too small");
+    return GNN_ERR_WORKSPACE;
+  }
+  const int chunk = pick_chunk(nnz);
+  GatBwdRowParams p;
+  p.g = ChunkGeom{row_ptr, col_ind, (int)n_rows, (int)nnz, chunk, num_chunks_for(nnz, chunk)};
+  p.gout = grad_out; p.ld_gout = HF;
+  p.feat = in_feat; p.ld_feat = HF;
+  p.attn_seg = attn_row; p.attn_idx = attn_col;
+  p.seg_max = edge_max; p.seg_sum = edge_sum;
+  p.ld_attn = H; p.slope = negative_slope;
+  p.H = H; p.F = F; p.width = (int)HF;
+  p.grad_attn_seg = grad_attn_row; p.rowpack = rowpack;
+  p.scratch = (float*)align_up((uintptr_t)workspace, 256);
+  bool ok = dispatch_tile(pl.HP, (int)HF, pl.vec, [&](auto hp, auto q, auto v) {
+    launch_row<decltype(hp)::value, decltype(q)::value, decltype(v)::value>(p, stream);
+  });
+  if (!ok) {
+    set_last_error("gnn_gat_bwd_row: no tile for this shape");
+    return GNN_ERR_UNSUPPORTED;
+  }
+  return check_launch("gnn_gat_bwd_row");
+}
+
+extern "C" int gnn_gat_bwd_col(const int* col_ptr, const int* row_ind, int64_t n_cols,
+                               int64_t nnz, const float* in_feat, const float* attn_col,
+                               const float* rowpack, const float* grad_out, int H, int F,
+                               float negative_slope, float* grad_feat, float* grad_attn_col,
+                               void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  if (n_cols < 0 || nnz < 0 || H <= 0 || F <= 0) return bad("gnn_gat_bwd_col: negative size");
+  if (n_cols > INT32_MAX - 1 || nnz > INT32_MAX - 4096) return bad("gnn_gat_bwd_col: size exceeds int32 indexing");
+  if (n_cols == 0) return GNN_OK;
+  if (!col_ptr || (!row_ind && nnz) || !in_feat || !attn_col || !rowpack || !grad_out ||
+      !grad_feat || !grad_attn_col)
+    return bad("gnn_gat_bwd_col: null pointer");
+  const int64_t HF = (int64_t)H * F;
+  const bool aligned = aligned16(in_feat) && aligned16(grad_out) && aligned16(grad_feat) && HF % 4 == 0;
+  HeadPlan pl;
+  if (!plan_heads(H, F, aligned, true, &pl) || !pl.fused) {
+    set_last_error("gnn_gat_bwd_col: H > 8 or H*F beyond the largest tile is not supported");
+    return GNN_ERR_UNSUPPORTED;
+  }
+  size_t need = 0;
+  gnn_gat_bwd_col_workspace_bytes(nnz, H, F, &need);
+  if (nnz > 0 && (!workspace || workspace_bytes < need)) {
+    set_last_error("gnn_gat_bwd_col: workspace too small");
+    return GNN_ERR_WORKSPACE;
+  }
+  const int chunk = pick_chunk(nnz);
+  GatBwdColParams p;
+  p.g = ChunkGeom{col_ptr, row_ind, (int)n_cols, (int)nnz, chunk, num_chunks_for(nnz, chunk)};
+  p.gout = grad_out; p.ld_gout = HF;
+  p.feat = in_feat; p.ld_feat = HF;
+  p.attn_seg = attn_col; p.rowpack = rowpack;
+  p.ld_attn = H; p.slope = negative_slope;
+  p.H = H; p.F = F; p.width = (int)HF;
+  p.grad_feat = grad_feat; p.ld_gfeat = HF;
+  p.grad_attn_seg = grad_attn_col;
+  p.scratch = (float*)align_up((uintptr_t)workspace, 256);
+  p.aux_off = round_up4((int)HF);
+  p.slot_stride = p.aux_off + round_up4(2 * pl.HP);
+  bool ok = dispatch_tile(pl.HP, (int)HF, pl.vec, [&](auto hp, auto q, auto v) {
+    launch_col<decltype(hp)::value, decltype(q)::value, decltype(v)::value>(p, stream);
+  });
+  if (!ok) {
+    set_last_error("gnn_gat_bwd_col: no tile for this shape");
+    return GNN_ERR_UNSUPPORTED;
+  }
+  return check_launch("gnn_gat_bwd_col");
+}
+
+extern "C" int gnn_gat_bwd_workspace_bytes(int64_t n_rows, int64_t nnz, int H, int F, size_t* bytes) {
+  if (!bytes || n_rows < 0) return bad("gnn_gat_bwd_workspace_bytes: bad argument");
+  size_t a = 0, b = 0;
+  int rc = gnn_gat_bwd_row_workspace_bytes(nnz, H, F, &a);
+  if (rc) return rc;
+  rc = gnn_gat_bwd_col_workspace_bytes(nnz, H, F, &b);
+  if (rc) return rc;
+  *bytes = align_up((size_t)n_rows * 4 * H * sizeof(float), 256) + (a > b ? a : b) + 256;
+  return GNN_OK;
+}
+
+extern "C" int gnn_gat_bwd(const int* row_ptr, const int* col_ind, const int* col_ptr,
+                           const int* row_ind, int64_t n, int64_t nnz, const float* edge_max,
+                           const float* edge_sum, const float* in_feat, const float* attn_row,
+                           const float* attn_col, const float* grad_out, int H, int F,
+                           float negative_slope, float* grad_feat, float* grad_attn_row,
+                           float* grad_attn_col, void* workspace, size_t workspace_bytes,
+                           cudaStream_t stream) {
+  size_t need = 0;
+  int rc = gnn_gat_bwd_workspace_bytes(n, nnz, H, F, &need);
+  if (rc) return rc;
+  if (n == 0) return GNN_OK;
+  if (!workspace || workspace_bytes < need) {
+    set_last_error("gnn_gat_bwd: workspace too small");
+    return GNN_ERR_WORKSPACE;
+  }
+  char* base = (char*)align_up((uintptr_t)workspace, 256);
+  float* rowpack = (float*)base;
+  const size_t pack_bytes = align_up((size_t)n * 4 * H * sizeof(float), 256);
+  void* scratch = base + pack_bytes;
+  const size_t scratch_bytes = workspace_bytes - (size_t)((char*)scratch - (char*)workspace);
+  rc = gnn_gat_bwd_row(row_ptr, col_ind, n, nnz, edge_max, edge_sum, in_feat, attn_row,
+                       attn_col, grad_out, H, F, negative_slope, grad_attn_row, rowpack,
+                       scratch, scratch_bytes, stream);
+  if (rc) return rc;
+  return gnn_gat_bwd_col(col_ptr, row_ind, n, nnz, in_feat, attn_col, rowpack, grad_out, H, F,
+                         negative_slope, grad_feat, grad_attn_col, scratch, scratch_bytes, stream);
+}

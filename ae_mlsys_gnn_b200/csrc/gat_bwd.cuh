@@ -1,0 +1,382 @@
+// Fused GAT backward, recompute flavour.  Two edge-balanced passes replace the
+// reference's three kernels and its E x H temporary
+// (src/fused_gat/fused_gat_SM.cu:560-607 mhspmm_backward_kernel, :656-732
+// mhsddmm, :734-801 fused_backward_kernel):
+//
+//  row pass (CSR, segments = destination rows r, gathers h[c]):
+//     g_j  = <G[r,h,:], h[c_j,h,:]>            per edge and head
+//     a_j  = exp(LeakyReLU(attn_row[r]+attn_col[c_j]) - max[r]) / sum[r]
+//     S    = sum_j a_j g_j
+//     grad_attn_row[r,h] = sum_j a_j d_j g_j - S * sum_j a_j d_j,
+//                          d_j = slope if the activated logit is < 0 else 1
+//     rowpack[r] = {attn_row[r,:], max[r,:], 1/sum[r,:], S[:]}
+//  col pass (CSC, segments = source columns c, gathers G[r]):
+//     grad_feat[c,h,:]   = sum_r a(r,c) G[r,h,:]
+//     grad_attn_col[c,h] = sum_r a(r,c) (<G[r,h,:], h[c,h,:]> - S[r,h]) d(r,c)
+//
+// Both passes are deterministic (no atomics): split segments are merged in
+// chunk order by one warp.
+#pragma once
+#include "wgather.cuh"
+
+namespace gnn {
+
+struct GatBwdRowParams {
+  ChunkGeom g;            // CSR: ptr = row_ptr, idx = col_ind
+  const float* gout;      // [nseg] rows of grad_out, segment indexed
+  int64_t ld_gout;
+  const float* feat;      // gathered h rows, indexed by col_ind
+  int64_t ld_feat;
+  const float* attn_seg;  // attn_row [nseg][ld_attn]
+  const float* attn_idx;  // attn_col [*][ld_attn]
+  const float* seg_max;   // [nseg][ld_attn]
+  const float* seg_sum;
+  int ld_attn;
+  float slope;
+  int H, F, width;
+  float* grad_attn_seg;   // [nseg][ld_attn]
+  float* rowpack;         // [nseg][4*H]
+  float* scratch;         // 2 * num_chunks slots of 4*HP floats
+};
+
+template <int HP, int Q, bool VEC>
+__global__ void __launch_bounds__(kThreadsPerCta)
+gat_bwd_row_kernel(GatBwdRowParams p) {
+  constexpr int VW = VEC ? 4 : 1;
+  constexpr int U0 = Unroll<Q, VEC>::U;
+  constexpr int U = (U0 * HP > 32) ? 32 / HP : U0;
+  constexpr int V = U * HP;
+  constexpr int VA = 4 * HP;  // A1, A2, A3 and one padding group
+  __shared__ int cs_all[kWarpsPerCta][32];
+  __shared__ float gs_all[kWarpsPerCta][32 * HP];
+
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int chunk_id = blockIdx.x * kWarpsPerCta + wib;
+  if (chunk_id >= p.g.num_chunks) return;
+  int* cs = cs_all[wib];
+  float* gs = gs_all[wib];
+  RowTile<Q, VEC> t;
+  t.init(lane, p.width, p.F, p.H);
+
+  for_each_piece(p.g, chunk_id, [&](int s, int a, int b, bool first, bool last) {
+    float gq[Q][VW];
+    t.load(p.gout + (size_t)s * p.ld_gout, lane, gq);
+    float ar[HP], mm[HP], is[HP];
+#pragma unroll
+    for (int h = 0; h < HP; ++h) {
+      ar[h] = 0.f; mm[h] = 0.f; is[h] = 0.f;
+      if (h < p.H) {
+        ar[h] = __ldg(p.attn_seg + (size_t)s * p.ld_attn + h);
+        mm[h] = __ldg(p.seg_max + (size_t)s * p.ld_attn + h);
+        is[h] = 1.f / __ldg(p.seg_sum + (size_t)s * p.ld_attn + h);
+      }
+    }
+    float A[VA];
+#pragma unroll
+    for (int i = 0; i < VA; ++i) A[i] = 0.f;
+
+    for (int base = a; base < b; base += 32) {
+      const int e = base + lane;
+      const bool ok = e < b;
+      const int c = __ldg(p.g.idx + (ok ? e : a));
+      float al[HP], dd[HP];
+      const float* ac = p.attn_idx + (size_t)c * p.ld_attn;
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        al[h] = 0.f; dd[h] = 1.f;
+        if (h < p.H) {
+          const float x = leaky_relu(ar[h] + __ldg(ac + h), p.slope);
+          al[h] = ok ? expf(x - mm[h]) * is[h] : 0.f;
+          dd[h] = x < 0.f ? p.slope : 1.f;
+        }
+      }
+      __syncwarp();
+      cs[lane] = c;
+      __syncwarp();
+      const int nb = min(32, b - base);
+      const int nbr = (nb + U - 1) / U * U;
+#pragma unroll 1
+      for (int jj = 0; jj < nbr; jj += U) {
+        float v[U][Q][VW];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          t.load(p.feat + (size_t)cs[jj + u] * p.ld_feat, lane, v[u]);
+        float pv[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) pv[i] = 0.f;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int q = 0; q < Q; ++q) {
+            float d = 0.f;
+#pragma unroll
+            for (int i = 0; i < VW; ++i) d = fmaf(gq[q][i], v[u][q][i], d);
+#pragma unroll
+            for (int h = 0; h < HP; ++h)
+              if (t.head[q] == h) pv[u * HP + h] += d;
+          }
+        }
+        warp_multi_sum<V>(pv, lane);
+        if ((lane & (32 / V - 1)) == 0) gs[jj * HP + lane / (32 / V)] = pv[0];
+      }
+      __syncwarp();
+      if (ok) {
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+          const float gd = gs[lane * HP + h];
+          A[h] = fmaf(al[h], gd, A[h]);
+          A[HP + h] = fmaf(al[h] * dd[h], gd, A[HP + h]);
+          A[2 * HP + h] = fmaf(al[h], dd[h], A[2 * HP + h]);
+        }
+      }
+    }
+    warp_multi_sum<VA>(A, lane);
+    // value index v = k*HP + h sits on lanes [v*32/VA, (v+1)*32/VA)
+    constexpr int LPV = 32 / VA >= 1 ? 32 / VA : 1;
+    if (first && last) {
+      const int h = lane < HP ? lane : 0;
+      const float a1 = __shfl_sync(kFull, A[0], (0 * HP + h) * LPV);
+      const float a2 = __shfl_sync(kFull, A[0], (1 * HP + h) * LPV);
+      const float a3 = __shfl_sync(kFull, A[0], (2 * HP + h) * LPV);
+      if (lane < p.H) {
+        p.grad_attn_seg[(size_t)s * p.ld_attn + lane] = a2 - a1 * a3;
+        float* rp = p.rowpack + (size_t)s * 4 * p.H;
+        rp[lane] = __ldg(p.attn_seg + (size_t)s * p.ld_attn + lane);
+        rp[p.H + lane] = __ldg(p.seg_max + (size_t)s * p.ld_attn + lane);
+        rp[2 * p.H + lane] = 1.f / __ldg(p.seg_sum + (size_t)s * p.ld_attn + lane);
+        rp[3 * p.H + lane] = a1;
+      }
+    } else {
+      float* slot = p.scratch + slot_index(chunk_id, first) * VA;
+      if ((lane & (LPV - 1)) == 0) slot[lane / LPV] = A[0];
+    }
+  });
+}
+
+template <int HP>
+__global__ void __launch_bounds__(kThreadsPerCta)
+gat_bwd_row_fixup_kernel(GatBwdRowParams p, int boundary_blocks) {
+  constexpr int VA = 4 * HP;
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  if ((int)blockIdx.x < boundary_blocks) {
+    const int bnd = 1 + blockIdx.x * kWarpsPerCta + wib;
+    if (bnd >= p.g.num_chunks) return;
+    const int x = bnd * p.g.chunk;
+    const int s = find_seg(p.g.ptr, p.g.nseg, x);
+    const int beg = __ldg(p.g.ptr + s);
+    if (!(beg < x && beg >= x - p.g.chunk)) return;
+    const int end = __ldg(p.g.ptr + s + 1);
+    const int c0 = bnd - 1;
+    const int c1 = (end - 1) / p.g.chunk;
+    float tot = 0.f;  // lane v < VA sums value v over the pieces
+    for (int c = c0; c <= c1; ++c) {
+      const float* slot = p.scratch + slot_index(c, c == c0) * VA;
+      if (lane < VA) tot += slot[lane];
+    }
+    const int h = lane < HP ? lane : 0;
+    const float a1 = __shfl_sync(kFull, tot, 0 * HP + h);
+    const float a2 = __shfl_sync(kFull, tot, 1 * HP + h);
+    const float a3 = __shfl_sync(kFull, tot, 2 * HP + h);
+    if (lane < p.H) {
+      p.grad_attn_seg[(size_t)s * p.ld_attn + lane] = a2 - a1 * a3;
+      float* rp = p.rowpack + (size_t)s * 4 * p.H;
+      rp[lane] = __ldg(p.attn_seg + (size_t)s * p.ld_attn + lane);
+      rp[p.H + lane] = __ldg(p.seg_max + (size_t)s * p.ld_attn + lane);
+      rp[2 * p.H + lane] = 1.f / __ldg(p.seg_sum + (size_t)s * p.ld_attn + lane);
+      rp[3 * p.H + lane] = a1;
+    }
+  } else {
+    const int s = ((int)blockIdx.x - boundary_blocks) * kThreadsPerCta + threadIdx.x;
+    if (s < p.g.nseg && __ldg(p.g.ptr + s) == __ldg(p.g.ptr + s + 1)) {
+      for (int h = 0; h < p.H; ++h) {
+        p.grad_attn_seg[(size_t)s * p.ld_attn + h] = 0.f;
+        float* rp = p.rowpack + (size_t)s * 4 * p.H;
+        rp[h] = __ldg(p.attn_seg + (size_t)s * p.ld_attn + h);
+        rp[p.H + h] = kNegBig;
+        rp[2 * p.H + h] = 0.f;
+        rp[3 * p.H + h] = 0.f;
+      }
+    }
+  }
+}
+
+struct GatBwdColParams {
+  ChunkGeom g;             // CSC: ptr = col_ptr, idx = row_ind
+  const float* gout;       // gathered grad_out rows, indexed by row_ind
+  int64_t ld_gout;
+  const float* feat;       // [nseg] rows of h, segment indexed
+  int64_t ld_feat;
+  const float* attn_seg;   // attn_col [nseg][ld_attn]
+  const float* rowpack;    // [*][4*H], indexed by row_ind
+  int ld_attn;
+  float slope;
+  int H, F, width;
+  float* grad_feat;        // [nseg] rows
+  int64_t ld_gfeat;
+  float* grad_attn_seg;    // grad_attn_col [nseg][ld_attn]
+  float* scratch;          // 2 * num_chunks slots of slot_stride floats
+  int slot_stride;
+  int aux_off;
+};
+
+template <int HP, int Q, bool VEC>
+__global__ void __launch_bounds__(kThreadsPerCta)
+gat_bwd_col_kernel(GatBwdColParams p) {
+  constexpr int VW = VEC ? 4 : 1;
+  constexpr int U0 = Unroll<Q, VEC>::U;
+  constexpr int U = (U0 * HP > 32) ? 32 / HP : U0;
+  constexpr int V = U * HP;
+  __shared__ int cs_all[kWarpsPerCta][32];
+  __shared__ float ws_all[kWarpsPerCta][32 * HP];
+  __shared__ float gs_all[kWarpsPerCta][32 * HP];
+
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int chunk_id = blockIdx.x * kWarpsPerCta + wib;
+  if (chunk_id >= p.g.num_chunks) return;
+  int* cs = cs_all[wib];
+  float* ws = ws_all[wib];
+  float* gs = gs_all[wib];
+  RowTile<Q, VEC> t;
+  t.init(lane, p.width, p.F, p.H);
+
+  for_each_piece(p.g, chunk_id, [&](int s, int a, int b, bool first, bool last) {
+    float fq[Q][VW];
+    t.load(p.feat + (size_t)s * p.ld_feat, lane, fq);
+    float ac[HP];
+#pragma unroll
+    for (int h = 0; h < HP; ++h)
+      ac[h] = h < p.H ? __ldg(p.attn_seg + (size_t)s * p.ld_attn + h) : 0.f;
+    float B[HP];
+#pragma unroll
+    for (int h = 0; h < HP; ++h) B[h] = 0.f;
+    float acc[Q][VW];
+    t.zero(acc);
+
+    for (int base = a; base < b; base += 32) {
+      const int e = base + lane;
+      const bool ok = e < b;
+      const int r = __ldg(p.g.idx + (ok ? e : a));
+      const float* rp = p.rowpack + (size_t)r * 4 * p.H;
+      float al[HP], dd[HP], sr[HP];
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        al[h] = 0.f; dd[h] = 1.f; sr[h] = 0.f;
+        if (h < p.H) {
+          const float x = leaky_relu(__ldg(rp + h) + ac[h], p.slope);
+          al[h] = ok ? expf(x - __ldg(rp + p.H + h)) * __ldg(rp + 2 * p.H + h) : 0.f;
+          dd[h] = x < 0.f ? p.slope : 1.f;
+          sr[h] = __ldg(rp + 3 * p.H + h);
+        }
+      }
+      __syncwarp();
+      cs[lane] = r;
+#pragma unroll
+      for (int h = 0; h < HP; ++h) ws[lane * HP + h] = al[h];
+      __syncwarp();
+      const int nb = min(32, b - base);
+      const int nbr = (nb + U - 1) / U * U;
+#pragma unroll 1
+      for (int jj = 0; jj < nbr; jj += U) {
+        float v[U][Q][VW];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          t.load(p.gout + (size_t)cs[jj + u] * p.ld_gout, lane, v[u]);
+        float pv[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) pv[i] = 0.f;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int q = 0; q < Q; ++q) {
+            const float wq = ws[(jj + u) * HP + t.head[q]];
+            float d = 0.f;
+#pragma unroll
+            for (int i = 0; i < VW; ++i) {
+              acc[q][i] = fmaf(wq, v[u][q][i], acc[q][i]);
+              d = fmaf(fq[q][i], v[u][q][i], d);
+            }
+#pragma unroll
+            for (int h = 0; h < HP; ++h)
+              if (t.head[q] == h) pv[u * HP + h] += d;
+          }
+        }
+        warp_multi_sum<V>(pv, lane);
+        if ((lane & (32 / V - 1)) == 0) gs[jj * HP + lane / (32 / V)] = pv[0];
+      }
+      __syncwarp();
+      if (ok) {
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+          const float gd = gs[lane * HP + h];
+          B[h] = fmaf(al[h] * dd[h], gd - sr[h], B[h]);
+        }
+      }
+    }
+    warp_multi_sum<HP>(B, lane);  // head h on lanes [h*32/HP, (h+1)*32/HP)
+    constexpr int LPH = 32 / HP;
+    if (first && last) {
+      t.store(p.grad_feat + (size_t)s * p.ld_gfeat, lane, acc);
+      if ((lane & (LPH - 1)) == 0 && lane / LPH < p.H)
+        p.grad_attn_seg[(size_t)s * p.ld_attn + lane / LPH] = B[0];
+    } else {
+      float* slot = p.scratch + slot_index(chunk_id, first) * p.slot_stride;
+      t.store(slot, lane, acc);
+      if ((lane & (LPH - 1)) == 0) slot[p.aux_off + lane / LPH] = B[0];
+    }
+  });
+}
+
+template <int HP, int Q, bool VEC>
+__global__ void __launch_bounds__(kThreadsPerCta)
+gat_bwd_col_fixup_kernel(GatBwdColParams p, int boundary_blocks) {
+  constexpr int VW = VEC ? 4 : 1;
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  RowTile<Q, VEC> t;
+  t.init(lane, p.width, p.F, p.H);
+  if ((int)blockIdx.x < boundary_blocks) {
+    const int bnd = 1 + blockIdx.x * kWarpsPerCta + wib;
+    if (bnd >= p.g.num_chunks) return;
+    const int x = bnd * p.g.chunk;
+    const int s = find_seg(p.g.ptr, p.g.nseg, x);
+    const int beg = __ldg(p.g.ptr + s);
+    if (!(beg < x && beg >= x - p.g.chunk)) return;
+    const int end = __ldg(p.g.ptr + s + 1);
+    const int c0 = bnd - 1;
+    const int c1 = (end - 1) / p.g.chunk;
+    float acc[Q][VW];
+    t.zero(acc);
+    float bt = 0.f;
+    for (int c = c0; c <= c1; ++c) {
+      const float* slot = p.scratch + slot_index(c, c == c0) * p.slot_stride;
+      float v[Q][VW];
+      t.load(slot, lane, v);
+#pragma unroll
+      for (int q = 0; q < Q; ++q)
+#pragma unroll
+        for (int i = 0; i < VW; ++i) acc[q][i] += v[q][i];
+      if (lane < HP) bt += slot[p.aux_off + lane];
+    }
+    t.store(p.grad_feat + (size_t)s * p.ld_gfeat, lane, acc);
+    if (lane < p.H) p.grad_attn_seg[(size_t)s * p.ld_attn + lane] = bt;
+  } else {
+    const int s = ((int)blockIdx.x - boundary_blocks) * kThreadsPerCta + threadIdx.x;
+    bool empty = false;
+    if (s < p.g.nseg) empty = __ldg(p.g.ptr + s) == __ldg(p.g.ptr + s + 1);
+    unsigned mask = __ballot_sync(kFull, empty);
+    float z[Q][VW];
+    t.zero(z);
+    while (mask) {
+      const int src = __ffs(mask) - 1;
+      mask &= mask - 1;
+      const int se = s - lane + src;
+      t.store(p.grad_feat + (size_t)se * p.ld_gfeat, lane, z);
+      if (lane < p.H) p.grad_attn_seg[(size_t)se * p.ld_attn + lane] = 0.f;
+    }
+  }
+}
+
+}  // namespace gnn

@@ -1,0 +1,430 @@
+// Weighted gather-reduce over the segments of a CSR/CSC array:
+//   out[s, :] = sum_{e in segment s} w(s, e, idx[e])[head(:)] * feat[idx[e], :]
+// with the per-edge, per-head weight w supplied by a policy (GAT attention
+// softmax, stored edge values, constant one, Gaussian mixture kernel).
+//
+// One warp owns one chunk of consecutive edges (see for_each_piece); the lanes
+// tile the feature row, so every gathered row is read with whole-warp 128-bit
+// loads.  U rows are in flight per lane before the first FMA consumes them.
+#pragma once
+#include <type_traits>
+#include "common.cuh"
+
+namespace gnn {
+
+template <int HP>
+__device__ __forceinline__ float pick(const float (&a)[HP], int i) {
+  float r = a[0];
+#pragma unroll
+  for (int h = 1; h < HP; ++h)
+    if (i == h) r = a[h];
+  return r;
+}
+
+template <int Q, bool VEC>
+struct Unroll {
+  static constexpr int R = Q * (VEC ? 4 : 1);
+  static constexpr int U = R >= 16 ? 2 : (R >= 8 ? 4 : 8);
+};
+
+struct WGatherParams {
+  ChunkGeom g;
+  const float* feat;   // gathered rows, indexed by idx[e]
+  int64_t ld_feat;     // floats between consecutive rows of feat
+  float* out;          // [nseg] rows, indexed by segment
+  int64_t ld_out;
+  int H;               // heads present (<= HP)
+  int F;               // floats per head
+  int width;           // H * F, floats handled per row
+  float* scratch;      // 2 * num_chunks slots of slot_stride floats
+  int slot_stride;     // round_up(width, 4) + aux floats, multiple of 4
+  int aux_off;         // round_up(width, 4)
+};
+
+// ----- weight policies ------------------------------------------------------
+
+// GAT: w = exp(LeakyReLU(attn_seg[s,h] + attn_idx[c,h]) - max_s), normalised by
+// the segment sum at the end (src/fused_gat/fused_gat_SM.cu:210-284).
+template <int HP>
+struct GatSoftmaxPolicy {
+  static constexpr bool kSoftmax = true;
+  const float* attn_seg;  // [nseg][ld_attn]
+  const float* attn_idx;  // [*][ld_attn]
+  int ld_attn;
+  float slope;
+  float* seg_max;         // [nseg][ld_attn]
+  float* seg_sum;
+};
+
+// Stored edge values att[e*ld + h] (nullptr: weight one).  When perm is given
+// the value of edge e is att[perm[e]*ld + h].
+template <int HP>
+struct EdgeValuePolicy {
+  static constexpr bool kSoftmax = false;
+  const float* att;
+  const int* perm;
+  int ld_att;
+};
+
+// Gaussian mixture weight, head h == mixture kernel k:
+//   w = exp(-0.5 * sum_d ((pseudo[pe,d] - mu[k,d]) * inv_sigma[k,d])^2)
+// (src/fused_gmmconv/gmmconv.cu:58-68), pe = perm ? perm[e] : e.
+template <int HP>
+struct GaussPolicy {
+  static constexpr bool kSoftmax = false;
+  const float* pseudo;  // [E][D]
+  const float* mu;      // [K][D]
+  const float* inv_sigma;
+  const int* perm;
+  int D;
+};
+
+template <int HP>
+__device__ __forceinline__ void edge_weights(const EdgeValuePolicy<HP>& pol,
+                                             int H, int e, float (&w)[HP]) {
+  if (pol.att == nullptr) {
+#pragma unroll
+    for (int h = 0; h < HP; ++h) w[h] = h < H ? 1.f : 0.f;
+    return;
+  }
+  const size_t pe = pol.perm ? (size_t)__ldg(pol.perm + e) : (size_t)e;
+#pragma unroll
+  for (int h = 0; h < HP; ++h)
+    w[h] = h < H ? __ldg(pol.att + pe * pol.ld_att + h) : 0.f;
+}
+
+template <int HP>
+__device__ __forceinline__ void edge_weights(const GaussPolicy<HP>& pol, int H,
+                                             int e, float (&w)[HP]) {
+  const size_t pe = pol.perm ? (size_t)__ldg(pol.perm + e) : (size_t)e;
+  float acc[HP];
+#pragma unroll
+  for (int h = 0; h < HP; ++h) acc[h] = 0.f;
+  for (int d = 0; d < pol.D; ++d) {
+    const float pd = __ldg(pol.pseudo + pe * pol.D + d);
+#pragma unroll
+    for (int h = 0; h < HP; ++h) {
+      if (h < H) {
+        float t = (pd - __ldg(pol.mu + h * pol.D + d)) *
+                  __ldg(pol.inv_sigma + h * pol.D + d);
+        acc[h] = fmaf(t, t, acc[h]);
+      }
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < HP; ++h) w[h] = h < H ? expf(-0.5f * acc[h]) : 0.f;
+}
+
+// ----- main kernel ----------------------------------------------------------
+
+template <template <int> class Policy, int HP, int Q, bool VEC>
+__global__ void __launch_bounds__(kThreadsPerCta)
+wgather_kernel(WGatherParams p, Policy<HP> pol) {
+  constexpr int VW = VEC ? 4 : 1;
+  constexpr int U = Unroll<Q, VEC>::U;
+  constexpr bool SOFTMAX = Policy<HP>::kSoftmax;
+  __shared__ int cs_all[kWarpsPerCta][32];
+  __shared__ float ws_all[kWarpsPerCta][32 * HP];
+
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int chunk_id = blockIdx.x * kWarpsPerCta + wib;
+  if (chunk_id >= p.g.num_chunks) return;
+  int* cs = cs_all[wib];
+  float* ws = ws_all[wib];
+  RowTile<Q, VEC> t;
+  t.init(lane, p.width, p.F, p.H);
+
+  for_each_piece(p.g, chunk_id, [&](int s, int a, int b, bool first, bool last) {
+    float segw[HP];   // GAT: attn_seg[s,h]
+    float segm[HP];   // GAT: piece maximum
+    float segs[HP];   // GAT: piece sum of exp
+#pragma unroll
+    for (int h = 0; h < HP; ++h) { segw[h] = 0.f; segm[h] = 0.f; segs[h] = 1.f; }
+
+    if constexpr (SOFTMAX) {
+      const auto& gp = pol;
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        segw[h] = h < p.H ? __ldg(gp.attn_seg + (size_t)s * gp.ld_attn + h) : 0.f;
+        segm[h] = kNegBig;
+        segs[h] = 0.f;
+      }
+      for (int base = a; base < b; base += 32) {
+        const int e = base + lane;
+        if (e < b) {
+          const int c = __ldg(p.g.idx + e);
+          const float* ac = gp.attn_idx + (size_t)c * gp.ld_attn;
+#pragma unroll
+          for (int h = 0; h < HP; ++h) {
+            if (h < p.H) {
+              const float x = leaky_relu(segw[h] + __ldg(ac + h), gp.slope);
+              if (x > segm[h]) {
+                segs[h] = segs[h] * expf(segm[h] - x) + 1.f;
+                segm[h] = x;
+              } else {
+                segs[h] += expf(x - segm[h]);
+              }
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        const float m = warp_max(segm[h]);
+        segs[h] = warp_sum(segs[h] * expf(segm[h] - m));
+        segm[h] = m;
+      }
+    }
+
+    float acc[Q][VW];
+    t.zero(acc);
+    for (int base = a; base < b; base += 32) {
+      const int e = base + lane;
+      const bool ok = e < b;
+      const int ee = ok ? e : a;
+      const int c = __ldg(p.g.idx + ee);
+      float w[HP];
+      if constexpr (SOFTMAX) {
+        const float* ac = pol.attn_idx + (size_t)c * pol.ld_attn;
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+          w[h] = 0.f;
+          if (h < p.H)
+            w[h] = expf(leaky_relu(segw[h] + __ldg(ac + h), pol.slope) - segm[h]);
+        }
+      } else {
+        edge_weights<HP>(pol, p.H, ee, w);
+      }
+      __syncwarp();
+      cs[lane] = c;
+#pragma unroll
+      for (int h = 0; h < HP; ++h) ws[lane * HP + h] = ok ? w[h] : 0.f;
+      __syncwarp();
+      const int nb = min(32, b - base);
+      const int nbr = (nb + U - 1) / U * U;
+#pragma unroll 1
+      for (int jj = 0; jj < nbr; jj += U) {
+        float v[U][Q][VW];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          t.load(p.feat + (size_t)cs[jj + u] * p.ld_feat, lane, v[u]);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int q = 0; q < Q; ++q) {
+            const float wq = ws[(jj + u) * HP + t.head[q]];
+#pragma unroll
+            for (int i = 0; i < VW; ++i) acc[q][i] = fmaf(wq, v[u][q][i], acc[q][i]);
+          }
+        }
+      }
+    }
+
+    if (first && last) {
+      if constexpr (SOFTMAX) {
+        float inv[HP];
+#pragma unroll
+        for (int h = 0; h < HP; ++h) inv[h] = 1.f / segs[h];
+#pragma unroll
+        for (int q = 0; q < Q; ++q) {
+          const float iv = pick<HP>(inv, t.head[q]);
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[q][i] *= iv;
+        }
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+          if (lane == h && h < p.H) {
+            pol.seg_max[(size_t)s * pol.ld_attn + h] = segm[h];
+            pol.seg_sum[(size_t)s * pol.ld_attn + h] = segs[h];
+          }
+        }
+      }
+      t.store(p.out + (size_t)s * p.ld_out, lane, acc);
+    } else {
+      float* slot = p.scratch + slot_index(chunk_id, first) * p.slot_stride;
+      t.store(slot, lane, acc);
+      if constexpr (SOFTMAX) {
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+          if (lane == h) {
+            slot[p.aux_off + h] = segm[h];
+            slot[p.aux_off + HP + h] = segs[h];
+          }
+        }
+      }
+    }
+  });
+}
+
+// ----- merge of split segments + defaults for empty segments -----------------
+//
+// Blocks [0, boundary_blocks) : one warp per chunk boundary; the warp whose
+//   boundary is the first one inside a segment merges all pieces of that
+//   segment in chunk order.
+// Blocks [boundary_blocks, ...) : one thread per segment, empty segments get
+//   zeros (and, for the softmax policy, max = -1e38 and sum = 0 like the
+//   reference's empty rows).
+template <template <int> class Policy, int HP, int Q, bool VEC>
+__global__ void __launch_bounds__(kThreadsPerCta)
+wgather_fixup_kernel(WGatherParams p, Policy<HP> pol, int boundary_blocks) {
+  constexpr int VW = VEC ? 4 : 1;
+  constexpr bool SOFTMAX = Policy<HP>::kSoftmax;
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  RowTile<Q, VEC> t;
+  t.init(lane, p.width, p.F, p.H);
+
+  if ((int)blockIdx.x < boundary_blocks) {
+    const int bnd = 1 + blockIdx.x * kWarpsPerCta + wib;
+    if (bnd >= p.g.num_chunks) return;
+    const int x = bnd * p.g.chunk;
+    const int s = find_seg(p.g.ptr, p.g.nseg, x);
+    const int beg = __ldg(p.g.ptr + s);
+    if (!(beg < x && beg >= x - p.g.chunk)) return;
+    const int end = __ldg(p.g.ptr + s + 1);
+    const int c0 = bnd - 1;
+    const int c1 = (end - 1) / p.g.chunk;
+    float m[HP], ssum[HP];
+#pragma unroll
+    for (int h = 0; h < HP; ++h) { m[h] = kNegBig; ssum[h] = 0.f; }
+    if constexpr (SOFTMAX) {
+      for (int c = c0; c <= c1; ++c) {
+        const float* slot = p.scratch + slot_index(c, c == c0) * p.slot_stride;
+#pragma unroll
+        for (int h = 0; h < HP; ++h) m[h] = fmaxf(m[h], slot[p.aux_off + h]);
+      }
+    }
+    float acc[Q][VW];
+    t.zero(acc);
+    for (int c = c0; c <= c1; ++c) {
+      const float* slot = p.scratch + slot_index(c, c == c0) * p.slot_stride;
+      float v[Q][VW];
+      t.load(slot, lane, v);
+      if constexpr (SOFTMAX) {
+        float sc[HP];
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+          sc[h] = expf(slot[p.aux_off + h] - m[h]);
+          ssum[h] = fmaf(slot[p.aux_off + HP + h], sc[h], ssum[h]);
+        }
+#pragma unroll
+        for (int q = 0; q < Q; ++q) {
+          const float f = pick<HP>(sc, t.head[q]);
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[q][i] = fmaf(f, v[q][i], acc[q][i]);
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < Q; ++q)
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[q][i] += v[q][i];
+      }
+    }
+    if constexpr (SOFTMAX) {
+      float inv[HP];
+#pragma unroll
+      for (int h = 0; h < HP; ++h) inv[h] = 1.f / ssum[h];
+#pragma unroll
+      for (int q = 0; q < Q; ++q) {
+        const float iv = pick<HP>(inv, t.head[q]);
+#pragma unroll
+        for (int i = 0; i < VW; ++i) acc[q][i] *= iv;
+      }
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        if (lane == h && h < p.H) {
+          pol.seg_max[(size_t)s * pol.ld_attn + h] = m[h];
+          pol.seg_sum[(size_t)s * pol.ld_attn + h] = ssum[h];
+        }
+      }
+    }
+    t.store(p.out + (size_t)s * p.ld_out, lane, acc);
+  } else {
+    const int s = ((int)blockIdx.x - boundary_blocks) * kThreadsPerCta + threadIdx.x;
+    bool empty = false;
+    if (s < p.g.nseg) empty = __ldg(p.g.ptr + s) == __ldg(p.g.ptr + s + 1);
+    unsigned mask = __ballot_sync(kFull, empty);
+    float z[Q][VW];
+    t.zero(z);
+    while (mask) {
+      const int src = __ffs(mask) - 1;
+      mask &= mask - 1;
+      const int se = s - lane + src;
+      t.store(p.out + (size_t)se * p.ld_out, lane, z);
+      if constexpr (SOFTMAX) {
+        if (lane < p.H) {
+          pol.seg_max[(size_t)se * pol.ld_attn + lane] = kNegBig;
+          pol.seg_sum[(size_t)se * pol.ld_attn + lane] = 0.f;
+        }
+      }
+    }
+  }
+}
+
+// ----- host-side launch helpers ----------------------------------------------
+
+inline int round_up4(int x) { return (x + 3) / 4 * 4; }
+
+// Floats of scratch one weighted-gather launch needs for (nnz, H, width).
+inline size_t wgather_scratch_floats(int64_t nnz, int HP, int width) {
+  const int chunk = pick_chunk(nnz);
+  const int nc = num_chunks_for(nnz, chunk);
+  return (size_t)nc * 2 * (size_t)(round_up4(width) + round_up4(2 * HP));
+}
+
+inline int next_pow2(int h) {
+  int p = 1;
+  while (p < h) p <<= 1;
+  return p;
+}
+
+// Calls fn(integral_constant<HP>, integral_constant<Q>, bool_constant<VEC>) for
+// the smallest instantiated tile that covers `width` floats; false if none.
+template <class Fn>
+inline bool dispatch_tile(int HP, int width, bool vec, Fn&& fn) {
+#define GNN_TILE(hp, q, v)                                            \
+  fn(std::integral_constant<int, hp>{}, std::integral_constant<int, q>{}, \
+     std::bool_constant<v>{});                                        \
+  return true;
+#define GNN_TILE_Q(hp)                                     \
+  if (vec) {                                               \
+    if (width <= 128) { GNN_TILE(hp, 1, true) }            \
+    if (width <= 256) { GNN_TILE(hp, 2, true) }            \
+    if (width <= 512) { GNN_TILE(hp, 4, true) }            \
+  } else {                                                 \
+    if (width <= 32) { GNN_TILE(hp, 1, false) }            \
+    if (width <= 64) { GNN_TILE(hp, 2, false) }            \
+    if (width <= 128) { GNN_TILE(hp, 4, false) }           \
+    if (width <= 256) { GNN_TILE(hp, 8, false) }           \
+  }                                                        \
+  return false;
+  switch (HP) {
+    case 1: GNN_TILE_Q(1)
+    case 2: GNN_TILE_Q(2)
+    case 4: GNN_TILE_Q(4)
+    case 8: GNN_TILE_Q(8)
+    default: return false;
+  }
+#undef GNN_TILE_Q
+#undef GNN_TILE
+}
+
+inline int max_tile_width(bool vec) { return vec ? 512 : 256; }
+
+template <template <int> class Policy, int HP, int Q, bool VEC>
+inline void launch_wgather(const WGatherParams& p, const Policy<HP>& pol,
+                           cudaStream_t stream) {
+  if (p.g.num_chunks > 0) {
+    const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
+    wgather_kernel<Policy, HP, Q, VEC><<<blocks, kThreadsPerCta, 0, stream>>>(p, pol);
+  }
+  const int nbound = p.g.num_chunks > 1 ? p.g.num_chunks - 1 : 0;
+  const int bblocks = (nbound + kWarpsPerCta - 1) / kWarpsPerCta;
+  const int sblocks = (p.g.nseg + kThreadsPerCta - 1) / kThreadsPerCta;
+  if (bblocks + sblocks > 0)
+    wgather_fixup_kernel<Policy, HP, Q, VEC>
+        <<<bblocks + sblocks, kThreadsPerCta, 0, stream>>>(p, pol, bblocks);
+}
+
+}  // namespace gnn

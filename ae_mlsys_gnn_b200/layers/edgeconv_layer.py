@@ -1,0 +1,28 @@
+"""EdgeConv layer (reference: layers/edgeconv_layer.py:6-43)."""
+from __future__ import annotations
+
+from torch import nn
+
+from ..operators.fused_edgeconv import fused_edgeconv_op
+
+
+class EdgeConv(nn.Module):
+    """out_i = max_j theta(x_j - x_i) + phi(x_i), computed as
+    max_j (h_dst[i] + h_src[j]) with h_src = theta(x), h_dst = phi(x) - theta(x)."""
+
+    def __init__(self, in_feat, out_feat, batch_norm=False, allow_zero_in_degree=False):
+        super().__init__()
+        self.batch_norm = batch_norm
+        self._allow_zero_in_degree = allow_zero_in_degree
+        self.theta = nn.Linear(in_feat, out_feat, bias=False)
+        self.phi = nn.Linear(in_feat, out_feat, bias=False)
+        if batch_norm:
+            self.bn = nn.BatchNorm1d(out_feat)
+
+    def set_allow_zero_in_degree(self, set_value):
+        self._allow_zero_in_degree = set_value
+
+    def forward(self, k, src_ind, feat):
+        h_theta = self.theta(feat)
+        h_phi = self.phi(feat)
+        return fused_edgeconv_op(k, src_ind, h_theta, h_phi - h_theta)

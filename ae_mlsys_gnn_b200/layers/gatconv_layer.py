@@ -1,0 +1,59 @@
+"""GAT layers (reference: layers/gatconv_layer.py:10-159)."""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from ..operators.fused_gat import fused_gat_fusescatter, fused_gat_op, fused_gat_stash_op
+
+
+class _GATBase(nn.Module):
+    """Parameters and initialisation shared by the three variants: ``W`` (in, H*F),
+    ``attn_l`` / ``attn_r`` (1, H, F), xavier-normal with the ReLU gain
+    (layers/gatconv_layer.py:22-45)."""
+
+    def __init__(self, in_feats, out_feats, num_heads, negative_slope=0.2):
+        super().__init__()
+        self.in_feats = in_feats
+        self.out_feats = out_feats
+        self.num_heads = num_heads
+        self.W = nn.Parameter(torch.empty(in_feats, out_feats * num_heads))
+        self.attn_l = nn.Parameter(torch.zeros(1, num_heads, out_feats))
+        self.attn_r = nn.Parameter(torch.zeros(1, num_heads, out_feats))
+        self.negative_slope = negative_slope
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        gain = nn.init.calculate_gain("relu")
+        nn.init.xavier_normal_(self.W, gain=gain)
+        nn.init.xavier_normal_(self.attn_l, gain=gain)
+        nn.init.xavier_normal_(self.attn_r, gain=gain)
+
+    def project(self, feat):
+        """h = feat @ W viewed (N,H,F); attn_row multiplies the destination (CSR row),
+        attn_col the source (layers/gatconv_layer.py:50-53)."""
+        h = torch.matmul(feat, self.W).view(-1, self.num_heads, self.out_feats)
+        attn_row = (self.attn_l * h).sum(dim=-1)
+        attn_col = (self.attn_r * h).sum(dim=-1)
+        return h, attn_row, attn_col
+
+
+class GATConv(_GATBase):
+    def forward(self, row_ptr, col_ind, col_ptr, row_ind, feat, save_memory=True):
+        h, attn_row, attn_col = self.project(feat)
+        return fused_gat_op(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind,
+                            self.negative_slope, h, save_memory)
+
+
+class GATConv_stash(_GATBase):
+    def forward(self, row_ptr, col_ind, col_ptr, row_ind, feat, permute):
+        h, attn_row, attn_col = self.project(feat)
+        return fused_gat_stash_op(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind,
+                                  self.negative_slope, h, permute)
+
+
+class GATConv_fusescatter(_GATBase):
+    def forward(self, row_ptr, col_ind, col_ptr, row_ind, feat, permute):
+        h, attn_row, attn_col = self.project(feat)
+        return fused_gat_fusescatter(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind,
+                                     self.negative_slope, h, permute)

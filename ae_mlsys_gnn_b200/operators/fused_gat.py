@@ -1,0 +1,214 @@
+"""Fused GAT operators (reference: operators/fused_gat.py).
+
+``fused_gat_op`` is the recompute flavour the reference's ``GATConv`` uses
+(operators/fused_gat.py:30-31, 52-71); ``fused_gat_stash_op`` and
+``fused_gat_fusescatter`` keep the reference signatures (:27-28, :33-34) and, like
+the reference variants, hold the E x H activated logits and attention values
+between forward and backward.  All three produce the same values.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _capi as capi
+
+I32, F32 = torch.int32, torch.float32
+
+
+def _check_graph(row_ptr, col_ind, dev, what="row_ptr/col_ind"):
+    capi.require(row_ptr, I32, f"{what}[0]", 1, dev)
+    capi.require(col_ind, I32, f"{what}[1]", 1, dev)
+
+
+def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat):
+    """(out, edge_max, edge_sum) — fused_gat_SM.gat_forward
+    (src/fused_gat/fused_gat_SM.cu:536-558).  ``attn_row`` and the outputs have one
+    row per CSR row; ``attn_col`` / ``in_feat`` are indexed by ``col_ind``."""
+    dev = in_feat.device
+    capi.require(in_feat, F32, "in_feat", 3)
+    n_rows = row_ptr.numel() - 1
+    H, F = in_feat.shape[1], in_feat.shape[2]
+    capi.require(attn_row, F32, "attn_row", 2, dev)
+    capi.require(attn_col, F32, "attn_col", 2, dev)
+    _check_graph(row_ptr, col_ind, dev)
+    if attn_row.shape != (n_rows, H):
+        raise ValueError(f"attn_row must be ({n_rows},{H}), got {tuple(attn_row.shape)}")
+    if attn_col.shape != (in_feat.shape[0], H):
+        raise ValueError("attn_col must have one row per in_feat row and H columns")
+    nnz = col_ind.numel()
+    out = torch.empty((n_rows, H, F), dtype=F32, device=dev)
+    edge_max = torch.empty((n_rows, H), dtype=F32, device=dev)
+    edge_sum = torch.empty((n_rows, H), dtype=F32, device=dev)
+    nbytes = capi.workspace_bytes("gnn_gat_fwd_workspace_bytes", nnz, H, F)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_fwd", capi.ptr(row_ptr), capi.ptr(col_ind), n_rows, nnz,
+                  capi.ptr(attn_row), capi.ptr(attn_col), capi.ptr(in_feat), H, F,
+                  float(negative_slope), capi.ptr(out), capi.ptr(edge_max), capi.ptr(edge_sum),
+                  capi.ptr(ws), ws.numel(), capi.stream_ptr(dev))
+    return out, edge_max, edge_sum
+
+
+def gat_backward(negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum,
+                 in_feat, attn_row, attn_col, grad_out):
+    """(grad_feat, grad_attn_row, grad_attn_col) — fused_gat_SM.gat_backward
+    (src/fused_gat/fused_gat_SM.cu:865-893) for a square graph."""
+    dev = in_feat.device
+    capi.require(in_feat, F32, "in_feat", 3)
+    capi.require(grad_out, F32, "grad_out", 3, dev)
+    n, H, F = in_feat.shape
+    _check_graph(row_ptr, col_ind, dev)
+    _check_graph(col_ptr, row_ind, dev, "col_ptr/row_ind")
+    for name, t in (("edge_max", edge_max), ("edge_sum", edge_sum), ("attn_row", attn_row),
+                    ("attn_col", attn_col)):
+        capi.require(t, F32, name, 2, dev)
+    if row_ptr.numel() - 1 != n or col_ptr.numel() - 1 != n:
+        raise ValueError("gat_backward expects a square graph with one row per in_feat row")
+    nnz = col_ind.numel()
+    grad_feat = torch.empty_like(in_feat)
+    grad_attn_row = torch.empty((n, H), dtype=F32, device=dev)
+    grad_attn_col = torch.empty((n, H), dtype=F32, device=dev)
+    nbytes = capi.workspace_bytes("gnn_gat_bwd_workspace_bytes", n, nnz, H, F)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_bwd", capi.ptr(row_ptr), capi.ptr(col_ind), capi.ptr(col_ptr),
+                  capi.ptr(row_ind), n, nnz, capi.ptr(edge_max), capi.ptr(edge_sum),
+                  capi.ptr(in_feat), capi.ptr(attn_row), capi.ptr(attn_col), capi.ptr(grad_out),
+                  H, F, float(negative_slope), capi.ptr(grad_feat), capi.ptr(grad_attn_row),
+                  capi.ptr(grad_attn_col), capi.ptr(ws), ws.numel(), capi.stream_ptr(dev))
+    return grad_feat, grad_attn_row, grad_attn_col
+
+
+def gat_backward_row(negative_slope, row_ptr, col_ind, edge_max, edge_sum, in_feat, attn_row,
+                     attn_col, grad_out):
+    """Row pass of the backward on a CSR row block: (grad_attn_row, rowpack)."""
+    dev = in_feat.device
+    n_rows = row_ptr.numel() - 1
+    H, F = in_feat.shape[1], in_feat.shape[2]
+    nnz = col_ind.numel()
+    capi.require(grad_out, F32, "grad_out", 3, dev)
+    grad_attn_row = torch.empty((n_rows, H), dtype=F32, device=dev)
+    rowpack = torch.empty((n_rows, 4, H), dtype=F32, device=dev)
+    nbytes = capi.workspace_bytes("gnn_gat_bwd_row_workspace_bytes", nnz, H, F)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_bwd_row", capi.ptr(row_ptr), capi.ptr(col_ind), n_rows, nnz,
+                  capi.ptr(edge_max), capi.ptr(edge_sum), capi.ptr(in_feat), capi.ptr(attn_row),
+                  capi.ptr(attn_col), capi.ptr(grad_out), H, F, float(negative_slope),
+                  capi.ptr(grad_attn_row), capi.ptr(rowpack), capi.ptr(ws), ws.numel(),
+                  capi.stream_ptr(dev))
+    return grad_attn_row, rowpack
+
+
+def gat_backward_col(negative_slope, col_ptr, row_ind, in_feat, attn_col, rowpack, grad_out):
+    """Column pass of the backward on a CSC column block: (grad_feat, grad_attn_col).
+    ``in_feat`` / ``attn_col`` have one row per CSC column; ``rowpack`` / ``grad_out``
+    are indexed by ``row_ind``."""
+    dev = in_feat.device
+    n_cols = col_ptr.numel() - 1
+    H, F = in_feat.shape[1], in_feat.shape[2]
+    nnz = row_ind.numel()
+    grad_feat = torch.empty((n_cols, H, F), dtype=F32, device=dev)
+    grad_attn_col = torch.empty((n_cols, H), dtype=F32, device=dev)
+    nbytes = capi.workspace_bytes("gnn_gat_bwd_col_workspace_bytes", nnz, H, F)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_bwd_col", capi.ptr(col_ptr), capi.ptr(row_ind), n_cols, nnz,
+                  capi.ptr(in_feat), capi.ptr(attn_col), capi.ptr(rowpack), capi.ptr(grad_out),
+                  H, F, float(negative_slope), capi.ptr(grad_feat), capi.ptr(grad_attn_col),
+                  capi.ptr(ws), ws.numel(), capi.stream_ptr(dev))
+    return grad_feat, grad_attn_col
+
+
+def gat_edge_alpha(attn_row, attn_col, row_ptr, col_ind, edge_max, edge_sum, negative_slope):
+    """(edge_relu_csr, edge_softmax_csr), each (E, H)."""
+    dev = attn_row.device
+    n_rows, H = attn_row.shape
+    nnz = col_ind.numel()
+    edge_relu = torch.empty((nnz, H), dtype=F32, device=dev)
+    edge_alpha = torch.empty((nnz, H), dtype=F32, device=dev)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_edge_alpha", capi.ptr(row_ptr), capi.ptr(col_ind), n_rows, nnz,
+                  capi.ptr(attn_row), capi.ptr(attn_col), capi.ptr(edge_max), capi.ptr(edge_sum),
+                  H, float(negative_slope), capi.ptr(edge_relu), capi.ptr(edge_alpha),
+                  capi.stream_ptr(dev))
+    return edge_relu, edge_alpha
+
+
+class FusedGATFunction_SM(torch.autograd.Function):
+    """Recompute flavour (operators/fused_gat.py:52-71): only edge_max / edge_sum (N x H)
+    are kept; the backward recomputes the attention values."""
+
+    @staticmethod
+    def forward(ctx, attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind, negative_slope,
+                in_feat):
+        attn_row = attn_row.contiguous()
+        attn_col = attn_col.contiguous()
+        in_feat = in_feat.contiguous()
+        out, edge_max, edge_sum = gat_forward(attn_row, attn_col, row_ptr, col_ind,
+                                              negative_slope, in_feat)
+        ctx.save_for_backward(row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, in_feat,
+                              attn_row, attn_col)
+        ctx.negative_slope = negative_slope
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, in_feat, attn_row,
+         attn_col) = ctx.saved_tensors
+        grad_feat, grad_attn_row, grad_attn_col = gat_backward(
+            ctx.negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, in_feat,
+            attn_row, attn_col, grad_out.contiguous())
+        return grad_attn_row, grad_attn_col, None, None, None, None, None, grad_feat
+
+
+class FusedGATFunction_stash(torch.autograd.Function):
+    """Stash flavour (operators/fused_gat.py:73-87): additionally materialises
+    edge_relu_csr and edge_softmax_csr (E x H) in the forward and keeps them."""
+
+    @staticmethod
+    def forward(ctx, attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind, negative_slope,
+                in_feat, permute):
+        attn_row = attn_row.contiguous()
+        attn_col = attn_col.contiguous()
+        in_feat = in_feat.contiguous()
+        out, edge_max, edge_sum = gat_forward(attn_row, attn_col, row_ptr, col_ind,
+                                              negative_slope, in_feat)
+        edge_relu, edge_alpha = gat_edge_alpha(attn_row, attn_col, row_ptr, col_ind, edge_max,
+                                               edge_sum, negative_slope)
+        ctx.save_for_backward(row_ptr, col_ind, col_ptr, row_ind, permute, edge_alpha, edge_relu,
+                              edge_max, edge_sum, in_feat, attn_row, attn_col)
+        ctx.negative_slope = negative_slope
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (row_ptr, col_ind, col_ptr, row_ind, _permute, _edge_alpha, _edge_relu, edge_max,
+         edge_sum, in_feat, attn_row, attn_col) = ctx.saved_tensors
+        grad_feat, grad_attn_row, grad_attn_col = gat_backward(
+            ctx.negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, in_feat,
+            attn_row, attn_col, grad_out.contiguous())
+        return grad_attn_row, grad_attn_col, None, None, None, None, None, grad_feat, None
+
+
+class FusedGATFunction(FusedGATFunction_stash):
+    """"fusescatter" flavour (operators/fused_gat.py:36-50); same values and the same
+    kept tensors as the stash flavour."""
+
+
+def fused_gat_op(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind, negative_slope, in_feat,
+                 save_memory=True):
+    return FusedGATFunction_SM.apply(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind,
+                                     negative_slope, in_feat)
+
+
+def fused_gat_stash_op(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind, negative_slope,
+                       in_feat, permute):
+    return FusedGATFunction_stash.apply(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind,
+                                        negative_slope, in_feat, permute)
+
+
+def fused_gat_fusescatter(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind, negative_slope,
+                          in_feat, permute):
+    return FusedGATFunction.apply(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind,
+                                  negative_slope, in_feat, permute)

@@ -1,0 +1,204 @@
+/*
+ * gnn_b200 — C ABI of the sm_100a fused GNN sparse kernels.
+ *
+ * One shared library (libgnn_b200.so) replaces the per-operator pybind11 modules
+ * that the reference JIT-builds from src/ at import time
+ * (operators/fused_gat.py:9-25, operators/fused_edgeconv.py:9-13,
+ * operators/fused_gmmconv.py:10-39, ...).  Conventions:
+ *
+ *  - every pointer is a device pointer on the current CUDA device unless stated;
+ *  - indices are int32, values fp32, all arrays dense and contiguous, row-major;
+ *  - "CSR" is the in-edge CSR of the reference: segment = destination node,
+ *    idx = source node.  A segment array (ptr[n_seg+1], idx[nnz]) may equally be
+ *    a CSC (segment = source, idx = destination) or one rank's row block of a
+ *    partitioned graph: arrays described as "segment indexed" have n_seg rows,
+ *    arrays described as "gathered" are indexed by the values stored in idx;
+ *  - the caller owns every buffer, outputs and workspace included.  The byte
+ *    size of a workspace comes from the matching *_workspace_bytes function;
+ *    a workspace is scratch: its contents are undefined before and after a call;
+ *  - every function only enqueues work on `stream` and returns 0, or a negative
+ *    GNN_ERR_* code with a message available from gnn_last_error_string().  No
+ *    function aborts, allocates device memory or synchronises (the reference
+ *    asserts / exit()s: src/fused_gat/fused_gat_SM.cpp:22-36,
+ *    src/util/computeUtil.h:14-22);
+ *  - outputs are deterministic (bit-identical from run to run) except where a
+ *    function says it uses atomics.
+ */
+#ifndef GNN_B200_H_
+#define GNN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GNN_B200_ABI_VERSION 1
+
+#define GNN_OK 0
+#define GNN_ERR_INVALID_ARG (-1)
+#define GNN_ERR_CUDA (-2)
+#define GNN_ERR_WORKSPACE (-3)
+#define GNN_ERR_UNSUPPORTED (-4)
+#define GNN_ERR_LIMIT (-5)
+
+#ifndef __CUDA_RUNTIME_H__
+typedef struct CUstream_st* cudaStream_t;
+#endif
+
+/* Message of the last error returned on the calling thread. */
+const char* gnn_last_error_string(void);
+int gnn_abi_version(void);
+
+/* ---- csr2csc -----------------------------------------------------------------
+ * Replaces transpose.csr2csc (src/csr2csc/csr2csc.cu:7-43, bound in
+ * src/csr2csc/csr2csc.cc) and the host SciPy transpose of the training scripts
+ * (script/train/train_gatconv_our.py:107-121).  Stable counting order: inside a
+ * column the CSR order is kept, so row ids ascend.  permute[i] is the CSR
+ * position of the i-th CSC edge, as int32 (the reference carries it as float32).
+ * The matrix may be rectangular (n_rows x n_cols). */
+int gnn_csr2csc_workspace_bytes(int64_t nnz, size_t* bytes);
+int gnn_csr2csc(const int* row_ptr, const int* col_ind, int64_t n_rows, int64_t n_cols,
+                int64_t nnz, int* col_ptr /*[n_cols+1]*/, int* row_ind /*[nnz]*/,
+                int* permute /*[nnz]*/, void* workspace, size_t workspace_bytes,
+                cudaStream_t stream);
+
+/* ---- fused GAT, recompute flavour ------------------------------------------------
+ * gnn_gat_fwd replaces fused_gat_SM.gat_forward
+ * (src/fused_gat/fused_gat_SM.cpp:14-38, src/fused_gat/fused_gat_SM.cu:514-558):
+ *   e = LeakyReLU(attn_row[r,h] + attn_col[c,h]); m = max e; s = sum exp(e - m)
+ *   out[r,h,:] = sum_c exp(e - m)/s * in_feat[c,h,:]; edge_max = m; edge_sum = s
+ * A row without edges gets out = 0, edge_max = -1e38, edge_sum = 0.
+ * attn_row/out/edge_max/edge_sum are segment indexed [n_rows]; attn_col/in_feat
+ * are gathered. */
+int gnn_gat_fwd_workspace_bytes(int64_t nnz, int H, int F, size_t* bytes);
+int gnn_gat_fwd(const int* row_ptr, const int* col_ind, int64_t n_rows, int64_t nnz,
+                const float* attn_row /*[n_rows,H]*/, const float* attn_col /*[*,H]*/,
+                const float* in_feat /*[*,H,F]*/, int H, int F, float negative_slope,
+                float* out /*[n_rows,H,F]*/, float* edge_max /*[n_rows,H]*/,
+                float* edge_sum /*[n_rows,H]*/, void* workspace, size_t workspace_bytes,
+                cudaStream_t stream);
+
+/* gnn_gat_bwd replaces fused_gat_SM.gat_backward
+ * (src/fused_gat/fused_gat_SM.cpp:55-118, src/fused_gat/fused_gat_SM.cu:831-893)
+ * on a square graph given as CSR and CSC.  No E x H temporary, no atomics.
+ * Requires H <= 8 and H*F <= 512 (16-byte aligned rows, F % 4 == 0) or 256. */
+int gnn_gat_bwd_workspace_bytes(int64_t n_rows, int64_t nnz, int H, int F, size_t* bytes);
+int gnn_gat_bwd(const int* row_ptr, const int* col_ind, const int* col_ptr, const int* row_ind,
+                int64_t n, int64_t nnz, const float* edge_max, const float* edge_sum,
+                const float* in_feat, const float* attn_row, const float* attn_col,
+                const float* grad_out, int H, int F, float negative_slope,
+                float* grad_feat /*[n,H,F]*/, float* grad_attn_row /*[n,H]*/,
+                float* grad_attn_col /*[n,H]*/, void* workspace, size_t workspace_bytes,
+                cudaStream_t stream);
+
+/* The two passes of gnn_gat_bwd, exposed so that a partitioned graph can
+ * exchange rowpack and grad_out between them.  No counterpart in the reference,
+ * which is single-GPU.
+ *  row pass: CSR row block; edge_max/edge_sum/attn_row/grad_out segment indexed,
+ *            in_feat/attn_col gathered.  Writes grad_attn_row [n_rows,H] and
+ *            rowpack [n_rows,4,H] = {attn_row, edge_max, 1/edge_sum, S}.
+ *  col pass: CSC column block; in_feat/attn_col segment indexed, rowpack/grad_out
+ *            gathered.  Writes grad_feat [n_cols,H,F], grad_attn_col [n_cols,H]. */
+int gnn_gat_bwd_row_workspace_bytes(int64_t nnz, int H, int F, size_t* bytes);
+int gnn_gat_bwd_row(const int* row_ptr, const int* col_ind, int64_t n_rows, int64_t nnz,
+                    const float* edge_max, const float* edge_sum, const float* in_feat,
+                    const float* attn_row, const float* attn_col, const float* grad_out,
+                    int H, int F, float negative_slope, float* grad_attn_row, float* rowpack,
+                    void* workspace, size_t workspace_bytes, cudaStream_t stream);
+int gnn_gat_bwd_col_workspace_bytes(int64_t nnz, int H, int F, size_t* bytes);
+int gnn_gat_bwd_col(const int* col_ptr, const int* row_ind, int64_t n_cols, int64_t nnz,
+                    const float* in_feat, const float* attn_col, const float* rowpack,
+                    const float* grad_out, int H, int F, float negative_slope,
+                    float* grad_feat, float* grad_attn_col, void* workspace,
+                    size_t workspace_bytes, cudaStream_t stream);
+
+/* Per-edge activated logits and normalised attention (E x H each), the tensors the
+ * stash / fusescatter variants keep: fused_gat_stash.gat_forward and
+ * fused_gat.gat_forward (src/fused_gat/fused_gat_stash.cu:193-288,
+ * src/fused_gat/fused_gat.cu:235-300). */
+int gnn_gat_edge_alpha(const int* row_ptr, const int* col_ind, int64_t n_rows, int64_t nnz,
+                       const float* attn_row, const float* attn_col, const float* edge_max,
+                       const float* edge_sum, int H, float negative_slope,
+                       float* edge_relu /*[nnz,H]*/, float* edge_alpha /*[nnz,H]*/,
+                       cudaStream_t stream);
+
+/* ---- fused EdgeConv ----------------------------------------------------------------
+ * Replaces fused_edgeconv.edgeconv_forward / edgeconv_backward
+ * (src/fused_edgeconv/fused_edgeconv.cpp:10-57, fused_edgeconv.cu:148-200).
+ *   out[i,f] = max_j (h_dst[i,f] + h_src[src_ind[i*k+j],f]),  max_idx = winning id
+ * with the reference's tie rule, so max_idx is bit-exact; it is int32 here (the
+ * reference stores it in a float32 tensor).  The backward zero-fills grad_src and
+ * scatters with fp32 atomics (sum order not fixed). */
+int gnn_edgeconv_fwd(int k, const int* src_ind /*[n*k]*/, const float* h_src /*[*,F]*/,
+                     const float* h_dst /*[n,F]*/, int64_t n, int F, float* out /*[n,F]*/,
+                     int* max_idx /*[n,F]*/, cudaStream_t stream);
+int gnn_edgeconv_bwd(const float* grad_out /*[n,F]*/, const int* max_idx /*[n,F]*/, int64_t n,
+                     int64_t n_src, int F, float* grad_src /*[n_src,F]*/, cudaStream_t stream);
+
+/* ---- fused GMMConv ------------------------------------------------------------------
+ * gnn_gmm_fwd replaces gmm.gmmconv (src/fused_gmmconv/gmmconv.cc,
+ * gmmconv.cu:48-80,201-219):
+ *   w[e,k] = exp(-0.5 sum_d ((pseudo[pe,d]-mu[k,d]) inv_sigma[k,d])^2)
+ *   out[s,k,:] = sum_e w[e,k] node_feat[idx[e],k,:]
+ * pe = perm ? perm[e] : e, so the transposed pass of the backward needs no
+ * separate mhtranspose of pseudo (operators/fused_gmmconv.py:54-56).
+ * Requires K <= 8 and K*F <= 512 (aligned) / 256. */
+int gnn_gmm_fwd_workspace_bytes(int64_t nnz, int K, int F, size_t* bytes);
+int gnn_gmm_fwd(const int* ptr, const int* idx, int64_t n_seg, int64_t nnz,
+                const float* node_feat /*[*,K,F]*/, const float* pseudo /*[nnz,D]*/,
+                const int* perm /*[nnz] or NULL*/, const float* mu /*[K,D]*/,
+                const float* inv_sigma /*[K,D]*/, int K, int D, int F,
+                float* out /*[n_seg,K,F]*/, void* workspace, size_t workspace_bytes,
+                cudaStream_t stream);
+/* gmm.Gaussian (gmmconv.cu:34-46,186-199). */
+int gnn_gaussian_fwd(const float* pseudo, const float* mu, const float* inv_sigma, int64_t E,
+                     int K, int D, float* out /*[E,K]*/, cudaStream_t stream);
+/* gmm.GaussianBp (gmmconv.cu:154-184,265-285) with the analytic gradients; D <= 8. */
+int gnn_gaussian_bwd_workspace_bytes(int64_t E, int K, int D, size_t* bytes);
+int gnn_gaussian_bwd(const float* pseudo, const float* mu, const float* inv_sigma,
+                     const float* grad_w /*[E,K]*/, int64_t E, int K, int D,
+                     float* grad_pseudo /*[E,D]*/, float* grad_mu /*[K,D]*/,
+                     float* grad_inv_sigma /*[K,D]*/, void* workspace, size_t workspace_bytes,
+                     cudaStream_t stream);
+
+/* ---- unfused operators that share the API ------------------------------------------------
+ * gnn_mhspmm: mhspmm.mhspmm (src/spmm/mhspmm.cu:4-66) and, with H = 1, the
+ * single-head csr_spmm / csr_spmm_no_edge_value that operators/spmm.py:35-41
+ * expects (att == NULL: unit weights).  perm (optional) reads att[perm[e]]. */
+int gnn_mhspmm_workspace_bytes(int64_t nnz, int H, int F, size_t* bytes);
+int gnn_mhspmm(const int* ptr, const int* idx, int64_t n_seg, int64_t nnz,
+               const float* att /*[nnz,H] or NULL*/, const int* perm /*[nnz] or NULL*/,
+               const float* feat /*[*,H,F]*/, int H, int F, float* out /*[n_seg,H,F]*/,
+               void* workspace, size_t workspace_bytes, cudaStream_t stream);
+/* mhsddmm.mhsddmm (src/sddmm/mhsddmm.cu:5-99) and, with H = 1, sddmm.csr_sddmm
+ * (src/sddmm/sddmm.cu:361-404): out[e,h] = <A[seg(e),h,:], B[idx[e],h,:]>. */
+int gnn_mhsddmm(const int* ptr, const int* idx, int64_t n_seg, int64_t nnz,
+                const float* A /*[n_seg,H,F]*/, const float* B /*[*,H,F]*/, int H, int F,
+                float* out /*[nnz,H]*/, cudaStream_t stream);
+/* sddmm.coo_sddmm (src/sddmm/sddmm.cpp:12-27). */
+int gnn_sddmm_coo(const int* row_ind, const int* col_ind, int64_t nnz, const float* A,
+                  const float* B, int F, float* out /*[nnz]*/, cudaStream_t stream);
+/* mhtranspose.mhtranspose (src/csr2csc/mhtranspose.cu:6-47): out[i,:] = vals[permute[i],:]. */
+int gnn_mhtranspose(const int* permute, const float* vals /*[E,H]*/, int64_t E, int H,
+                    float* out /*[E,H]*/, cudaStream_t stream);
+/* u_add_v.u_add_v_forward / u_add_v_backward (src/u_add_v/u_add_v.cu:4-90).  The
+ * backward zero-fills both outputs and accumulates with fp32 atomics. */
+int gnn_u_add_v_fwd(const int* row_ptr, const int* col_ind, int64_t n_rows, int64_t nnz,
+                    const float* row_val /*[n_rows,F]*/, const float* col_val /*[*,F]*/, int F,
+                    float* out /*[nnz,F]*/, cudaStream_t stream);
+int gnn_u_add_v_bwd(const int* row_ptr, const int* col_ind, int64_t n_rows, int64_t n_cols,
+                    int64_t nnz, const float* grad_out /*[nnz,F]*/, int F,
+                    float* grad_row /*[n_rows,F]*/, float* grad_col /*[n_cols,F]*/,
+                    cudaStream_t stream);
+/* edge_softmax.edge_softmax / edge_softmax_backward (src/edge_softmax/edge_softmax.cu:7-128). */
+int gnn_edge_softmax_fwd(const int* row_ptr, int64_t n_rows, int64_t nnz, const float* in /*[nnz,H]*/,
+                         int H, float* out /*[nnz,H]*/, cudaStream_t stream);
+int gnn_edge_softmax_bwd(const int* row_ptr, int64_t n_rows, int64_t nnz, const float* y,
+                         const float* grad_y, int H, float* grad_x, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GNN_B200_H_ */

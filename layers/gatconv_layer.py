@@ -1,0 +1,2 @@
+from ae_mlsys_gnn_b200.layers import gatconv_layer as _impl
+globals().update({k: v for k, v in vars(_impl).items() if not k.startswith('__')})

@@ -1,0 +1,3 @@
+from ae_mlsys_gnn_b200.operators.csr2csc import *  # noqa: F401,F403
+from ae_mlsys_gnn_b200.operators import csr2csc as _impl
+globals().update({k: v for k, v in vars(_impl).items() if not k.startswith('__')})
