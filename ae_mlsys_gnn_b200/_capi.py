@@ -106,8 +106,57 @@ def check(rc: int, what: str) -> None:
         raise GnnError(f"{what} failed with code {rc}: {last_error()}")
 
 
+# Kernels launched by one call of each entry point (main kernels, merge kernels,
+# memsets excluded); bench.py uses it to count its own launches.
+KERNELS_PER_CALL = {
+    "gnn_csr2csc": None,  # depends on the number of radix passes, see launches_csr2csc
+    "gnn_gat_fwd": 2, "gnn_gat_bwd": 4, "gnn_gat_bwd_row": 2, "gnn_gat_bwd_col": 2,
+    "gnn_gat_edge_alpha": 1, "gnn_edgeconv_fwd": 1, "gnn_edgeconv_bwd": 1, "gnn_gmm_fwd": 2,
+    "gnn_gaussian_fwd": 1, "gnn_gaussian_bwd": 2, "gnn_mhspmm": 2, "gnn_mhsddmm": 1,
+    "gnn_sddmm_coo": 1, "gnn_mhtranspose": 1, "gnn_u_add_v_fwd": 1, "gnn_u_add_v_bwd": 1,
+    "gnn_edge_softmax_fwd": 1, "gnn_edge_softmax_bwd": 1,
+}
+
+
+class CallTimer:
+    """Optional per-entry-point timing with CUDA events on the launching stream.
+    ``records`` holds (name, start_event, end_event) for every call made while the
+    timer is installed; ``counts`` the number of calls per entry point."""
+
+    def __init__(self, with_events: bool = True):
+        self.with_events = with_events
+        self.records: list[tuple[str, torch.cuda.Event, torch.cuda.Event]] = []
+        self.counts: dict[str, int] = {}
+
+    def totals_ms(self) -> dict[str, float]:
+        out: dict[str, float] = {}
+        for name, a, b in self.records:
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        return out
+
+
+_timer: CallTimer | None = None
+
+
+def install_timer(timer: CallTimer | None) -> None:
+    global _timer
+    _timer = timer
+
+
 def call(name: str, *args) -> None:
+    t = _timer
+    if t is None:
+        check(getattr(lib(), name)(*args), name)
+        return
+    t.counts[name] = t.counts.get(name, 0) + 1
+    if not t.with_events:
+        check(getattr(lib(), name)(*args), name)
+        return
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
     check(getattr(lib(), name)(*args), name)
+    b.record()
+    t.records.append((name, a, b))
 
 
 def workspace_bytes(name: str, *args) -> int:

@@ -120,10 +120,12 @@ def chung_lu_graph(n: int, mean_deg: float, max_deg: float, seed: int = 0, devic
 
 
 def rmat_graph(n: int, n_pairs: int, abcd=(0.57, 0.19, 0.19, 0.05), seed: int = 0, device="cpu",
-               symmetric: bool = True) -> Graph:
+               symmetric: bool = True, relabel: bool = True) -> Graph:
     """R-MAT on ceil(log2 n) bits; pairs with an endpoint >= n are discarded, the rest
     symmetrised, deduplicated and given self-loops (config 5).  ``n_pairs`` is the
-    number of generated (undirected) pairs before those steps."""
+    number of generated (undirected) pairs before those steps.  With ``relabel`` the
+    node ids are shuffled (seeded), as Graph500-style generators do, so that degree is
+    not a function of the id."""
     g = _gen(seed, device)
     bits = max(1, math.ceil(math.log2(n)))
     a, b, c, _ = abcd
@@ -147,7 +149,11 @@ def rmat_graph(n: int, n_pairs: int, abcd=(0.57, 0.19, 0.19, 0.05), seed: int = 
         parts.append(torch.unique(k))
     key = torch.unique(torch.cat(parts))
     d = torch.div(key, n, rounding_mode="floor")
-    return csr_from_edges(n, d, key - d * n)
+    s = key - d * n
+    if relabel:
+        perm = torch.randperm(n, generator=g, device=device)
+        d, s = perm[d], perm[s]
+    return csr_from_edges(n, d, s)
 
 
 def knn_sources(points: torch.Tensor, k: int) -> torch.Tensor:

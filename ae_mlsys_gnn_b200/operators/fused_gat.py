@@ -64,6 +64,20 @@ def gat_backward(negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, e
         capi.require(t, F32, name, 2, dev)
     if row_ptr.numel() - 1 != n or col_ptr.numel() - 1 != n:
         raise ValueError("gat_backward expects a square graph with one row per in_feat row")
+    # the two passes of gnn_gat_bwd, called one after the other so that each can be timed
+    grad_attn_row, rowpack = gat_backward_row(negative_slope, row_ptr, col_ind, edge_max, edge_sum,
+                                              in_feat, attn_row, attn_col, grad_out)
+    grad_feat, grad_attn_col = gat_backward_col(negative_slope, col_ptr, row_ind, in_feat, attn_col,
+                                                rowpack, grad_out)
+    return grad_feat, grad_attn_row, grad_attn_col
+
+
+def gat_backward_single_call(negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum,
+                             in_feat, attn_row, attn_col, grad_out):
+    """Same result as ``gat_backward`` through the single entry point gnn_gat_bwd (both
+    passes and the per-row pack inside one caller-provided workspace)."""
+    dev = in_feat.device
+    n, H, F = in_feat.shape
     nnz = col_ind.numel()
     grad_feat = torch.empty_like(in_feat)
     grad_attn_row = torch.empty((n, H), dtype=F32, device=dev)

@@ -1,0 +1,586 @@
+#!/usr/bin/env python
+"""Benchmark of the fused GNN sparse-kernel path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload C1..C5] [--impl reference]
+
+One "step" is one training epoch of the workload's model on its synthetic graph:
+forward, loss, backward and Adam update over the whole graph (the reference's epoch,
+script/train/train_gatconv_our.py:184-200).  Prints ONE JSON line (rank 0).
+
+Default workload: C5, the 3-layer GAT (4x128, 4x128, 1x47) on the R-MAT graph with
+2,449,029 nodes and ~124 M directed edges — the configuration the 1/2/4/8-GPU metric
+is quoted on; it fits one GPU, so the same workload is timed at every N (strong
+scaling: destination-row blocks over the ranks, all-gather of projected features).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+import torch.nn.functional as F  # noqa: E402
+
+METRIC = "fwd_bwd_epoch_ms"
+UNIT = "ms/epoch"
+
+WORKLOADS = {
+    "C1": dict(kind="gat", desc="GAT 2-layer, 2,708 nodes / 10,556+2,708 edges, in 1433, 8x8 -> 1x7",
+               n=2708, edges=10556, in_dim=1433, hidden=[8], heads=[8], classes=7),
+    "C2": dict(kind="gat", desc="GAT 2-layer, Chung-Lu power-law 232,965 nodes / ~114.6M edges, in 602, 4x64 -> 1x41",
+               n=232965, mean_deg=492, max_deg=21600, in_dim=602, hidden=[64], heads=[4], classes=41),
+    "C3": dict(kind="edgeconv", desc="DGCNN 4 EdgeConv layers (64,64,128,256), 32 clouds x 1024 points, kNN k=20, 40 classes",
+               batch=32, points=1024, k=20, dims=[64, 64, 128, 256], classes=40),
+    "C4": dict(kind="gmm", desc="MoNet 2 GMMConv layers, 19,717 nodes / 88,648+19,717 edges, in 500, K=3, D=2, hidden 16, 3 classes",
+               n=19717, edges=88648, in_dim=500, hidden=16, classes=3, kernels=3, dim=2),
+    "C5": dict(kind="gat", desc="GAT 3-layer, R-MAT 2,449,029 nodes / ~124M directed edges, in 100, 4x128 -> 4x128 -> 1x47",
+               n=2449029, rmat_pairs=108_000_000, in_dim=100, hidden=[128, 128], heads=[4, 4], classes=47),
+}
+
+
+# ----------------------------------------------------------------------------------------
+# helpers
+# ----------------------------------------------------------------------------------------
+
+def env_int(name, default):
+    return int(os.environ.get(name, default))
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason sampling during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+                except ValueError:
+                    continue
+                for nm, v in zip(names, f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(nm)
+        finally:
+            try:
+                os.unlink(self.path)
+            except OSError:
+                pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "power_w_max": max(power), "samples": len(sm)}
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def algorithmic_bytes(name: str, n: int, e: int, H: int, Fw: int, D: int = 0) -> float:
+    """Bytes one call of an entry point must move when every gathered row is read once
+    per edge and every per-node array once (no cache reuse)."""
+    HF = H * Fw
+    if name == "gnn_gat_fwd":
+        return 4.0 * e * (1 + H + HF) + 4.0 * n * (1 + 3 * H + HF)
+    if name == "gnn_gat_bwd_row":
+        return 4.0 * e * (1 + H + HF) + 4.0 * n * (1 + HF + 3 * H)
+    if name == "gnn_gat_bwd_col":
+        return 4.0 * e * (1 + 3 * H + HF) + 4.0 * n * (1 + HF + 3 * H)
+    if name == "gnn_edgeconv_fwd":
+        return 4.0 * e * (1 + Fw) + 12.0 * n * Fw
+    if name == "gnn_edgeconv_bwd":
+        return 16.0 * n * Fw
+    if name == "gnn_gmm_fwd":
+        return 4.0 * e * (1 + D + HF) + 4.0 * n * (1 + HF)
+    if name == "gnn_mhsddmm":
+        return 4.0 * e * (1 + HF + H) + 4.0 * n * (1 + HF)
+    return 0.0
+
+
+class BytesLedger:
+    """Wraps _capi.call so that every timed entry-point call is stored with the
+    algorithmic bytes of its arguments."""
+
+    def __init__(self):
+        from ae_mlsys_gnn_b200 import _capi
+
+        self.capi = _capi
+        self.timer = _capi.CallTimer(with_events=True)
+        self.bytes: list[float] = []
+        self._orig = _capi.call
+
+    def __enter__(self):
+        capi, ledger = self.capi, self
+        capi.install_timer(self.timer)
+        orig = self._orig
+
+        def call(name, *args):
+            ledger.bytes.append(ledger._bytes_of(name, args))
+            orig(name, *args)
+
+        capi.call = call  # operator modules look the function up as capi.call at call time
+        return self
+
+    def __exit__(self, *exc):
+        self.capi.call = self._orig
+        self.capi.install_timer(None)
+
+    @staticmethod
+    def _bytes_of(name, a):
+        if name == "gnn_gat_fwd":
+            return algorithmic_bytes(name, a[2], a[3], a[7], a[8])
+        if name == "gnn_gat_bwd_row":
+            return algorithmic_bytes(name, a[2], a[3], a[10], a[11])
+        if name == "gnn_gat_bwd_col":
+            return algorithmic_bytes(name, a[2], a[3], a[8], a[9])
+        if name == "gnn_edgeconv_fwd":
+            return algorithmic_bytes(name, a[4], a[4] * a[0], 1, a[5])
+        if name == "gnn_edgeconv_bwd":
+            return algorithmic_bytes(name, a[2], 0, 1, a[4])
+        if name == "gnn_gmm_fwd":
+            return algorithmic_bytes(name, a[2], a[3], a[9], a[11], a[10])
+        if name == "gnn_mhsddmm":
+            return algorithmic_bytes(name, a[2], a[3], a[6], a[7])
+        return 0.0
+
+    def summary(self):
+        per = {}
+        for (name, s, t), b in zip(self.timer.records, self.bytes):
+            d = per.setdefault(name, {"ms": 0.0, "bytes": 0.0, "calls": 0})
+            d["ms"] += s.elapsed_time(t)
+            d["bytes"] += b
+            d["calls"] += 1
+        return per
+
+
+def count_launches(counts: dict, csr2csc_launches: int) -> int:
+    from ae_mlsys_gnn_b200._capi import KERNELS_PER_CALL
+
+    total = 0
+    for name, c in counts.items():
+        k = KERNELS_PER_CALL.get(name)
+        total += c * (csr2csc_launches if k is None else k)
+    return total
+
+
+def csr2csc_launch_count(n_cols: int, nnz: int) -> int:
+    bits = 1
+    while bits < 31 and (1 << bits) < n_cols:
+        bits += 1
+    passes = (bits + 7) // 8
+    tiles = max(1, (nnz + 4095) // 4096)
+    scan = 3 if (256 * tiles + 4095) // 4096 > 1 else 1
+    return passes * (2 + scan) + 3
+
+
+# ----------------------------------------------------------------------------------------
+# workload construction (device-side, seeded; nothing here is timed)
+# ----------------------------------------------------------------------------------------
+
+def build_inputs(wl: dict, device, seed: int, scale: float = 1.0):
+    """Returns a dict with the graph / inputs / labels of a workload on `device`.
+    ``scale`` < 1 builds the same generator at 1/scale fewer nodes and edges (used for
+    the bounded CPU sample)."""
+    from ae_mlsys_gnn_b200 import graphs as G
+
+    kind = wl["kind"]
+    if kind == "edgeconv":
+        batch = max(1, int(round(wl["batch"] * scale)))
+        pts = G.unit_ball_points(batch, wl["points"], seed, device)
+        src = G.knn_sources(pts, wl["k"])
+        labels = G.uniform_labels(batch, wl["classes"], seed + 2, device)
+        return dict(points=pts, src=src, labels=labels, n=batch * wl["points"], nnz=int(src.numel()))
+    n = max(64, int(round(wl["n"] * scale)))
+    if "rmat_pairs" in wl:
+        g = G.rmat_graph(n, int(wl["rmat_pairs"] * scale), seed=seed, device=device)
+    elif "mean_deg" in wl:
+        # a scaled-down sample keeps the degree law but cannot keep the degrees themselves
+        mean = min(wl["mean_deg"], n / 32)
+        g = G.chung_lu_graph(n, mean, min(n / 2, mean * wl["max_deg"] / wl["mean_deg"]), seed=seed,
+                             device=device)
+    else:
+        g = G.uniform_graph(n, int(wl["edges"] * scale), seed=seed, device=device)
+    if wl["name"] == "C1":
+        x = G.bag_of_words(n, wl["in_dim"], 0.0127, seed + 1, device)
+    elif kind == "gmm":
+        x = G.sparse_l1_features(n, wl["in_dim"], 0.1, seed + 1, device)
+    else:
+        x = G.normal_features(n, wl["in_dim"], seed + 1, device)
+    labels = G.uniform_labels(n, wl["classes"], seed + 2, device)
+    out = dict(graph=g, x=x, labels=labels, n=n, nnz=g.nnz)
+    if kind == "gmm":
+        out["pseudo"] = G.degree_pseudo(g)
+    return out
+
+
+def make_model(wl: dict, cpu: bool = False):
+    if cpu:
+        from oracle import cpu_models as M
+        if wl["kind"] == "gat":
+            return M.CpuGAT(wl["in_dim"], wl["hidden"], wl["heads"], wl["classes"], 1)
+        if wl["kind"] == "edgeconv":
+            return M.CpuDGCNN(wl["k"], wl["dims"], wl["classes"])
+        return M.CpuMoNet(wl["in_dim"], wl["hidden"], wl["classes"], 2, wl["dim"], wl["kernels"])
+    from ae_mlsys_gnn_b200 import models as M
+    if wl["kind"] == "gat":
+        return M.GAT(wl["in_dim"], wl["hidden"], wl["heads"], wl["classes"], 1)
+    if wl["kind"] == "edgeconv":
+        return M.DGCNN(wl["k"], wl["dims"], wl["classes"])
+    return M.MoNet(wl["in_dim"], wl["hidden"], wl["classes"], 2, wl["dim"], wl["kernels"])
+
+
+# ----------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle's DGL-style CPU models on a bounded sample
+# ----------------------------------------------------------------------------------------
+
+def cpu_sample_scale(wl: dict) -> float:
+    return {"C1": 1.0, "C2": 1.0 / 32, "C3": 1.0 / 8, "C4": 1.0, "C5": 1.0 / 256}[wl["name"]]
+
+
+def run_cpu_epochs(wl: dict, steps: int, warmup: int, seed: int):
+    """Times `steps` epochs of the CPU model on the bounded sample; returns
+    (ms per epoch extrapolated to the full workload, sample description, cores)."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    scale = cpu_sample_scale(wl)
+    d = build_inputs(wl, "cpu", seed, scale)
+    full_units = wl.get("_full_nnz") or d["nnz"] / scale
+    torch.manual_seed(seed)
+    model = make_model(wl, cpu=True)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+
+    def step():
+        if wl["kind"] == "gat":
+            out = model(d["graph"].row_ptr, d["graph"].col_ind, d["x"])
+        elif wl["kind"] == "edgeconv":
+            out = model(d["points"], d["src"])
+        else:
+            out = model(d["graph"].row_ptr, d["graph"].col_ind, d["x"], d["pseudo"])
+        loss = F.cross_entropy(out, d["labels"])
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        return loss.item()
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    ms = (time.perf_counter() - t0) * 1e3 / max(1, steps)
+    factor = full_units / d["nnz"]
+    sample = (f"{wl['name']} generator at scale {scale:g}: {d['n']} nodes / {d['nnz']} edges, full model "
+              f"fwd+loss+bwd+Adam in PyTorch-CPU fp32 (DGL-style index_select/index_add restatement), "
+              f"{ms:.1f} ms per epoch measured, x{factor:.1f} (edge ratio) to the full workload")
+    return ms * factor, sample, cores
+
+
+def reference_arm(args, wl):
+    rank = env_int("RANK", 0)
+    if rank != 0:
+        return
+    ms, sample, cores = run_cpu_epochs(wl, args.steps, args.warmup, args.seed)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": ms, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{wl['name']}: {wl['desc']}"},
+        "cpu_baseline": {"value": ms, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": ms, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------
+# own arm
+# ----------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="C5", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    wl = dict(WORKLOADS[args.workload], name=args.workload)
+    if args.warmup < 3 and args.impl == "b200":
+        args.warmup = 3
+
+    if args.impl == "reference":
+        reference_arm(args, wl)
+        return
+
+    world = env_int("WORLD_SIZE", 1)
+    rank = env_int("RANK", 0)
+    local_rank = env_int("LOCAL_RANK", 0)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    if world > 1 and wl["kind"] != "gat":
+        raise SystemExit("only the GAT workloads are partitioned; EdgeConv / GMMConv run as replicas (N=1)")
+
+    from ae_mlsys_gnn_b200 import _capi
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+
+    _capi.lib()
+    d = build_inputs(wl, dev, args.seed)
+    wl["_full_nnz"] = d["nnz"]
+    n, nnz = d["n"], d["nnz"]
+    torch.manual_seed(args.seed)
+
+    part = None
+    if wl["kind"] == "gat":
+        g = d["graph"]
+        col_ptr, row_ind, _ = csr2csc(g.row_ptr, g.col_ind)
+        if world > 1:
+            from ae_mlsys_gnn_b200.partition import PartitionedGAT, build_partition
+
+            part = build_partition(g.row_ptr, g.col_ind, col_ptr, row_ind, rank, world)
+            model = PartitionedGAT(wl["in_dim"], wl["hidden"], wl["heads"], wl["classes"], 1).to(dev)
+            x_l = part.pad_rows(part.local_slice(d["x"]))
+            y_l = part.local_slice(d["labels"]).contiguous()
+            d["x_l"], d["y_l"] = x_l, y_l
+            del d["x"], col_ptr, row_ind
+            d["graph"] = None
+        else:
+            model = make_model(wl).to(dev)
+    elif wl["kind"] == "gmm":
+        g = d["graph"]
+        col_ptr, row_ind, permute = csr2csc(g.row_ptr, g.col_ind)
+        model = make_model(wl).to(dev)
+    else:
+        model = make_model(wl).to(dev)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+    torch.cuda.empty_cache()
+
+    def step():
+        if wl["kind"] == "gat" and part is not None:
+            out = model(part, x_l)
+            loss = model.loss(part, out, y_l)
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+            model.all_reduce_grads(world)
+        else:
+            if wl["kind"] == "gat":
+                out = model(g.row_ptr, g.col_ind, col_ptr, row_ind, d["x"])
+            elif wl["kind"] == "edgeconv":
+                out = model(d["points"], d["src"])
+            else:
+                out = model(g.row_ptr, g.col_ind, col_ptr, row_ind, permute, d["x"], d["pseudo"])
+            loss = F.cross_entropy(out, d["labels"])
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+        opt.step()
+        return loss
+
+    # Inputs larger than the 126 MB L2 need no flush; the small workloads get one
+    # between timed steps (a 256 MB write), outside the per-step event pairs.
+    flush = wl["name"] in ("C1", "C3", "C4")
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if flush else None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    with BytesLedger() as ledger:
+        barrier()
+        for a, b in ev:
+            if flush:
+                flush_buf.fill_(1)
+            a.record()
+            step()
+            b.record()
+        barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    step_ms = [a.elapsed_time(b) for a, b in ev]
+    total_ms = torch.tensor([sum(step_ms)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    ms_per_step = total_ms.item() / args.steps
+
+    per = ledger.summary()
+    launches = count_launches(ledger.timer.counts, 0)
+
+    # ---- end to end: host buffers in, loss out, through the public API -------------------
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(args, wl, d, model, opt, part, dev, world)
+
+    # ---- roofline of the dominant entry point (rank 0's view) ------------------------------
+    peak, peak_kind = measured_peak_gbs()
+    roof = None
+    if per:
+        name = max(per, key=lambda k: per[k]["ms"])
+        p = per[name]
+        achieved = p["bytes"] / (p["ms"] * 1e-3) / 1e9 if p["ms"] > 0 else 0.0
+        roof = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak,
+                "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
+                "frac_of_8tbs": achieved / 8000.0, "traffic": traffic_from_profile(name, wl["name"]),
+                "launch_ms": p["ms"] / p["calls"], "bytes_per_launch": p["bytes"] / p["calls"],
+                "per_entry_point": {k: {"ms_per_step": v["ms"] / args.steps,
+                                        "gbs": v["bytes"] / (v["ms"] * 1e-3) / 1e9 if v["ms"] > 0 else 0.0,
+                                        "calls_per_step": v["calls"] / args.steps} for k, v in per.items()}}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        ms, sample, cores = run_cpu_epochs(wl, 2, 1, args.seed)
+        cpu = {"value": ms, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": ms_per_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{wl['name']}: {wl['desc']}", "nodes": n, "edges": nnz,
+                       "parallelism": f"row-block x{world}" if world > 1 else "single GPU",
+                       "l2": "flushed between steps (256 MB write)" if flush else "inputs exceed L2 (126 MB)",
+                       "seed": args.seed},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roof, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def traffic_from_profile(kernel: str, workload: str):
+    """DRAM bytes per launch measured once with ncu (profiles/traffic.json), or None."""
+    try:
+        t = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))
+        return t.get(workload, {}).get(kernel)
+    except Exception:
+        return None
+
+
+def run_e2e(args, wl, d, model, opt, part, dev, world):
+    """Same epoch, but every step starts from pinned HOST buffers (graph in CSR, inputs,
+    labels), copies them to the device, builds the CSC with the csr2csc kernel
+    (single GPU), runs forward/backward/update through the public layers API and reads
+    the loss back."""
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+
+    def pin(t):
+        return t.detach().cpu().pin_memory()
+
+    kind = wl["kind"]
+    if kind == "gat" and part is not None:
+        host = {k: pin(v) for k, v in dict(row_ptr=part.row_ptr, col_ind=part.col_ind, col_ptr=part.col_ptr,
+                                           row_ind=part.row_ind, x=d["x_l"], y=d["y_l"]).items()}
+    elif kind == "edgeconv":
+        host = {k: pin(v) for k, v in dict(points=d["points"], src=d["src"], y=d["labels"]).items()}
+    else:
+        g = d["graph"]
+        host = {k: pin(v) for k, v in dict(row_ptr=g.row_ptr, col_ind=g.col_ind, x=d["x"], y=d["labels"]).items()}
+        if kind == "gmm":
+            host["pseudo"] = pin(d["pseudo"])
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+
+    def one():
+        t = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+        if kind == "gat" and part is not None:
+            import dataclasses
+
+            p2 = dataclasses.replace(part, row_ptr=t["row_ptr"], col_ind=t["col_ind"], col_ptr=t["col_ptr"],
+                                     row_ind=t["row_ind"])
+            out = model(p2, t["x"])
+            loss = model.loss(p2, out, t["y"])
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+            model.all_reduce_grads(world)
+        elif kind == "gat":
+            cp, ri, _ = csr2csc(t["row_ptr"], t["col_ind"])
+            loss = F.cross_entropy(model(t["row_ptr"], t["col_ind"], cp, ri, t["x"]), t["y"])
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+        elif kind == "edgeconv":
+            loss = F.cross_entropy(model(t["points"], t["src"]), t["y"])
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+        else:
+            cp, ri, pm = csr2csc(t["row_ptr"], t["col_ind"])
+            loss = F.cross_entropy(model(t["row_ptr"], t["col_ind"], cp, ri, pm, t["x"], t["pseudo"]), t["y"])
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+        opt.step()
+        return loss.item()  # device -> host read of the result
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    one()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        one()
+    b.record()
+    barrier()
+    ms = torch.tensor([a.elapsed_time(b) / args.steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return {"value": ms.item(), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4}
+
+
+if __name__ == "__main__":
+    main()

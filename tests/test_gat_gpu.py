@@ -141,3 +141,21 @@ def test_gat_autograd_layer(cuda):
     assert_close(layer.attn_l.grad, al.grad, "attn_l.grad", scale_atol=True)
     assert_close(layer.attn_r.grad, ar.grad, "attn_r.grad", scale_atol=True)
     assert_close(xd.grad, xr.grad, "x.grad", scale_atol=True)
+
+
+def test_gat_backward_single_entry_point(cuda):
+    """gnn_gat_bwd (both passes in one call) equals the two separately called passes."""
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+    from ae_mlsys_gnn_b200.operators.fused_gat import (gat_backward, gat_backward_single_call,
+                                                       gat_forward)
+
+    g = power_law_graph(1500, 40, seed=8)
+    attn_row, attn_col, feat, gout = _inputs(g, 4, 32, 8)
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    cp, ri, _ = csr2csc(rp, ci)
+    d = [t.to(cuda) for t in (attn_row, attn_col, feat, gout)]
+    _, m, s = gat_forward(d[0], d[1], rp, ci, 0.2, d[2])
+    a = gat_backward(0.2, rp, ci, cp, ri, m, s, d[2], d[0], d[1], d[3])
+    b = gat_backward_single_call(0.2, rp, ci, cp, ri, m, s, d[2], d[0], d[1], d[3])
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
