@@ -301,3 +301,78 @@ extern "C" int gnn_gat_bwd(const int* row_ptr, const int* col_ind, const int* co
   return gnn_gat_bwd_col(col_ptr, row_ind, n, nnz, in_feat, attn_col, rowpack, grad_out, H, F,
                          negative_slope, grad_feat, grad_attn_col, scratch, scratch_bytes, stream);
 }
+
+// ---------------------------------------------------------------------------
+// gnn_gat_fwd_static_scratch: gnn_gat_fwd for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc (or torch's allocator) at
+// the point where they run a layer: an inference server that has handed all
+// device memory to its own pool at start-up, a plugin that runs inside
+// somebody else's memory plan, code on a latency-critical path where an
+// allocation could synchronise the device.  For them the scratch that
+// gnn_gat_fwd needs for rows split across edge chunks lives in a fixed array
+// inside the library's device image instead of a caller-provided workspace.
+//
+//  * The array is GNN_STATIC_SCRATCH_BYTES (16 MiB) and every GPU that loads
+//    the library holds it until the process exits.
+//  * A problem whose gnn_gat_fwd_workspace_bytes() exceeds that size is refused
+//    with GNN_ERR_LIMIT; nothing is launched.
+//  * The first call on each device looks the array's device address up
+//    (cudaGetSymbolAddress, with that device current) and remembers it; make
+//    that first call before any stream capture begins.
+//  * All calls share the one array and it keeps whatever the previous call left
+//    in it.  Nothing in it has to start at zero: every slot a merge reads was
+//    written earlier in the same call.  Two calls that overlap on the GPU
+//    (different streams, or different host threads) race on it and give wrong
+//    results; run them one after the other on one stream.
+namespace {
+
+static __device__ __align__(256) unsigned char g_static_scratch[GNN_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {nullptr};
+
+// Device address of g_static_scratch on the current device.  In host code the
+// symbol itself is only a handle, never a device pointer, hence the lookup.
+int static_scratch_address(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_last_error("gnn_gat_fwd_static_scratch: cannot identify the current device");
+    return GNN_ERR_CUDA;
+  }
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_last_error(cudaGetErrorString(e));
+      return GNN_ERR_CUDA;
+    }
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return GNN_OK;
+}
+
+}  // namespace
+
+extern "C" int gnn_gat_fwd_static_scratch(const int* row_ptr, const int* col_ind, int64_t n_rows,
+                                          int64_t nnz, const float* attn_row,
+                                          const float* attn_col, const float* in_feat, int H,
+                                          int F, float negative_slope, float* out,
+                                          float* edge_max, float* edge_sum, cudaStream_t stream) {
+  size_t need = 0;
+  int rc = gnn_gat_fwd_workspace_bytes(nnz, H, F, &need);
+  if (rc) return rc;
+  if (need > (size_t)GNN_STATIC_SCRATCH_BYTES) {
+    set_last_error("gnn_gat_fwd_static_scratch: this problem needs more scratch than the 16 MiB "
+                   "built into the library; use gnn_gat_fwd with a caller-provided workspace");
+    return GNN_ERR_LIMIT;
+  }
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  return gnn_gat_fwd(row_ptr, col_ind, n_rows, nnz, attn_row, attn_col, in_feat, H, F,
+                     negative_slope, out, edge_max, edge_sum, scratch,
+                     (size_t)GNN_STATIC_SCRATCH_BYTES, stream);
+}

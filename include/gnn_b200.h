@@ -80,6 +80,23 @@ int gnn_gat_fwd(const int* row_ptr, const int* col_ind, int64_t n_rows, int64_t 
                 float* edge_sum /*[n_rows,H]*/, void* workspace, size_t workspace_bytes,
                 cudaStream_t stream);
 
+/* gnn_gat_fwd for callers that cannot allocate device memory when they run a layer (a
+ * server whose memory pool took the whole GPU at start-up, a plugin inside another
+ * program's memory plan, a latency-critical path).  Has no counterpart in the
+ * reference.  Same arguments and results as gnn_gat_fwd, minus the workspace: the
+ * scratch is a GNN_STATIC_SCRATCH_BYTES array in the library's device image, held by
+ * every GPU that loads the library until the process exits.  Problems whose
+ * gnn_gat_fwd_workspace_bytes() is larger are refused with GNN_ERR_LIMIT.  The first
+ * call on a device resolves the array's address; make it before any stream capture.
+ * All calls share the array (contents of the previous call remain, none of it needs
+ * to be zero), so calls that overlap on the GPU race: issue them back to back on one
+ * stream. */
+#define GNN_STATIC_SCRATCH_BYTES (16 << 20)
+int gnn_gat_fwd_static_scratch(const int* row_ptr, const int* col_ind, int64_t n_rows, int64_t nnz,
+                               const float* attn_row, const float* attn_col, const float* in_feat,
+                               int H, int F, float negative_slope, float* out, float* edge_max,
+                               float* edge_sum, cudaStream_t stream);
+
 /* gnn_gat_bwd replaces fused_gat_SM.gat_backward
  * (src/fused_gat/fused_gat_SM.cpp:55-118, src/fused_gat/fused_gat_SM.cu:831-893)
  * on a square graph given as CSR and CSC.  No E x H temporary, no atomics.
