@@ -44,7 +44,7 @@ WORKLOADS = {
     "C4": dict(kind="gmm", desc="MoNet 2 GMMConv layers, 19,717 nodes / 88,648+19,717 edges, in 500, K=3, D=2, hidden 16, 3 classes",
                n=19717, edges=88648, in_dim=500, hidden=16, classes=3, kernels=3, dim=2),
     "C5": dict(kind="gat", desc="GAT 3-layer, R-MAT 2,449,029 nodes / ~124M directed edges, in 100, 4x128 -> 4x128 -> 1x47",
-               n=2449029, rmat_pairs=82_000_000, in_dim=100, hidden=[128, 128], heads=[4, 4], classes=47),
+               n=2449029, rmat_pairs=83_400_000, in_dim=100, hidden=[128, 128], heads=[4, 4], classes=47),
 }
 
 
