@@ -1,0 +1,143 @@
+"""Row-block partition and the partitioned GAT exchange logic, on CPU: two gloo ranks
+with the oracle standing in for the CUDA kernels (the kernels themselves are covered by
+the GPU tests; what is checked here is slicing, id remapping, the all-gathers, padding,
+the loss normalisation and the gradient all-reduce)."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import ops as ref
+from tests.util import assert_close, power_law_graph
+
+
+class OracleKernels:
+    """Same three methods as partition._CudaKernels, computed by the CPU oracle."""
+
+    @staticmethod
+    def forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full):
+        o, m, s = ref.gat_forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full)
+        return o.float(), m.float(), s.float()
+
+    @staticmethod
+    def backward_row(slope, row_ptr, col_ind, edge_max, edge_sum, h_full, attn_row, attn_col_full, grad_out):
+        rows, cols = ref.rows_of(row_ptr), col_ind.long()
+        e, alpha = ref.gat_alpha(attn_row, attn_col_full, row_ptr, col_ind, slope, edge_max, edge_sum)
+        g = (grad_out.double()[rows] * h_full.double()[cols]).sum(-1)
+        n, H = attn_row.shape
+        S = torch.zeros(n, H, dtype=torch.float64).index_add_(0, rows, alpha * g)
+        ge = alpha * (g - S[rows])
+        ge = torch.where(e < 0, ge * slope, ge)
+        gar = torch.zeros(n, H, dtype=torch.float64).index_add_(0, rows, ge)
+        pack = torch.stack([attn_row.double(), edge_max.double(), 1.0 / edge_sum.double(), S], 1)
+        return gar.float(), pack.float()
+
+    @staticmethod
+    def backward_col(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full):
+        cols, rows = ref.rows_of(col_ptr), row_ind.long()   # segments are the owned sources
+        rp = rowpack_full.double()
+        x = rp[rows, 0] + attn_col_local.double()[cols]
+        e = torch.where(x > 0, x, x * slope)
+        alpha = torch.exp(e - rp[rows, 1]) * rp[rows, 2]
+        G = gout_full.double()[rows]
+        n, H, F = h_local.shape
+        gh = torch.zeros(n, H, F, dtype=torch.float64).index_add_(0, cols, alpha[:, :, None] * G)
+        g = (G * h_local.double()[cols]).sum(-1)
+        ge = alpha * (g - rp[rows, 3])
+        ge = torch.where(e < 0, ge * slope, ge)
+        gac = torch.zeros(n, H, dtype=torch.float64).index_add_(0, cols, ge)
+        return gh.float(), gac.float()
+
+
+def test_edge_balanced_bounds():
+    from ae_mlsys_gnn_b200.partition import edge_balanced_bounds
+
+    g = power_law_graph(2000, 30, seed=1)
+    for world in (1, 2, 4, 8):
+        b = edge_balanced_bounds(g.row_ptr, world)
+        assert b[0] == 0 and b[-1] == g.n and len(b) == world + 1
+        assert all(b[i] <= b[i + 1] for i in range(world))
+        rp = g.row_ptr.long()
+        per = [int(rp[b[i + 1]] - rp[b[i]]) for i in range(world)]
+        assert max(per) <= g.nnz / world + int((rp[1:] - rp[:-1]).max())
+
+
+def test_partition_blocks_cover_graph():
+    from ae_mlsys_gnn_b200.partition import build_partition
+
+    g = power_law_graph(500, 12, seed=2)
+    cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)
+    world = 4
+    parts = [build_partition(g.row_ptr, g.col_ind, cp, ri, r, world) for r in range(world)]
+    max_n = parts[0].max_n
+    assert sum(p.n_local for p in parts) == g.n
+    assert sum(p.col_ind.numel() for p in parts) == g.nnz == sum(p.row_ind.numel() for p in parts)
+    # padded ids map back to the global ids
+    b = torch.tensor(parts[0].bounds)
+    glob = torch.cat([p.col_ind.long() for p in parts])
+    owner = glob // max_n
+    assert torch.equal(b[owner] + glob % max_n, g.col_ind.long())
+
+
+def _worker(rank, world, port, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ae_mlsys_gnn_b200.partition import PartitionedGAT, build_partition
+
+        torch.manual_seed(0)
+        g = power_law_graph(300, 10, seed=3)
+        cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)
+        x = torch.randn(g.n, 12, generator=torch.Generator().manual_seed(1))
+        y = torch.randint(0, 5, (g.n,), generator=torch.Generator().manual_seed(2))
+        part = build_partition(g.row_ptr, g.col_ind, cp, ri, rank, world)
+        model = PartitionedGAT(12, [8], [2], 5, 1, kernels=OracleKernels)
+        out = model(part, part.pad_rows(part.local_slice(x)))
+        loss = model.loss(part, out, part.local_slice(y))
+        loss.backward()
+        model.all_reduce_grads(world)
+        total = loss.detach().clone()
+        dist.all_reduce(total)
+        gathered = [torch.empty(part.max_n, out.shape[1]) for _ in range(world)]
+        dist.all_gather(gathered, out.detach())
+        if rank == 0:
+            full = torch.cat([gathered[r][: part.bounds[r + 1] - part.bounds[r]] for r in range(world)])
+            results["out"] = full
+            results["loss"] = total
+            results["grads"] = {k: p.grad.clone() for k, p in model.named_parameters()}
+            results["state"] = {k: v.clone() for k, v in model.state_dict().items()}
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_partitioned_gat_two_ranks_matches_single():
+    import socket
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
+
+    g = power_law_graph(300, 10, seed=3)
+    x = torch.randn(g.n, 12, generator=torch.Generator().manual_seed(1))
+    y = torch.randint(0, 5, (g.n,), generator=torch.Generator().manual_seed(2))
+    st = {k: v.double().requires_grad_(True) for k, v in results["state"].items()}
+    h = x.double()
+    h = ref.gat_layer_dgl(g.row_ptr, g.col_ind, h, st["gat_layers.0.W"], st["gat_layers.0.attn_l"],
+                          st["gat_layers.0.attn_r"], 0.2).flatten(1)
+    h = torch.nn.functional.elu(h)
+    out = ref.gat_layer_dgl(g.row_ptr, g.col_ind, h, st["gat_layers.1.W"], st["gat_layers.1.attn_l"],
+                            st["gat_layers.1.attn_r"], 0.2).mean(1)
+    loss = torch.nn.functional.cross_entropy(out, y)
+    loss.backward()
+    assert_close(results["out"], out, "partitioned logits")
+    assert_close(results["loss"], loss, "loss")
+    for k, gval in results["grads"].items():
+        assert_close(gval, st[k].grad, f"grad {k}", scale_atol=True)
