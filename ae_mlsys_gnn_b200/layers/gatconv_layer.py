@@ -4,7 +4,8 @@ from __future__ import annotations
 import torch
 from torch import nn
 
-from ..operators.fused_gat import fused_gat_fusescatter, fused_gat_op, fused_gat_stash_op
+from ..operators.fused_gat import (fused_gat_fusescatter, fused_gat_layer_op, fused_gat_op,
+                                   fused_gat_stash_op, fused_scores_supported)
 
 
 class _GATBase(nn.Module):
@@ -39,7 +40,17 @@ class _GATBase(nn.Module):
 
 
 class GATConv(_GATBase):
+    """``fuse_scores`` (default on) computes attn_row / attn_col and their gradients with
+    the one-pass score kernels inside the same autograd node as the fused op; off, the
+    layer is composed exactly like the reference's (framework ops + fused_gat_op)."""
+
+    fuse_scores = True
+
     def forward(self, row_ptr, col_ind, col_ptr, row_ind, feat, save_memory=True):
+        if self.fuse_scores and fused_scores_supported(self.num_heads, self.out_feats):
+            h = torch.matmul(feat, self.W).view(-1, self.num_heads, self.out_feats)
+            return fused_gat_layer_op(h, self.attn_l, self.attn_r, row_ptr, col_ind, col_ptr,
+                                      row_ind, self.negative_slope)
         h, attn_row, attn_col = self.project(feat)
         return fused_gat_op(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind,
                             self.negative_slope, h, save_memory)

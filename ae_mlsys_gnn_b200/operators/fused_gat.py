@@ -149,6 +149,80 @@ def gat_edge_alpha(attn_row, attn_col, row_ptr, col_ind, edge_max, edge_sum, neg
     return edge_relu, edge_alpha
 
 
+def gat_scores_forward(h, attn_l, attn_r):
+    """(attn_row, attn_col), each (N,H): the two score reductions of
+    layers/gatconv_layer.py:52-53 in one pass over ``h`` (N,H,F)."""
+    dev = h.device
+    capi.require(h, F32, "h", 3)
+    n, H, F = h.shape
+    al = capi.require(attn_l.reshape(H, F), F32, "attn_l", 2, dev)
+    ar = capi.require(attn_r.reshape(H, F), F32, "attn_r", 2, dev)
+    attn_row = torch.empty((n, H), dtype=F32, device=dev)
+    attn_col = torch.empty((n, H), dtype=F32, device=dev)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_scores_fwd", capi.ptr(h), capi.ptr(al), capi.ptr(ar), n, H, F,
+                  capi.ptr(attn_row), capi.ptr(attn_col), capi.stream_ptr(dev))
+    return attn_row, attn_col
+
+
+def gat_scores_backward(h, attn_l, attn_r, grad_attn_row, grad_attn_col, grad_feat):
+    """Adds the score gradients into ``grad_feat`` IN PLACE and returns
+    (grad_attn_l, grad_attn_r), each (H,F)."""
+    dev = h.device
+    n, H, F = h.shape
+    al, ar = attn_l.reshape(H, F), attn_r.reshape(H, F)
+    capi.require(grad_feat, F32, "grad_feat", 3, dev)
+    capi.require(grad_attn_row, F32, "grad_attn_row", 2, dev)
+    capi.require(grad_attn_col, F32, "grad_attn_col", 2, dev)
+    gl = torch.empty((H, F), dtype=F32, device=dev)
+    gr = torch.empty((H, F), dtype=F32, device=dev)
+    nbytes = capi.workspace_bytes("gnn_gat_scores_bwd_workspace_bytes", n, H, F)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_scores_bwd", capi.ptr(h), capi.ptr(al), capi.ptr(ar),
+                  capi.ptr(grad_attn_row), capi.ptr(grad_attn_col), n, H, F, capi.ptr(grad_feat),
+                  capi.ptr(gl), capi.ptr(gr), capi.ptr(ws), ws.numel(), capi.stream_ptr(dev))
+    return gl, gr
+
+
+def fused_scores_supported(H, F):
+    """Shapes the one-pass score kernels cover (same limit as the fused backward)."""
+    return H <= 8 and H * F <= (512 if F % 4 == 0 else 256)
+
+
+class FusedGATLayerFunction(torch.autograd.Function):
+    """Scores + fused_gat_op as one autograd node: h (N,H,F), attn_l / attn_r (1,H,F) ->
+    out (N,H,F).  Same mathematics as GATConv.forward after the projection
+    (layers/gatconv_layer.py:52-55), but the per-node scores and their gradients never
+    go through framework elementwise kernels, and grad_h is accumulated in place."""
+
+    @staticmethod
+    def forward(ctx, h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind, negative_slope):
+        h = h.contiguous()
+        attn_l, attn_r = attn_l.contiguous(), attn_r.contiguous()
+        attn_row, attn_col = gat_scores_forward(h, attn_l, attn_r)
+        out, edge_max, edge_sum = gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, h)
+        ctx.save_for_backward(row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, h, attn_row,
+                              attn_col, attn_l, attn_r)
+        ctx.negative_slope = negative_slope
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, h, attn_row, attn_col, attn_l,
+         attn_r) = ctx.saved_tensors
+        grad_feat, gar, gac = gat_backward(ctx.negative_slope, row_ptr, col_ind, col_ptr, row_ind,
+                                           edge_max, edge_sum, h, attn_row, attn_col,
+                                           grad_out.contiguous())
+        gl, gr = gat_scores_backward(h, attn_l, attn_r, gar, gac, grad_feat)
+        return grad_feat, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None
+
+
+def fused_gat_layer_op(h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind, negative_slope):
+    return FusedGATLayerFunction.apply(h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind,
+                                       negative_slope)
+
+
 class FusedGATFunction_SM(torch.autograd.Function):
     """Recompute flavour (operators/fused_gat.py:52-71): only edge_max / edge_sum (N x H)
     are kept; the backward recomputes the attention values."""

@@ -101,17 +101,28 @@ def build_partition(row_ptr, col_ind, col_ptr, row_ind, rank: int, world: int,
 
 def all_gather_rows(x: torch.Tensor, world: int, group=None, async_op: bool = False):
     """All-gather of equally sized row blocks: (max_n, ...) -> (world*max_n, ...)."""
-    out = x.new_empty((world * x.shape[0],) + tuple(x.shape[1:]))
     if world == 1:
-        out.copy_(x)
-        return (out, None) if async_op else out
+        return (x, None) if async_op else x
+    out = x.new_empty((world * x.shape[0],) + tuple(x.shape[1:]))
     work = dist.all_gather_into_tensor(out, x.contiguous(), group=group, async_op=async_op)
     return (out, work) if async_op else out
 
 
 class _CudaKernels:
     """The product kernels (C ABI).  Tests on CPU substitute an oracle-backed object
-    with the same three methods to exercise the exchange logic under gloo."""
+    with the same methods to exercise the exchange logic under gloo."""
+
+    @staticmethod
+    def scores_forward(h, attn_l, attn_r):
+        from .operators.fused_gat import gat_scores_forward
+
+        return gat_scores_forward(h, attn_l, attn_r)
+
+    @staticmethod
+    def scores_backward(h, attn_l, attn_r, grad_attn_row, grad_attn_col, grad_feat):
+        from .operators.fused_gat import gat_scores_backward
+
+        return gat_scores_backward(h, attn_l, attn_r, grad_attn_row, grad_attn_col, grad_feat)
 
     @staticmethod
     def forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full):
@@ -136,24 +147,31 @@ class _CudaKernels:
 
 
 class PartitionedGATFunction(torch.autograd.Function):
-    """fused_gat_op on a row-block partition.  Inputs and output have max_n rows."""
+    """Scores + fused GAT aggregation on a row-block partition, one autograd node.
+    ``h`` and the output have max_n rows (the rank's rows, then zero padding)."""
 
     @staticmethod
-    def forward(ctx, attn_row, attn_col, h, part: RowBlockPartition, slope, kernels, group):
+    def forward(ctx, h, attn_l, attn_r, part: RowBlockPartition, slope, kernels, group):
         n, P = part.n_local, part.world
-        attn_row, attn_col, h = attn_row.contiguous(), attn_col.contiguous(), h.contiguous()
-        h_full = all_gather_rows(h, P, group)
+        h, attn_l, attn_r = h.contiguous(), attn_l.contiguous(), attn_r.contiguous()
+        # start moving h while the scores are computed from the local copy
+        h_full, work = all_gather_rows(h, P, group, async_op=True)
+        attn_row, attn_col = kernels.scores_forward(h, attn_l, attn_r)
         ac_full = all_gather_rows(attn_col, P, group)
+        if work is not None:
+            work.wait()
         out_l, edge_max, edge_sum = kernels.forward(attn_row[:n], ac_full, part.row_ptr,
                                                     part.col_ind, slope, h_full)
         out = part.pad_rows(out_l) if n < part.max_n else out_l
-        ctx.save_for_backward(attn_row, attn_col, h, h_full, ac_full, edge_max, edge_sum)
+        ctx.save_for_backward(attn_row, attn_col, h, h_full, ac_full, edge_max, edge_sum, attn_l,
+                              attn_r)
         ctx.part, ctx.slope, ctx.kernels, ctx.group = part, slope, kernels, group
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        attn_row, attn_col, h, h_full, ac_full, edge_max, edge_sum = ctx.saved_tensors
+        (attn_row, attn_col, h, h_full, ac_full, edge_max, edge_sum, attn_l,
+         attn_r) = ctx.saved_tensors
         part, slope, kernels, group = ctx.part, ctx.slope, ctx.kernels, ctx.group
         n, P = part.n_local, part.world
         grad_out = grad_out.contiguous()
@@ -166,7 +184,8 @@ class PartitionedGATFunction(torch.autograd.Function):
             work.wait()
         gh_l, gac_l = kernels.backward_col(slope, part.col_ptr, part.row_ind, h[:n], attn_col[:n],
                                            rp_full, gout_full)
-        return part.pad_rows(gar_l), part.pad_rows(gac_l), part.pad_rows(gh_l), None, None, None, None
+        gl, gr = kernels.scores_backward(h[:n], attn_l, attn_r, gar_l, gac_l, gh_l)
+        return part.pad_rows(gh_l), gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None
 
 
 class PartitionedGATConv(_GATBase):
@@ -179,8 +198,8 @@ class PartitionedGATConv(_GATBase):
         self.group = group
 
     def forward(self, part: RowBlockPartition, feat):
-        h, attn_row, attn_col = self.project(feat)
-        return PartitionedGATFunction.apply(attn_row, attn_col, h, part, self.negative_slope,
+        h = torch.matmul(feat, self.W).view(-1, self.num_heads, self.out_feats)
+        return PartitionedGATFunction.apply(h, self.attn_l, self.attn_r, part, self.negative_slope,
                                             self.kernels, self.group)
 
 

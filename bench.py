@@ -135,6 +135,10 @@ def algorithmic_bytes(name: str, n: int, e: int, H: int, Fw: int, D: int = 0) ->
         return 4.0 * e * (1 + D + HF) + 4.0 * n * (1 + HF)
     if name == "gnn_mhsddmm":
         return 4.0 * e * (1 + HF + H) + 4.0 * n * (1 + HF)
+    if name == "gnn_gat_scores_fwd":
+        return 4.0 * n * (HF + 2 * H)
+    if name == "gnn_gat_scores_bwd":
+        return 4.0 * n * (3 * HF + 2 * H)
     return 0.0
 
 
@@ -182,6 +186,10 @@ class BytesLedger:
             return algorithmic_bytes(name, a[2], a[3], a[9], a[11], a[10])
         if name == "gnn_mhsddmm":
             return algorithmic_bytes(name, a[2], a[3], a[6], a[7])
+        if name == "gnn_gat_scores_fwd":
+            return algorithmic_bytes(name, a[3], 0, a[4], a[5])
+        if name == "gnn_gat_scores_bwd":
+            return algorithmic_bytes(name, a[5], 0, a[6], a[7])
         return 0.0
 
     def summary(self):

@@ -131,6 +131,24 @@ int gnn_gat_bwd_col(const int* col_ptr, const int* row_ind, int64_t n_cols, int6
                     float* grad_feat, float* grad_attn_col, void* workspace,
                     size_t workspace_bytes, cudaStream_t stream);
 
+/* Attention scores of a GAT layer in one pass over the projected features, and their
+ * backward fused with the accumulation into grad_feat.  Replaces the framework kernels
+ * behind layers/gatconv_layer.py:52-53 (attn_row = (attn_l*h).sum(-1), attn_col =
+ * (attn_r*h).sum(-1)) and autograd's backward of those lines:
+ *   fwd: attn_row[n,h] = <attn_l[h,:], feat[n,h,:]>, attn_col[n,h] = <attn_r[h,:], feat[n,h,:]>
+ *   bwd: grad_feat[n,h,:] += grad_attn_row[n,h]*attn_l[h,:] + grad_attn_col[n,h]*attn_r[h,:]  (in place)
+ *        grad_attn_l[h,:] = sum_n grad_attn_row[n,h]*feat[n,h,:], grad_attn_r likewise.
+ * Requires H <= 8 and H*F <= 512 (aligned) / 256. */
+int gnn_gat_scores_fwd(const float* feat /*[n,H,F]*/, const float* attn_l /*[H,F]*/,
+                       const float* attn_r /*[H,F]*/, int64_t n, int H, int F,
+                       float* attn_row /*[n,H]*/, float* attn_col /*[n,H]*/, cudaStream_t stream);
+int gnn_gat_scores_bwd_workspace_bytes(int64_t n, int H, int F, size_t* bytes);
+int gnn_gat_scores_bwd(const float* feat, const float* attn_l, const float* attn_r,
+                       const float* grad_attn_row, const float* grad_attn_col, int64_t n, int H,
+                       int F, float* grad_feat /*[n,H,F], updated in place*/,
+                       float* grad_attn_l /*[H,F]*/, float* grad_attn_r /*[H,F]*/, void* workspace,
+                       size_t workspace_bytes, cudaStream_t stream);
+
 /* Per-edge activated logits and normalised attention (E x H each), the tensors the
  * stash / fusescatter variants keep: fused_gat_stash.gat_forward and
  * fused_gat.gat_forward (src/fused_gat/fused_gat_stash.cu:193-288,

@@ -159,3 +159,55 @@ def test_gat_backward_single_entry_point(cuda):
     b = gat_backward_single_call(0.2, rp, ci, cp, ri, m, s, d[2], d[0], d[1], d[3])
     for x, y in zip(a, b):
         assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("H,F", [(4, 128), (4, 64), (8, 8), (1, 7), (1, 47), (3, 12), (2, 100)])
+def test_gat_scores_kernels(cuda, H, F):
+    """One-pass score kernels against the framework formulation of
+    layers/gatconv_layer.py:52-53 and its autograd backward (fp64)."""
+    from ae_mlsys_gnn_b200.operators.fused_gat import gat_scores_backward, gat_scores_forward
+
+    gen = torch.Generator().manual_seed(H * 100 + F)
+    n = 3001
+    h = torch.randn(n, H, F, generator=gen)
+    al, ar = torch.randn(1, H, F, generator=gen), torch.randn(1, H, F, generator=gen)
+    gar, gac = torch.randn(n, H, generator=gen), torch.randn(n, H, generator=gen)
+    gf = torch.randn(n, H, F, generator=gen)
+    row, col = gat_scores_forward(h.to(cuda), al.to(cuda), ar.to(cuda))
+    hd = h.double().requires_grad_(True)
+    ald, ard = al.double().requires_grad_(True), ar.double().requires_grad_(True)
+    er, ec = (ald * hd).sum(-1), (ard * hd).sum(-1)
+    (er * gar.double()).sum().add((ec * gac.double()).sum()).backward()
+    assert_close(row, er, "attn_row", scale_atol=True)
+    assert_close(col, ec, "attn_col", scale_atol=True)
+    gfd = gf.to(cuda).clone()
+    gl, gr = gat_scores_backward(h.to(cuda), al.to(cuda), ar.to(cuda), gar.to(cuda), gac.to(cuda), gfd)
+    assert_close(gfd, gf.double() + hd.grad, "grad_feat (in place)", scale_atol=True)
+    assert_close(gl, ald.grad[0], "grad_attn_l", scale_atol=True)
+    assert_close(gr, ard.grad[0], "grad_attn_r", scale_atol=True)
+
+
+def test_gat_layer_unfused_scores_path(cuda):
+    """GATConv with fuse_scores off is composed like the reference layer (framework ops
+    around fused_gat_op) and must agree with the fused-scores path."""
+    from ae_mlsys_gnn_b200.layers import GATConv
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+
+    torch.manual_seed(3)
+    g = power_law_graph(600, 20, seed=9)
+    layer = GATConv(16, 8, 4).to(cuda)
+    x = torch.randn(g.n, 16, device=cuda)
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    cp, ri, _ = csr2csc(rp, ci)
+    gout = torch.randn(g.n, 4, 8, device=cuda)
+    res = []
+    for fuse in (True, False):
+        layer.fuse_scores = fuse
+        layer.zero_grad()
+        xd = x.clone().requires_grad_(True)
+        out = layer(rp, ci, cp, ri, xd)
+        out.backward(gout)
+        res.append((out.detach(), xd.grad, layer.W.grad.clone(), layer.attn_l.grad.clone(),
+                    layer.attn_r.grad.clone()))
+    for name, a, b in zip(("out", "x.grad", "W.grad", "attn_l.grad", "attn_r.grad"), *res):
+        assert_close(a, b, name, scale_atol=True)

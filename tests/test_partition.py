@@ -17,6 +17,15 @@ class OracleKernels:
     """Same three methods as partition._CudaKernels, computed by the CPU oracle."""
 
     @staticmethod
+    def scores_forward(h, attn_l, attn_r):
+        return (attn_l * h).sum(-1), (attn_r * h).sum(-1)
+
+    @staticmethod
+    def scores_backward(h, attn_l, attn_r, gar, gac, grad_feat):
+        grad_feat += gar[:, :, None] * attn_l + gac[:, :, None] * attn_r
+        return (gar[:, :, None] * h).sum(0), (gac[:, :, None] * h).sum(0)
+
+    @staticmethod
     def forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full):
         o, m, s = ref.gat_forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full)
         return o.float(), m.float(), s.float()

@@ -1,0 +1,241 @@
+"""A/B against the reference's own CUDA operators (compiled unmodified into oracle/_ref by
+oracle/build_ref.py) on the same seeded inputs: reference vs CPU oracle vs B200 kernels.
+
+Shapes are restricted to those for which reading the reference kernels shows them to be
+race-free and in-bounds:
+  * fused_gat_SM forward, F > 64 (fused_forward_kernel): the warps of a block share one
+    32-entry staging buffer guarded only by __syncwarp (fused_gat_SM.cu:267-281), and the
+    gather is unguarded for fid >= F (:279)  ->  F % 32 == 0 and every degree <= 32;
+  * forward, F <= 64 (fused_forward_kernel_small_f_sm): the column-id buffer is shared by
+    the per-head warps (:470,480) -> one head, or every degree <= 32; F % 32 == 0 (:451);
+  * backward: mhspmm_backward_kernel_small_f (F <= 64), mhsddmm and fused_backward_kernel
+    keep per-warp state only -> any degree; F % 32 == 0.  The F > 64 backward shares its
+    staging buffer like the forward -> every out-degree <= 32;
+  * fuseGmm: shared-memory index kid*kernels+lane overlaps for K > 1 (gmmconv.cu:69,75) ->
+    K = 1; it reads pseudo up to 31 rows past a row's end (:64) -> pseudo is a view of a
+    buffer with 32 spare rows; F % 32 == 0;
+  * gaussian writes out of bounds unless E % 32 == 0 (gmmconv.cu:36,45) -> E % 32 == 0.
+GaussianBp, u_add_v backward and the EdgeConv backward are not compared: the reference
+kernels are wrong or racy there.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import build_ref
+from oracle import ops as ref
+from tests.util import assert_close, graph_from_degrees, power_law_graph
+
+pytestmark = pytest.mark.gpu
+
+
+def _mod(name):
+    if not build_ref.available(name):
+        pytest.skip(f"oracle/_ref/{name} not built (python -m oracle.build_ref)")
+    return build_ref.load_module(name)
+
+
+def _bounded_graph(n, max_deg, seed):
+    """Square graph with in- and out-degree <= max_deg: every node points to the next
+    `d` nodes (cyclically), d drawn per node."""
+    rng = np.random.default_rng(seed)
+    d = max_deg // 2
+    rows = []
+    for r in range(n):
+        k = int(rng.integers(1, d + 1))
+        rows.append(np.sort((r + np.arange(k) * 1) % n))
+    row_ptr = np.zeros(n + 1, dtype=np.int64)
+    row_ptr[1:] = np.cumsum([len(c) for c in rows])
+    from ae_mlsys_gnn_b200.graphs import Graph
+
+    return Graph(n, torch.from_numpy(row_ptr.astype(np.int32)),
+                 torch.from_numpy(np.concatenate(rows).astype(np.int32)))
+
+
+def _gat_inputs(g, H, F, seed):
+    gen = torch.Generator().manual_seed(seed)
+    return (torch.randn(g.n, H, generator=gen), torch.randn(g.n, H, generator=gen),
+            torch.randn(g.n, H, F, generator=gen), torch.randn(g.n, H, F, generator=gen))
+
+
+GAT_CASES = [("powerlaw", 1, 64), ("powerlaw", 1, 32), ("bounded", 4, 64), ("bounded", 4, 128),
+             ("bounded", 8, 32)]
+
+
+@pytest.mark.parametrize("kind,H,F", GAT_CASES)
+def test_gat_forward_three_way(cuda, kind, H, F):
+    from ae_mlsys_gnn_b200.operators.fused_gat import gat_forward
+
+    m = _mod("fused_gat_SM")
+    g = power_law_graph(1500, 40, seed=1) if kind == "powerlaw" else _bounded_graph(1500, 32, 1)
+    ar, ac, x, _ = _gat_inputs(g, H, F, 2)
+    dv = [t.to(cuda) for t in (ar, ac, g.row_ptr, g.col_ind, x)]
+    r_out, r_max, r_sum = m.gat_forward(dv[0], dv[1], dv[2], dv[3], 0.2, dv[4])
+    o_out, o_max, o_sum = ref.gat_forward(ar, ac, g.row_ptr, g.col_ind, 0.2, x)
+    b_out, b_max, b_sum = gat_forward(dv[0], dv[1], dv[2], dv[3], 0.2, dv[4])
+    torch.cuda.synchronize()
+    assert_close(r_out, o_out, "reference vs oracle: out")
+    assert_close(r_sum, o_sum, "reference vs oracle: edge_sum")
+    assert_close(r_max, o_max, "reference vs oracle: edge_max", rtol=1e-6, atol=1e-6)
+    assert_close(b_out, r_out, "B200 vs reference: out")
+    assert_close(b_sum, r_sum, "B200 vs reference: edge_sum")
+    assert torch.equal(b_max, r_max), "edge_max is a max of identical fp32 values"
+
+
+@pytest.mark.parametrize("kind,H,F", [("powerlaw", 4, 64), ("powerlaw", 1, 32), ("powerlaw", 8, 32),
+                                      ("bounded", 4, 128)])
+def test_gat_backward_three_way(cuda, kind, H, F):
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+    from ae_mlsys_gnn_b200.operators.fused_gat import gat_backward, gat_forward
+
+    m = _mod("fused_gat_SM")
+    g = power_law_graph(1200, 30, seed=3) if kind == "powerlaw" else _bounded_graph(1200, 32, 3)
+    ar, ac, x, go = _gat_inputs(g, H, F, 4)
+    dv = [t.to(cuda) for t in (ar, ac, g.row_ptr, g.col_ind, x, go)]
+    cp, ri, _ = csr2csc(dv[2], dv[3])
+    _, e_max, e_sum = gat_forward(dv[0], dv[1], dv[2], dv[3], 0.2, dv[4])
+    r = m.gat_backward(0.2, dv[2], dv[3], cp, ri, e_max, e_sum, dv[4], dv[0], dv[1], dv[5])
+    b = gat_backward(0.2, dv[2], dv[3], cp, ri, e_max, e_sum, dv[4], dv[0], dv[1], dv[5])
+    _, om, os_ = ref.gat_forward(ar, ac, g.row_ptr, g.col_ind, 0.2, x)
+    o = ref.gat_backward(0.2, g.row_ptr, g.col_ind, om, os_, x, ar, ac, go)
+    torch.cuda.synchronize()
+    for name, rr, bb, oo in zip(("grad_feat", "grad_attn_row", "grad_attn_col"), r, b, o):
+        assert_close(rr, oo, f"reference vs oracle: {name}", scale_atol=True)
+        assert_close(bb, rr, f"B200 vs reference: {name}", scale_atol=True)
+
+
+@pytest.mark.parametrize("n,k,F", [(512, 20, 64), (300, 40, 128), (257, 20, 3), (100, 33, 40), (64, 20, 256)])
+@pytest.mark.parametrize("ties", [False, True])
+def test_edgeconv_forward_three_way(cuda, n, k, F, ties):
+    from ae_mlsys_gnn_b200.operators.fused_edgeconv import edgeconv_forward
+
+    m = _mod("fused_edgeconv")
+    gen = torch.Generator().manual_seed(n + k)
+    src = torch.randint(0, n, (n * k,), generator=gen, dtype=torch.int32)
+    if ties:
+        hs, hd = torch.randint(0, 3, (n, F), generator=gen).float(), torch.randint(0, 2, (n, F), generator=gen).float()
+    else:
+        hs, hd = torch.randn(n, F, generator=gen), torch.randn(n, F, generator=gen)
+    r_out, r_idx = m.edgeconv_forward(k, src.to(cuda), hs.to(cuda), hd.to(cuda))
+    b_out, b_idx = edgeconv_forward(k, src.to(cuda), hs.to(cuda), hd.to(cuda))
+    o_out, o_idx = ref.edgeconv_forward(k, src, hs, hd)
+    torch.cuda.synchronize()
+    assert torch.equal(r_out.cpu(), o_out) and torch.equal(r_idx.cpu().to(torch.int32), o_idx), \
+        "oracle must reproduce the reference bit for bit"
+    assert torch.equal(b_out, r_out) and torch.equal(b_idx, r_idx.to(torch.int32)), \
+        "B200 kernel must reproduce the reference bit for bit"
+
+
+def test_csr2csc_against_cusparse_path(cuda):
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+
+    m = _mod("csrtocsc")
+    g = power_law_graph(20000, 25, seed=6)
+    assert g.nnz < (1 << 24)  # the reference carries the permutation as float32
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    vals = torch.arange(g.nnz, dtype=torch.float32, device=cuda)
+    r_cp, r_ri, r_val = m.csr2csc(rp, ci, vals)
+    b_cp, b_ri, b_pm = csr2csc(rp, ci)
+    o_cp, o_ri, o_pm = ref.csr2csc_scipy(g.row_ptr, g.col_ind)
+    torch.cuda.synchronize()
+    assert torch.equal(r_cp.cpu(), o_cp) and torch.equal(r_ri.cpu(), o_ri)
+    assert torch.equal(r_val.cpu().to(torch.int32), o_pm)
+    assert torch.equal(b_cp, r_cp) and torch.equal(b_ri, r_ri) and torch.equal(b_pm, r_val.to(torch.int32))
+
+
+def test_gmm_forward_three_way(cuda):
+    from ae_mlsys_gnn_b200.operators.fused_gmmconv import gmmconv
+
+    m = _mod("gmmconv")
+    g = power_law_graph(800, 20, seed=7)
+    gen = torch.Generator().manual_seed(7)
+    K, D, F = 1, 2, 32
+    feat = torch.randn(g.n, K, F, generator=gen)
+    buf = torch.rand(g.nnz + 32, D, generator=gen).to(cuda)
+    pseudo = buf[: g.nnz]
+    mu, sg = torch.randn(K, D, generator=gen) * 0.3, torch.rand(K, D, generator=gen) + 0.5
+    dv = [t.to(cuda) for t in (g.row_ptr, g.col_ind, feat, mu, sg)]
+    r = m.gmmconv(dv[0], dv[1], dv[2], pseudo, dv[3], dv[4])
+    b = gmmconv(dv[0], dv[1], dv[2], pseudo, dv[3], dv[4])
+    o = ref.gmm_forward(g.row_ptr, g.col_ind, feat, pseudo.cpu(), mu, sg)
+    torch.cuda.synchronize()
+    assert_close(r, o, "reference vs oracle: gmmconv")
+    assert_close(b, r, "B200 vs reference: gmmconv")
+
+
+def test_gaussian_three_way(cuda):
+    from ae_mlsys_gnn_b200.operators.fused_gmmconv import gaussian
+
+    m = _mod("gmmconv")
+    gen = torch.Generator().manual_seed(8)
+    E, K, D = 2048, 3, 2
+    p, mu, sg = torch.rand(E, D, generator=gen), torch.randn(K, D, generator=gen), torch.rand(K, D, generator=gen) + 0.2
+    r = m.Gaussian(p.to(cuda), mu.to(cuda), sg.to(cuda))
+    b = gaussian(p.to(cuda), mu.to(cuda), sg.to(cuda))
+    torch.cuda.synchronize()
+    assert_close(r, ref.gaussian(p, mu, sg), "reference vs oracle: gaussian")
+    assert_close(b, r, "B200 vs reference: gaussian")
+
+
+@pytest.mark.parametrize("H", [1, 4, 3])
+def test_edge_softmax_three_way(cuda, H):
+    from ae_mlsys_gnn_b200.operators.edge_softmax import edge_softmax_backward, edge_softmax_forward
+
+    m = _mod("edge_softmax")
+    g = power_law_graph(900, 25, seed=9)
+    gen = torch.Generator().manual_seed(9)
+    h, go = torch.randn(g.nnz, H, generator=gen) * 2, torch.randn(g.nnz, H, generator=gen)
+    rp = g.row_ptr.to(cuda)
+    r = m.edge_softmax(rp, h.to(cuda))
+    b = edge_softmax_forward(rp, h.to(cuda))
+    hr = h.double().requires_grad_(True)
+    o = ref.edge_softmax(g.row_ptr, hr)
+    o.backward(go.double())
+    rg = m.edge_softmax_backward(rp, r, go.to(cuda))
+    bg = edge_softmax_backward(rp, b, go.to(cuda))
+    torch.cuda.synchronize()
+    assert_close(r, o, "reference vs oracle: edge_softmax")
+    assert_close(b, r, "B200 vs reference: edge_softmax")
+    assert_close(rg, hr.grad, "reference vs oracle: edge_softmax grad", scale_atol=True)
+    assert_close(bg, rg, "B200 vs reference: edge_softmax grad", scale_atol=True)
+
+
+@pytest.mark.parametrize("H,F", [(4, 16), (1, 64), (2, 100)])
+def test_mhspmm_mhsddmm_mhtranspose_three_way(cuda, H, F):
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+    from ae_mlsys_gnn_b200.operators.mhspmm import mhsddmm_forward, mhspmm_forward, mhtranspose_forward
+
+    sp, sd, tr = _mod("mhspmm"), _mod("mhsddmm"), _mod("mhtranspose")
+    g = power_law_graph(700, 18, seed=10)
+    gen = torch.Generator().manual_seed(10)
+    feat, att = torch.randn(g.n, H, F, generator=gen), torch.randn(g.nnz, H, generator=gen)
+    other = torch.randn(g.n, H, F, generator=gen)
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    _, _, pm = csr2csc(rp, ci)
+    r1 = sp.mhspmm(rp, ci, att.to(cuda), feat.to(cuda))
+    b1 = mhspmm_forward(rp, ci, att.to(cuda), feat.to(cuda))
+    r2 = sd.mhsddmm(rp, ci, other.to(cuda), feat.to(cuda))
+    b2 = mhsddmm_forward(rp, ci, other.to(cuda), feat.to(cuda))
+    r3 = tr.mhtranspose(pm, att.to(cuda))
+    b3 = mhtranspose_forward(pm, att.to(cuda))
+    torch.cuda.synchronize()
+    assert_close(r1, ref.mhspmm(g.row_ptr, g.col_ind, att, feat), "reference vs oracle: mhspmm", scale_atol=True)
+    assert_close(b1, r1, "B200 vs reference: mhspmm", scale_atol=True)
+    assert_close(r2, ref.mhsddmm(g.row_ptr, g.col_ind, other, feat), "reference vs oracle: mhsddmm", scale_atol=True)
+    assert_close(b2, r2, "B200 vs reference: mhsddmm", scale_atol=True)
+    assert torch.equal(r3, b3)
+
+
+def test_u_add_v_forward_three_way(cuda):
+    from ae_mlsys_gnn_b200.operators.u_add_v import u_add_v_forward
+
+    m = _mod("u_add_v")
+    g = power_law_graph(600, 15, seed=11)
+    gen = torch.Generator().manual_seed(11)
+    rv, cv = torch.randn(g.n, 4, generator=gen), torch.randn(g.n, 4, generator=gen)
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    r = m.u_add_v_forward(rp, ci, rv.to(cuda), cv.to(cuda))
+    b = u_add_v_forward(rp, ci, rv.to(cuda), cv.to(cuda))
+    torch.cuda.synchronize()
+    assert torch.equal(r, b)
+    assert_close(r, ref.u_add_v(g.row_ptr, g.col_ind, rv, cv), "reference vs oracle: u_add_v")
