@@ -3,6 +3,7 @@ from __future__ import annotations
 
 from torch import nn
 
+from ..operators import dense
 from ..operators.fused_edgeconv import fused_edgeconv_op
 
 
@@ -23,6 +24,6 @@ class EdgeConv(nn.Module):
         self._allow_zero_in_degree = set_value
 
     def forward(self, k, src_ind, feat):
-        h_theta = self.theta(feat)
-        h_phi = self.phi(feat)
+        h_theta = dense.linear(feat, self.theta.weight)
+        h_phi = dense.linear(feat, self.phi.weight)
         return fused_edgeconv_op(k, src_ind, h_theta, h_phi - h_theta)

@@ -4,6 +4,7 @@ from __future__ import annotations
 import torch
 from torch import nn
 
+from ..operators import dense
 from ..operators.fused_gat import (fused_gat_fusescatter, fused_gat_layer_op, fused_gat_op,
                                    fused_gat_stash_op, fused_scores_supported)
 
@@ -33,7 +34,7 @@ class _GATBase(nn.Module):
     def project(self, feat):
         """h = feat @ W viewed (N,H,F); attn_row multiplies the destination (CSR row),
         attn_col the source (layers/gatconv_layer.py:50-53)."""
-        h = torch.matmul(feat, self.W).view(-1, self.num_heads, self.out_feats)
+        h = dense.project(feat, self.W).view(-1, self.num_heads, self.out_feats)
         attn_row = (self.attn_l * h).sum(dim=-1)
         attn_col = (self.attn_r * h).sum(dim=-1)
         return h, attn_row, attn_col
@@ -48,7 +49,7 @@ class GATConv(_GATBase):
 
     def forward(self, row_ptr, col_ind, col_ptr, row_ind, feat, save_memory=True):
         if self.fuse_scores and fused_scores_supported(self.num_heads, self.out_feats):
-            h = torch.matmul(feat, self.W).view(-1, self.num_heads, self.out_feats)
+            h = dense.project(feat, self.W).view(-1, self.num_heads, self.out_feats)
             return fused_gat_layer_op(h, self.attn_l, self.attn_r, row_ptr, col_ind, col_ptr,
                                       row_ind, self.negative_slope)
         h, attn_row, attn_col = self.project(feat)

@@ -1,4 +1,5 @@
 """Mirror of the reference's ``operators`` package."""
+from . import dense
 from .csr2csc import csr2csc, sparsetrans
 from .edge_softmax import csr_edge_softmax
 from .fused_edgeconv import fused_edgeconv_op

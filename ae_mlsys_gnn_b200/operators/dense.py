@@ -1,0 +1,106 @@
+"""Dense node-feature projection on the tensor cores (no counterpart module in the
+reference, which calls torch.matmul / nn.Linear: layers/gatconv_layer.py:50,
+layers/edgeconv_layer.py:37-38, layers/gmmconv_layer.py:68).
+
+``matmul_tf32x3(x, w)`` computes ``x @ w`` with the error-compensated 3xTF32 tcgen05
+kernel (fp32-level accuracy); its backward uses the same kernel for grad_x and the
+framework GEMM for the small grad_w.  ``project`` picks it whenever the shape is
+supported and falls back to ``torch.matmul`` (cuBLAS fp32) otherwise.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _capi as capi
+
+F32 = torch.float32
+enabled = True  # set False to force the cuBLAS fp32 path
+
+_status: dict[int, torch.Tensor] = {}
+
+
+def _status_word(dev: torch.device) -> torch.Tensor:
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status[idx] = t
+    return t
+
+
+def check_status(dev=None) -> None:
+    """Synchronises and raises if any GEMM launched so far reported an expired wait."""
+    for idx, t in _status.items():
+        if dev is not None and torch.device(dev).index not in (None, idx):
+            continue
+        if int(t.item()) != 0:
+            t.zero_()
+            raise capi.GnnError("gnn_gemm_tf32x3: a barrier wait expired inside the kernel")
+
+
+def supported(m: int, n: int, k: int, a: torch.Tensor) -> bool:
+    return (enabled and a.is_cuda and a.dtype == F32 and a.is_contiguous()
+            and a.data_ptr() % 16 == 0 and bool(capi.lib().gnn_gemm_tf32x3_supported(m, n, k)))
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool) -> torch.Tensor:
+    """a (M,K) times b, where b is (K,N) or, with ``b_is_n_by_k``, (N,K)."""
+    dev = a.device
+    capi.require(a, F32, "a", 2)
+    capi.require(b, F32, "b", 2, dev)
+    M, K = a.shape
+    N = b.shape[0] if b_is_n_by_k else b.shape[1]
+    if (b.shape[1] if b_is_n_by_k else b.shape[0]) != K:
+        raise ValueError(f"inner dimensions differ: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
+    out = torch.empty((M, N), dtype=F32, device=dev)
+    nbytes = capi.workspace_bytes("gnn_gemm_tf32x3_workspace_bytes", M, N, K)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gemm_tf32x3", capi.ptr(a), capi.ptr(b), int(b_is_n_by_k), capi.ptr(out), M, N, K,
+                  capi.ptr(ws), ws.numel(), capi.ptr(_status_word(dev)), capi.stream_ptr(dev))
+    return out
+
+
+class _MatmulFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, w_is_out_by_in):
+        x = x.contiguous()
+        w = w.contiguous()
+        ctx.save_for_backward(x, w)
+        ctx.w_is_out_by_in = w_is_out_by_in
+        return gemm(x, w, w_is_out_by_in)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        g = g.contiguous()
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            # grad_x = g @ w^T (w given K x N) or g @ w (w given N x K)
+            n_out = g.shape[1]
+            if supported(g.shape[0], x.shape[1], n_out, g):
+                gx = gemm(g, w, not ctx.w_is_out_by_in)
+            else:
+                gx = g @ (w if ctx.w_is_out_by_in else w.t())
+        if ctx.needs_input_grad[1]:
+            gw = (g.t() @ x) if ctx.w_is_out_by_in else (x.t() @ g)
+        return gx, gw, None
+
+
+def matmul_tf32x3(x, w):
+    """x (M,K) @ w (K,N)."""
+    return _MatmulFunction.apply(x, w, False)
+
+
+def project(x, w):
+    """x @ w, on the tensor cores when the shape allows (K % 4 == 0, contiguous CUDA fp32)."""
+    if x.dim() == 2 and supported(x.shape[0], w.shape[1], w.shape[0], x.contiguous()):
+        return matmul_tf32x3(x, w)
+    return torch.matmul(x, w)
+
+
+def linear(x, weight):
+    """nn.Linear without bias: x (M,K) @ weight(N,K)^T."""
+    if x.dim() == 2 and supported(x.shape[0], weight.shape[0], weight.shape[1], x.contiguous()):
+        return _MatmulFunction.apply(x, weight, True)
+    return torch.nn.functional.linear(x, weight)

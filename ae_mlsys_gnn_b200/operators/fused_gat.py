@@ -15,12 +15,22 @@ from .. import _capi as capi
 I32, F32 = torch.int32, torch.float32
 
 
+def _rows(n_rows, pad_to, tail_shape, dev):
+    """Uninitialised (rows, *tail_shape) fp32 tensor with rows = max(n_rows, pad_to); rows
+    past n_rows (padding of a partitioned tensor) are zeroed, the kernels fill the rest."""
+    rows = n_rows if pad_to is None else max(n_rows, int(pad_to))
+    t = torch.empty((rows,) + tuple(tail_shape), dtype=F32, device=dev)
+    if rows > n_rows:
+        t[n_rows:].zero_()
+    return t
+
+
 def _check_graph(row_ptr, col_ind, dev, what="row_ptr/col_ind"):
     capi.require(row_ptr, I32, f"{what}[0]", 1, dev)
     capi.require(col_ind, I32, f"{what}[1]", 1, dev)
 
 
-def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat):
+def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, pad_to=None):
     """(out, edge_max, edge_sum) — fused_gat_SM.gat_forward
     (src/fused_gat/fused_gat_SM.cu:536-558).  ``attn_row`` and the outputs have one
     row per CSR row; ``attn_col`` / ``in_feat`` are indexed by ``col_ind``."""
@@ -36,7 +46,7 @@ def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat):
     if attn_col.shape != (in_feat.shape[0], H):
         raise ValueError("attn_col must have one row per in_feat row and H columns")
     nnz = col_ind.numel()
-    out = torch.empty((n_rows, H, F), dtype=F32, device=dev)
+    out = _rows(n_rows, pad_to, (H, F), dev)
     edge_max = torch.empty((n_rows, H), dtype=F32, device=dev)
     edge_sum = torch.empty((n_rows, H), dtype=F32, device=dev)
     nbytes = capi.workspace_bytes("gnn_gat_fwd_workspace_bytes", nnz, H, F)
@@ -94,7 +104,7 @@ def gat_backward_single_call(negative_slope, row_ptr, col_ind, col_ptr, row_ind,
 
 
 def gat_backward_row(negative_slope, row_ptr, col_ind, edge_max, edge_sum, in_feat, attn_row,
-                     attn_col, grad_out):
+                     attn_col, grad_out, pad_to=None):
     """Row pass of the backward on a CSR row block: (grad_attn_row, rowpack)."""
     dev = in_feat.device
     n_rows = row_ptr.numel() - 1
@@ -102,7 +112,7 @@ def gat_backward_row(negative_slope, row_ptr, col_ind, edge_max, edge_sum, in_fe
     nnz = col_ind.numel()
     capi.require(grad_out, F32, "grad_out", 3, dev)
     grad_attn_row = torch.empty((n_rows, H), dtype=F32, device=dev)
-    rowpack = torch.empty((n_rows, 4, H), dtype=F32, device=dev)
+    rowpack = _rows(n_rows, pad_to, (4, H), dev)
     nbytes = capi.workspace_bytes("gnn_gat_bwd_row_workspace_bytes", nnz, H, F)
     ws = capi.workspace(dev, nbytes)
     with torch.cuda.device(dev):
@@ -114,7 +124,8 @@ def gat_backward_row(negative_slope, row_ptr, col_ind, edge_max, edge_sum, in_fe
     return grad_attn_row, rowpack
 
 
-def gat_backward_col(negative_slope, col_ptr, row_ind, in_feat, attn_col, rowpack, grad_out):
+def gat_backward_col(negative_slope, col_ptr, row_ind, in_feat, attn_col, rowpack, grad_out,
+                     pad_to=None):
     """Column pass of the backward on a CSC column block: (grad_feat, grad_attn_col).
     ``in_feat`` / ``attn_col`` have one row per CSC column; ``rowpack`` / ``grad_out``
     are indexed by ``row_ind``."""
@@ -122,7 +133,7 @@ def gat_backward_col(negative_slope, col_ptr, row_ind, in_feat, attn_col, rowpac
     n_cols = col_ptr.numel() - 1
     H, F = in_feat.shape[1], in_feat.shape[2]
     nnz = row_ind.numel()
-    grad_feat = torch.empty((n_cols, H, F), dtype=F32, device=dev)
+    grad_feat = _rows(n_cols, pad_to, (H, F), dev)
     grad_attn_col = torch.empty((n_cols, H), dtype=F32, device=dev)
     nbytes = capi.workspace_bytes("gnn_gat_bwd_col_workspace_bytes", nnz, H, F)
     ws = capi.workspace(dev, nbytes)

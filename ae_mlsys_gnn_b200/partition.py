@@ -28,6 +28,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from .layers.gatconv_layer import _GATBase
+from .operators import dense
 
 
 def edge_balanced_bounds(row_ptr: torch.Tensor, world: int) -> list[int]:
@@ -125,25 +126,26 @@ class _CudaKernels:
         return gat_scores_backward(h, attn_l, attn_r, grad_attn_row, grad_attn_col, grad_feat)
 
     @staticmethod
-    def forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full):
+    def forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full, pad_to=None):
         from .operators.fused_gat import gat_forward
 
-        return gat_forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full)
+        return gat_forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full, pad_to=pad_to)
 
     @staticmethod
     def backward_row(slope, row_ptr, col_ind, edge_max, edge_sum, h_full, attn_row, attn_col_full,
-                     grad_out):
+                     grad_out, pad_to=None):
         from .operators.fused_gat import gat_backward_row
 
         return gat_backward_row(slope, row_ptr, col_ind, edge_max, edge_sum, h_full, attn_row,
-                                attn_col_full, grad_out)
+                                attn_col_full, grad_out, pad_to=pad_to)
 
     @staticmethod
-    def backward_col(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full):
+    def backward_col(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full,
+                     pad_to=None):
         from .operators.fused_gat import gat_backward_col
 
         return gat_backward_col(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full,
-                                gout_full)
+                                gout_full, pad_to=pad_to)
 
 
 class PartitionedGATFunction(torch.autograd.Function):
@@ -160,9 +162,8 @@ class PartitionedGATFunction(torch.autograd.Function):
         ac_full = all_gather_rows(attn_col, P, group)
         if work is not None:
             work.wait()
-        out_l, edge_max, edge_sum = kernels.forward(attn_row[:n], ac_full, part.row_ptr,
-                                                    part.col_ind, slope, h_full)
-        out = part.pad_rows(out_l) if n < part.max_n else out_l
+        out, edge_max, edge_sum = kernels.forward(attn_row[:n], ac_full, part.row_ptr, part.col_ind,
+                                                  slope, h_full, pad_to=part.max_n)
         ctx.save_for_backward(attn_row, attn_col, h, h_full, ac_full, edge_max, edge_sum, attn_l,
                               attn_r)
         ctx.part, ctx.slope, ctx.kernels, ctx.group = part, slope, kernels, group
@@ -177,15 +178,16 @@ class PartitionedGATFunction(torch.autograd.Function):
         grad_out = grad_out.contiguous()
         # the gather of grad_out does not depend on the row pass: run them together
         gout_full, work = all_gather_rows(grad_out, P, group, async_op=True)
-        gar_l, rowpack_l = kernels.backward_row(slope, part.row_ptr, part.col_ind, edge_max, edge_sum,
-                                                h_full, attn_row[:n], ac_full, grad_out[:n])
-        rp_full = all_gather_rows(part.pad_rows(rowpack_l), P, group)
+        gar_l, rowpack = kernels.backward_row(slope, part.row_ptr, part.col_ind, edge_max, edge_sum,
+                                              h_full, attn_row[:n], ac_full, grad_out[:n],
+                                              pad_to=part.max_n)
+        rp_full = all_gather_rows(rowpack, P, group)
         if work is not None:
             work.wait()
-        gh_l, gac_l = kernels.backward_col(slope, part.col_ptr, part.row_ind, h[:n], attn_col[:n],
-                                           rp_full, gout_full)
-        gl, gr = kernels.scores_backward(h[:n], attn_l, attn_r, gar_l, gac_l, gh_l)
-        return part.pad_rows(gh_l), gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None
+        gh, gac_l = kernels.backward_col(slope, part.col_ptr, part.row_ind, h[:n], attn_col[:n],
+                                         rp_full, gout_full, pad_to=part.max_n)
+        gl, gr = kernels.scores_backward(h[:n], attn_l, attn_r, gar_l, gac_l, gh[:n])
+        return gh, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None
 
 
 class PartitionedGATConv(_GATBase):
@@ -198,7 +200,7 @@ class PartitionedGATConv(_GATBase):
         self.group = group
 
     def forward(self, part: RowBlockPartition, feat):
-        h = torch.matmul(feat, self.W).view(-1, self.num_heads, self.out_feats)
+        h = dense.project(feat, self.W).view(-1, self.num_heads, self.out_feats)
         return PartitionedGATFunction.apply(h, self.attn_l, self.attn_r, part, self.negative_slope,
                                             self.kernels, self.group)
 

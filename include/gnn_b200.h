@@ -198,6 +198,20 @@ int gnn_gaussian_bwd(const float* pseudo, const float* mu, const float* inv_sigm
                      float* grad_inv_sigma /*[K,D]*/, void* workspace, size_t workspace_bytes,
                      cudaStream_t stream);
 
+/* ---- dense projection on the tensor cores ---------------------------------------------------
+ * C[M,N] = A[M,K] * op(B) in fp32-level accuracy on tcgen05 (error-compensated 3xTF32,
+ * fp32 accumulation in tensor memory, TMA operand loads).  Replaces the cuBLAS SGEMM behind
+ * torch.matmul(feat, W) / nn.Linear in the layers (layers/gatconv_layer.py:50,
+ * layers/edgeconv_layer.py:37-38, layers/gmmconv_layer.py:68).  B is K x N row-major
+ * (b_is_n_by_k = 0) or N x K row-major (b_is_n_by_k = 1, the nn.Linear weight layout).
+ * Requires K % 4 == 0 and 16-byte aligned A.  `status` is a device int the caller zeroes;
+ * a CTA whose bounded barrier wait expires sets it to 1 (results are then invalid). */
+int gnn_gemm_tf32x3_supported(int64_t M, int64_t N, int64_t K);
+int gnn_gemm_tf32x3_workspace_bytes(int64_t M, int64_t N, int64_t K, size_t* bytes);
+int gnn_gemm_tf32x3(const float* A, const float* B, int b_is_n_by_k, float* C, int64_t M, int64_t N,
+                    int64_t K, void* workspace, size_t workspace_bytes, int* status,
+                    cudaStream_t stream);
+
 /* ---- unfused operators that share the API ------------------------------------------------
  * gnn_mhspmm: mhspmm.mhspmm (src/spmm/mhspmm.cu:4-66) and, with H = 1, the
  * single-head csr_spmm / csr_spmm_no_edge_value that operators/spmm.py:35-41

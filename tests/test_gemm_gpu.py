@@ -1,0 +1,60 @@
+"""tcgen05 3xTF32 projection GEMM against an fp64 product; the tolerance is the one of
+the fp32 operators (rel 1e-4, abs 1e-5 scaled by the largest output magnitude)."""
+import pytest
+import torch
+
+from tests.util import assert_close
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(128, 128, 32), (1000, 512, 100), (300, 47, 512), (4097, 512, 512), (130, 70, 36), (5, 3, 4),
+          (257, 256, 64), (2048, 64, 128), (999, 41, 256)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("n_by_k", [False, True])
+def test_gemm_tf32x3(cuda, M, N, K, n_by_k):
+    from ae_mlsys_gnn_b200.operators import dense
+
+    gen = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=gen)
+    b = torch.randn(N, K, generator=gen) if n_by_k else torch.randn(K, N, generator=gen)
+    out = dense.gemm(a.to(cuda), b.to(cuda), n_by_k)
+    dense.check_status()
+    exp = a.double() @ (b.double().t() if n_by_k else b.double())
+    assert_close(out, exp, f"gemm {M}x{N}x{K}", scale_atol=True)
+    # a single TF32 pass would be off by ~1e-3 relative: make sure the compensation is on
+    err = (out.cpu().double() - exp).abs().max().item() / exp.abs().max().item()
+    assert err < 1e-5, f"relative error {err:.2e} is not fp32-level"
+
+
+def test_gemm_large_magnitude_spread(cuda):
+    """Entries spanning many orders of magnitude: the hi/lo split must stay exact."""
+    from ae_mlsys_gnn_b200.operators import dense
+
+    gen = torch.Generator().manual_seed(5)
+    a = torch.randn(513, 128, generator=gen) * torch.logspace(-6, 6, 128)
+    b = torch.randn(128, 96, generator=gen)
+    out = dense.gemm(a.to(cuda), b.to(cuda), False)
+    dense.check_status()
+    assert_close(out, a.double() @ b.double(), "gemm spread", scale_atol=True)
+
+
+def test_matmul_autograd_and_fallback(cuda):
+    from ae_mlsys_gnn_b200.operators import dense
+
+    gen = torch.Generator().manual_seed(9)
+    for K in (64, 30):  # 30 is not a multiple of 4: falls back to the framework GEMM
+        x = torch.randn(700, K, generator=gen)
+        w = torch.randn(K, 48, generator=gen)
+        g = torch.randn(700, 48, generator=gen)
+        xd, wd = x.to(cuda).requires_grad_(True), w.to(cuda).requires_grad_(True)
+        dense.project(xd, wd).backward(g.to(cuda))
+        xr, wr = x.double().requires_grad_(True), w.double().requires_grad_(True)
+        (xr @ wr).backward(g.double())
+        assert_close(xd.grad, xr.grad, "grad_x", scale_atol=True)
+        assert_close(wd.grad, wr.grad, "grad_w", scale_atol=True)
+        lin_w = torch.randn(48, K, generator=gen)
+        out = dense.linear(x.to(cuda), lin_w.to(cuda))
+        assert_close(out, x.double() @ lin_w.double().t(), "linear", scale_atol=True)
+    dense.check_status()

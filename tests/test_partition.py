@@ -13,6 +13,14 @@ from oracle import ops as ref
 from tests.util import assert_close, power_law_graph
 
 
+def _pad(t, rows):
+    if rows is None or rows <= t.shape[0]:
+        return t
+    out = t.new_zeros((rows,) + tuple(t.shape[1:]))
+    out[: t.shape[0]] = t
+    return out
+
+
 class OracleKernels:
     """Same three methods as partition._CudaKernels, computed by the CPU oracle."""
 
@@ -26,12 +34,13 @@ class OracleKernels:
         return (gar[:, :, None] * h).sum(0), (gac[:, :, None] * h).sum(0)
 
     @staticmethod
-    def forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full):
+    def forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full, pad_to=None):
         o, m, s = ref.gat_forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full)
-        return o.float(), m.float(), s.float()
+        return _pad(o.float(), pad_to), m.float(), s.float()
 
     @staticmethod
-    def backward_row(slope, row_ptr, col_ind, edge_max, edge_sum, h_full, attn_row, attn_col_full, grad_out):
+    def backward_row(slope, row_ptr, col_ind, edge_max, edge_sum, h_full, attn_row, attn_col_full, grad_out,
+                     pad_to=None):
         rows, cols = ref.rows_of(row_ptr), col_ind.long()
         e, alpha = ref.gat_alpha(attn_row, attn_col_full, row_ptr, col_ind, slope, edge_max, edge_sum)
         g = (grad_out.double()[rows] * h_full.double()[cols]).sum(-1)
@@ -41,10 +50,10 @@ class OracleKernels:
         ge = torch.where(e < 0, ge * slope, ge)
         gar = torch.zeros(n, H, dtype=torch.float64).index_add_(0, rows, ge)
         pack = torch.stack([attn_row.double(), edge_max.double(), 1.0 / edge_sum.double(), S], 1)
-        return gar.float(), pack.float()
+        return gar.float(), _pad(pack.float(), pad_to)
 
     @staticmethod
-    def backward_col(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full):
+    def backward_col(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full, pad_to=None):
         cols, rows = ref.rows_of(col_ptr), row_ind.long()   # segments are the owned sources
         rp = rowpack_full.double()
         x = rp[rows, 0] + attn_col_local.double()[cols]
@@ -57,7 +66,7 @@ class OracleKernels:
         ge = alpha * (g - rp[rows, 3])
         ge = torch.where(e < 0, ge * slope, ge)
         gac = torch.zeros(n, H, dtype=torch.float64).index_add_(0, cols, ge)
-        return gh.float(), gac.float()
+        return _pad(gh.float(), pad_to), gac.float()
 
 
 def test_edge_balanced_bounds():
