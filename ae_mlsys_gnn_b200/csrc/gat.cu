@@ -123,7 +123,18 @@ template <int HP, int Q, bool VEC>
 void launch_row(const GatBwdRowParams& p, cudaStream_t stream) {
   if (p.g.num_chunks > 0) {
     const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
-    gat_bwd_row_kernel<HP, Q, VEC><<<blocks, kThreadsPerCta, 0, stream>>>(p);
+    bool done = false;
+    if constexpr (VEC) {
+      if (p.width == 128 * Q) {  // every slot fully used: heads are aligned with the tile slots
+        if constexpr (Q <= HP) {
+          if (p.F == 128) { gat_bwd_row_kernel<HP, Q, VEC, 1><<<blocks, kThreadsPerCta, 0, stream>>>(p); done = true; }
+        }
+        if constexpr (2 * Q <= HP) {
+          if (p.F == 64) { gat_bwd_row_kernel<HP, Q, VEC, 2><<<blocks, kThreadsPerCta, 0, stream>>>(p); done = true; }
+        }
+      }
+    }
+    if (!done) gat_bwd_row_kernel<HP, Q, VEC><<<blocks, kThreadsPerCta, 0, stream>>>(p);
   }
   const int nbound = p.g.num_chunks > 1 ? p.g.num_chunks - 1 : 0;
   const int bblocks = (nbound + kWarpsPerCta - 1) / kWarpsPerCta;
@@ -136,7 +147,18 @@ template <int HP, int Q, bool VEC>
 void launch_col(const GatBwdColParams& p, cudaStream_t stream) {
   if (p.g.num_chunks > 0) {
     const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
-    gat_bwd_col_kernel<HP, Q, VEC><<<blocks, kThreadsPerCta, 0, stream>>>(p);
+    bool done = false;
+    if constexpr (VEC) {
+      if (p.width == 128 * Q) {  // every slot fully used: heads are aligned with the tile slots
+        if constexpr (Q <= HP) {
+          if (p.F == 128) { gat_bwd_col_kernel<HP, Q, VEC, 1><<<blocks, kThreadsPerCta, 0, stream>>>(p); done = true; }
+        }
+        if constexpr (2 * Q <= HP) {
+          if (p.F == 64) { gat_bwd_col_kernel<HP, Q, VEC, 2><<<blocks, kThreadsPerCta, 0, stream>>>(p); done = true; }
+        }
+      }
+    }
+    if (!done) gat_bwd_col_kernel<HP, Q, VEC><<<blocks, kThreadsPerCta, 0, stream>>>(p);
   }
   const int nbound = p.g.num_chunks > 1 ? p.g.num_chunks - 1 : 0;
   const int bblocks = (nbound + kWarpsPerCta - 1) / kWarpsPerCta;

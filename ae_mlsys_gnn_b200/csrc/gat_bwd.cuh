@@ -39,9 +39,14 @@ struct GatBwdRowParams {
   float* scratch;         // 2 * num_chunks slots of 4*HP floats
 };
 
-template <int HP, int Q, bool VEC>
-__global__ void __launch_bounds__(kThreadsPerCta)
+// HPS (heads per slot): when F * HPS equals the 128 floats one tile slot spans (128-bit
+// accesses), slot q of a lane lies in head q*HPS + lane_head with lane_head = 4*lane/F
+// fixed per lane, so the per-head bookkeeping needs HPS selects and no runtime indexing
+// of register arrays.  HPS = 0 is the general mapping.
+template <int HP, int Q, bool VEC, int HPS = 0>
+__global__ void __launch_bounds__(kThreadsPerCta, 2)
 gat_bwd_row_kernel(GatBwdRowParams p) {
+  static_assert(HPS == 0 || Q * HPS <= HP, "slot-aligned heads need Q * HPS <= HP");
   constexpr int VW = VEC ? 4 : 1;
   constexpr int U0 = Unroll<Q, VEC>::U;
   constexpr int U = (U0 * HP > 32) ? 32 / HP : U0;
@@ -58,6 +63,7 @@ gat_bwd_row_kernel(GatBwdRowParams p) {
   float* gs = gs_all[wib];
   RowTile<Q, VEC> t;
   t.init(lane, p.width, p.F, p.H);
+  const int lane_head = HPS > 1 ? (lane * VW) / p.F : 0;
 
   for_each_piece(p.g, chunk_id, [&](int s, int a, int b, bool first, bool last) {
     float gq[Q][VW];
@@ -96,12 +102,15 @@ gat_bwd_row_kernel(GatBwdRowParams p) {
       __syncwarp();
       const int nb = min(32, b - base);
       const int nbr = (nb + U - 1) / U * U;
-#pragma unroll 1
-      for (int jj = 0; jj < nbr; jj += U) {
-        float v[U][Q][VW];
+      // Software pipeline: the rows of the next U edges are requested before the dot
+      // products of the current U edges are reduced, so the shuffle chain of one group
+      // overlaps the gather latency of the next.
+      auto load_rows = [&](float (&v)[U][Q][VW], int jj) {
 #pragma unroll
         for (int u = 0; u < U; ++u)
           t.load(p.feat + (size_t)cs[jj + u] * p.ld_feat, lane, v[u]);
+      };
+      auto process = [&](float (&v)[U][Q][VW], int jj) {
         float pv[V];
 #pragma unroll
         for (int i = 0; i < V; ++i) pv[i] = 0.f;
@@ -112,13 +121,30 @@ gat_bwd_row_kernel(GatBwdRowParams p) {
             float d = 0.f;
 #pragma unroll
             for (int i = 0; i < VW; ++i) d = fmaf(gq[q][i], v[u][q][i], d);
+            if constexpr (HPS > 0) {
 #pragma unroll
-            for (int h = 0; h < HP; ++h)
-              if (t.head[q] == h) pv[u * HP + h] += d;
+              for (int k = 0; k < HPS; ++k) pv[u * HP + q * HPS + k] = (lane_head == k) ? d : 0.f;
+            } else {
+#pragma unroll
+              for (int h = 0; h < HP; ++h)
+                if (t.head[q] == h) pv[u * HP + h] += d;
+            }
           }
         }
         warp_multi_sum<V>(pv, lane);
         if ((lane & (32 / V - 1)) == 0) gs[jj * HP + lane / (32 / V)] = pv[0];
+      };
+      float va[U][Q][VW], vb[U][Q][VW];
+      load_rows(va, 0);
+#pragma unroll 1
+      for (int jj = 0; jj < nbr; jj += 2 * U) {
+        const bool more = jj + U < nbr;
+        if (more) load_rows(vb, jj + U);
+        process(va, jj);
+        if (more) {
+          if (jj + 2 * U < nbr) load_rows(va, jj + 2 * U);
+          process(vb, jj + U);
+        }
       }
       __syncwarp();
       if (ok) {
@@ -221,9 +247,10 @@ struct GatBwdColParams {
   int aux_off;
 };
 
-template <int HP, int Q, bool VEC>
+template <int HP, int Q, bool VEC, int HPS = 0>
 __global__ void __launch_bounds__(kThreadsPerCta)
 gat_bwd_col_kernel(GatBwdColParams p) {
+  static_assert(HPS == 0 || Q * HPS <= HP, "slot-aligned heads need Q * HPS <= HP");
   constexpr int VW = VEC ? 4 : 1;
   constexpr int U0 = Unroll<Q, VEC>::U;
   constexpr int U = (U0 * HP > 32) ? 32 / HP : U0;
@@ -241,6 +268,7 @@ gat_bwd_col_kernel(GatBwdColParams p) {
   float* gs = gs_all[wib];
   RowTile<Q, VEC> t;
   t.init(lane, p.width, p.F, p.H);
+  const int lane_head = HPS > 1 ? (lane * VW) / p.F : 0;
 
   for_each_piece(p.g, chunk_id, [&](int s, int a, int b, bool first, bool last) {
     float fq[Q][VW];
@@ -291,16 +319,21 @@ gat_bwd_col_kernel(GatBwdColParams p) {
         for (int u = 0; u < U; ++u) {
 #pragma unroll
           for (int q = 0; q < Q; ++q) {
-            const float wq = ws[(jj + u) * HP + t.head[q]];
+            const float wq = ws[(jj + u) * HP + (HPS > 0 ? q * HPS + lane_head : t.head[q])];
             float d = 0.f;
 #pragma unroll
             for (int i = 0; i < VW; ++i) {
               acc[q][i] = fmaf(wq, v[u][q][i], acc[q][i]);
               d = fmaf(fq[q][i], v[u][q][i], d);
             }
+            if constexpr (HPS > 0) {
 #pragma unroll
-            for (int h = 0; h < HP; ++h)
-              if (t.head[q] == h) pv[u * HP + h] += d;
+              for (int k = 0; k < HPS; ++k) pv[u * HP + q * HPS + k] = (lane_head == k) ? d : 0.f;
+            } else {
+#pragma unroll
+              for (int h = 0; h < HP; ++h)
+                if (t.head[q] == h) pv[u * HP + h] += d;
+            }
           }
         }
         warp_multi_sum<V>(pv, lane);
