@@ -203,12 +203,14 @@ wgather_kernel(WGatherParams p, Policy<HP> pol) {
       __syncwarp();
       const int nb = min(32, b - base);
       const int nbr = (nb + U - 1) / U * U;
-#pragma unroll 1
-      for (int jj = 0; jj < nbr; jj += U) {
-        float v[U][Q][VW];
+      // Software pipeline: the next U rows are requested before the current U rows are
+      // accumulated, so a warp always has gathers in flight.
+      auto load_rows = [&](float (&v)[U][Q][VW], int jj) {
 #pragma unroll
         for (int u = 0; u < U; ++u)
           t.load(p.feat + (size_t)cs[jj + u] * p.ld_feat, lane, v[u]);
+      };
+      auto accumulate = [&](float (&v)[U][Q][VW], int jj) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
 #pragma unroll
@@ -217,6 +219,18 @@ wgather_kernel(WGatherParams p, Policy<HP> pol) {
 #pragma unroll
             for (int i = 0; i < VW; ++i) acc[q][i] = fmaf(wq, v[u][q][i], acc[q][i]);
           }
+        }
+      };
+      float va[U][Q][VW], vb[U][Q][VW];
+      load_rows(va, 0);
+#pragma unroll 1
+      for (int jj = 0; jj < nbr; jj += 2 * U) {
+        const bool more = jj + U < nbr;
+        if (more) load_rows(vb, jj + U);
+        accumulate(va, jj);
+        if (more) {
+          if (jj + 2 * U < nbr) load_rows(va, jj + 2 * U);
+          accumulate(vb, jj + U);
         }
       }
     }
