@@ -30,6 +30,10 @@ PROTOTYPES = {
     "gnn_gat_fwd_workspace_bytes": [_I64, _INT, _INT, _SZP],
     "gnn_gat_fwd": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _INT, _INT, _F32,
                     _PTR, _PTR, _PTR, _PTR, _SZ, _PTR],
+    "gnn_gat_fwd_part": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _INT, _INT, _F32,
+                         _PTR, _PTR, _PTR, _INT, _INT, _PTR, _SZ, _PTR],
+    "gnn_gat_bwd_col_part": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _PTR, _INT, _INT, _F32,
+                             _PTR, _PTR, _INT, _PTR, _SZ, _PTR],
     "gnn_gat_fwd_static_scratch": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _INT, _INT, _F32,
                                    _PTR, _PTR, _PTR, _PTR],
     "gnn_gat_bwd_workspace_bytes": [_I64, _I64, _INT, _INT, _SZP],
@@ -119,7 +123,8 @@ def check(rc: int, what: str) -> None:
 # memsets excluded); bench.py uses it to count its own launches.
 KERNELS_PER_CALL = {
     "gnn_csr2csc": None,  # depends on the number of radix passes, see launches_csr2csc
-    "gnn_gat_fwd": 2, "gnn_gat_fwd_static_scratch": 2, "gnn_gat_bwd": 4, "gnn_gat_bwd_row": 2, "gnn_gat_bwd_col": 2,
+    "gnn_gat_fwd": 2, "gnn_gat_fwd_part": 2, "gnn_gat_bwd_col_part": 2,
+    "gnn_gat_fwd_static_scratch": 2, "gnn_gat_bwd": 4, "gnn_gat_bwd_row": 2, "gnn_gat_bwd_col": 2,
     "gnn_gat_scores_fwd": 1, "gnn_gat_scores_bwd": 2, "gnn_gemm_tf32x3": 3,
     "gnn_gat_edge_alpha": 1, "gnn_edgeconv_fwd": 1, "gnn_edgeconv_bwd": 1, "gnn_gmm_fwd": 2,
     "gnn_gaussian_fwd": 1, "gnn_gaussian_bwd": 2, "gnn_mhspmm": 2, "gnn_mhsddmm": 1,

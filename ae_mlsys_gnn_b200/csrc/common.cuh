@@ -113,6 +113,23 @@ struct RowTile {
       }
     }
   }
+  // Same as load, with ordinary (coherent) loads: for rows this kernel also writes.
+  __device__ __forceinline__ void load_rw(const float* row, int lane, float (&v)[Q][VW]) const {
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+      if (valid[q]) {
+        if constexpr (VEC) {
+          float4 t = *(reinterpret_cast<const float4*>(row) + lane + 32 * q);
+          v[q][0] = t.x; v[q][1] = t.y; v[q][2] = t.z; v[q][3] = t.w;
+        } else {
+          v[q][0] = row[lane + 32 * q];
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < VW; ++i) v[q][i] = 0.f;
+      }
+    }
+  }
   __device__ __forceinline__ void store(float* __restrict__ row, int lane,
                                         const float (&v)[Q][VW]) const {
 #pragma unroll

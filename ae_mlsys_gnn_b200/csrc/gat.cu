@@ -52,6 +52,17 @@ extern "C" int gnn_gat_fwd(const int* row_ptr, const int* col_ind, int64_t n_row
                            const float* in_feat, int H, int F, float negative_slope,
                            float* out, float* edge_max, float* edge_sum,
                            void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  return gnn_gat_fwd_part(row_ptr, col_ind, n_rows, nnz, attn_row, attn_col, in_feat, H, F,
+                          negative_slope, out, edge_max, edge_sum, 0, 1, workspace, workspace_bytes,
+                          stream);
+}
+
+extern "C" int gnn_gat_fwd_part(const int* row_ptr, const int* col_ind, int64_t n_rows,
+                                int64_t nnz, const float* attn_row, const float* attn_col,
+                                const float* in_feat, int H, int F, float negative_slope,
+                                float* out, float* edge_max, float* edge_sum, int accumulate,
+                                int finalize, void* workspace, size_t workspace_bytes,
+                                cudaStream_t stream) {
   if (n_rows < 0 || nnz < 0 || H <= 0 || F <= 0) return bad("gnn_gat_fwd: negative size");
   if (n_rows > INT32_MAX - 1 || nnz > INT32_MAX - 4096) return bad("gnn_gat_fwd: size exceeds int32 indexing");
   if (n_rows == 0) return GNN_OK;
@@ -88,6 +99,8 @@ extern "C" int gnn_gat_fwd(const int* row_ptr, const int* col_ind, int64_t n_row
       p.scratch = scratch;
       p.aux_off = round_up4(w);
       p.slot_stride = p.aux_off + round_up4(2 * pl.HP);
+      p.accumulate = accumulate ? 1 : 0;
+      p.finalize = finalize ? 1 : 0;
       bool ok = dispatch_tile(pl.HP, w, pl.vec, [&](auto hp, auto q, auto v) {
         constexpr int HP = decltype(hp)::value;
         GatSoftmaxPolicy<HP> pol;
@@ -243,6 +256,17 @@ extern "C" int gnn_gat_bwd_col(const int* col_ptr, const int* row_ind, int64_t n
                                const float* rowpack, const float* grad_out, int H, int F,
                                float negative_slope, float* grad_feat, float* grad_attn_col,
                                void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  return gnn_gat_bwd_col_part(col_ptr, row_ind, n_cols, nnz, in_feat, attn_col, rowpack, grad_out, H,
+                              F, negative_slope, grad_feat, grad_attn_col, 0, workspace,
+                              workspace_bytes, stream);
+}
+
+extern "C" int gnn_gat_bwd_col_part(const int* col_ptr, const int* row_ind, int64_t n_cols,
+                                    int64_t nnz, const float* in_feat, const float* attn_col,
+                                    const float* rowpack, const float* grad_out, int H, int F,
+                                    float negative_slope, float* grad_feat, float* grad_attn_col,
+                                    int accumulate, void* workspace, size_t workspace_bytes,
+                                    cudaStream_t stream) {
   if (n_cols < 0 || nnz < 0 || H <= 0 || F <= 0) return bad("gnn_gat_bwd_col: negative size");
   if (n_cols > INT32_MAX - 1 || nnz > INT32_MAX - 4096) return bad("gnn_gat_bwd_col: size exceeds int32 indexing");
   if (n_cols == 0) return GNN_OK;
@@ -275,6 +299,7 @@ extern "C" int gnn_gat_bwd_col(const int* col_ptr, const int* row_ind, int64_t n
   p.scratch = (float*)align_up((uintptr_t)workspace, 256);
   p.aux_off = round_up4((int)HF);
   p.slot_stride = p.aux_off + round_up4(2 * pl.HP);
+  p.accumulate = accumulate ? 1 : 0;
   bool ok = dispatch_tile(pl.HP, (int)HF, pl.vec, [&](auto hp, auto q, auto v) {
     launch_col<decltype(hp)::value, decltype(q)::value, decltype(v)::value>(p, stream);
   });

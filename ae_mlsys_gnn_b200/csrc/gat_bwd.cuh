@@ -245,6 +245,7 @@ struct GatBwdColParams {
   float* scratch;          // 2 * num_chunks slots of slot_stride floats
   int slot_stride;
   int aux_off;
+  int accumulate = 0;      // 1: add to the grad_feat / grad_attn_col left by earlier launches
 };
 
 template <int HP, int Q, bool VEC, int HPS = 0>
@@ -351,9 +352,20 @@ gat_bwd_col_kernel(GatBwdColParams p) {
     warp_multi_sum<HP>(B, lane);  // head h on lanes [h*32/HP, (h+1)*32/HP)
     constexpr int LPH = 32 / HP;
     if (first && last) {
-      t.store(p.grad_feat + (size_t)s * p.ld_gfeat, lane, acc);
-      if ((lane & (LPH - 1)) == 0 && lane / LPH < p.H)
-        p.grad_attn_seg[(size_t)s * p.ld_attn + lane / LPH] = B[0];
+      float* grow = p.grad_feat + (size_t)s * p.ld_gfeat;
+      if (p.accumulate) {
+        float old[Q][VW];
+        t.load_rw(grow, lane, old);
+#pragma unroll
+        for (int q = 0; q < Q; ++q)
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[q][i] += old[q][i];
+      }
+      t.store(grow, lane, acc);
+      if ((lane & (LPH - 1)) == 0 && lane / LPH < p.H) {
+        float* ga = p.grad_attn_seg + (size_t)s * p.ld_attn + lane / LPH;
+        *ga = p.accumulate ? *ga + B[0] : B[0];
+      }
     } else {
       float* slot = p.scratch + slot_index(chunk_id, first) * p.slot_stride;
       t.store(slot, lane, acc);
@@ -393,9 +405,22 @@ gat_bwd_col_fixup_kernel(GatBwdColParams p, int boundary_blocks) {
         for (int i = 0; i < VW; ++i) acc[q][i] += v[q][i];
       if (lane < HP) bt += slot[p.aux_off + lane];
     }
-    t.store(p.grad_feat + (size_t)s * p.ld_gfeat, lane, acc);
-    if (lane < p.H) p.grad_attn_seg[(size_t)s * p.ld_attn + lane] = bt;
+    float* grow = p.grad_feat + (size_t)s * p.ld_gfeat;
+    if (p.accumulate) {
+      float old[Q][VW];
+      t.load_rw(grow, lane, old);
+#pragma unroll
+      for (int q = 0; q < Q; ++q)
+#pragma unroll
+        for (int i = 0; i < VW; ++i) acc[q][i] += old[q][i];
+    }
+    t.store(grow, lane, acc);
+    if (lane < p.H) {
+      float* ga = p.grad_attn_seg + (size_t)s * p.ld_attn + lane;
+      *ga = p.accumulate ? *ga + bt : bt;
+    }
   } else {
+    if (p.accumulate) return;  // segments without edges in this launch keep what they have
     const int s = ((int)blockIdx.x - boundary_blocks) * kThreadsPerCta + threadIdx.x;
     bool empty = false;
     if (s < p.g.nseg) empty = __ldg(p.g.ptr + s) == __ldg(p.g.ptr + s + 1);

@@ -39,6 +39,14 @@ struct WGatherParams {
   float* scratch;      // 2 * num_chunks slots of slot_stride floats
   int slot_stride;     // round_up(width, 4) + aux floats, multiple of 4
   int aux_off;         // round_up(width, 4)
+  // Several launches may build one result, each over the edges of one column block of
+  // the graph (so that a block can be processed as soon as its rows have arrived):
+  //   accumulate = 1 : `out` (and the softmax state seg_max / seg_sum) already hold the
+  //                    partial result of earlier launches and are merged with this one;
+  //   finalize   = 0 : leave the softmax result un-normalised for a later launch.
+  // A single launch over the whole graph uses accumulate = 0, finalize = 1.
+  int accumulate = 0;
+  int finalize = 1;
 };
 
 // ----- weight policies ------------------------------------------------------
@@ -113,6 +121,72 @@ __device__ __forceinline__ void edge_weights(const GaussPolicy<HP>& pol, int H,
   }
 #pragma unroll
   for (int h = 0; h < HP; ++h) w[h] = h < H ? expf(-0.5f * acc[h]) : 0.f;
+}
+
+// Final step for one segment whose edges (of this launch) have all been reduced into
+// acc (softmax: un-normalised, relative to maximum m, with exp-sum ssum): merge with the
+// state left by earlier launches, normalise if asked to, store.
+template <template <int> class Policy, int HP, int Q, bool VEC>
+__device__ __forceinline__ void finish_segment(const WGatherParams& p, const Policy<HP>& pol,
+                                               const RowTile<Q, VEC>& t, int lane, int s,
+                                               float (&acc)[Q][VEC ? 4 : 1], float (&m)[HP],
+                                               float (&ssum)[HP]) {
+  constexpr int VW = VEC ? 4 : 1;
+  float* orow = p.out + (size_t)s * p.ld_out;
+  if constexpr (Policy<HP>::kSoftmax) {
+    if (p.accumulate) {
+      float fo[HP], fn[HP];
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        fo[h] = 0.f; fn[h] = 1.f;
+        if (h < p.H) {
+          const float mo = pol.seg_max[(size_t)s * pol.ld_attn + h];
+          const float so = pol.seg_sum[(size_t)s * pol.ld_attn + h];
+          const float M = fmaxf(mo, m[h]);
+          fo[h] = expf(mo - M);
+          fn[h] = expf(m[h] - M);
+          ssum[h] = so * fo[h] + ssum[h] * fn[h];
+          m[h] = M;
+        }
+      }
+      float old[Q][VW];
+      t.load_rw(orow, lane, old);
+#pragma unroll
+      for (int q = 0; q < Q; ++q) {
+        const float a = pick<HP>(fo, t.head[q]), b = pick<HP>(fn, t.head[q]);
+#pragma unroll
+        for (int i = 0; i < VW; ++i) acc[q][i] = fmaf(old[q][i], a, acc[q][i] * b);
+      }
+    }
+    if (p.finalize) {
+      float inv[HP];
+#pragma unroll
+      for (int h = 0; h < HP; ++h) inv[h] = 1.f / ssum[h];
+#pragma unroll
+      for (int q = 0; q < Q; ++q) {
+        const float iv = pick<HP>(inv, t.head[q]);
+#pragma unroll
+        for (int i = 0; i < VW; ++i) acc[q][i] *= iv;
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < HP; ++h) {
+      if (lane == h && h < p.H) {
+        pol.seg_max[(size_t)s * pol.ld_attn + h] = m[h];
+        pol.seg_sum[(size_t)s * pol.ld_attn + h] = ssum[h];
+      }
+    }
+  } else {
+    if (p.accumulate) {
+      float old[Q][VW];
+      t.load_rw(orow, lane, old);
+#pragma unroll
+      for (int q = 0; q < Q; ++q)
+#pragma unroll
+        for (int i = 0; i < VW; ++i) acc[q][i] += old[q][i];
+    }
+  }
+  t.store(orow, lane, acc);
 }
 
 // ----- main kernel ----------------------------------------------------------
@@ -236,25 +310,7 @@ wgather_kernel(WGatherParams p, Policy<HP> pol) {
     }
 
     if (first && last) {
-      if constexpr (SOFTMAX) {
-        float inv[HP];
-#pragma unroll
-        for (int h = 0; h < HP; ++h) inv[h] = 1.f / segs[h];
-#pragma unroll
-        for (int q = 0; q < Q; ++q) {
-          const float iv = pick<HP>(inv, t.head[q]);
-#pragma unroll
-          for (int i = 0; i < VW; ++i) acc[q][i] *= iv;
-        }
-#pragma unroll
-        for (int h = 0; h < HP; ++h) {
-          if (lane == h && h < p.H) {
-            pol.seg_max[(size_t)s * pol.ld_attn + h] = segm[h];
-            pol.seg_sum[(size_t)s * pol.ld_attn + h] = segs[h];
-          }
-        }
-      }
-      t.store(p.out + (size_t)s * p.ld_out, lane, acc);
+      finish_segment<Policy, HP, Q, VEC>(p, pol, t, lane, s, acc, segm, segs);
     } else {
       float* slot = p.scratch + slot_index(chunk_id, first) * p.slot_stride;
       t.store(slot, lane, acc);
@@ -335,29 +391,14 @@ wgather_fixup_kernel(WGatherParams p, Policy<HP> pol, int boundary_blocks) {
           for (int i = 0; i < VW; ++i) acc[q][i] += v[q][i];
       }
     }
-    if constexpr (SOFTMAX) {
-      float inv[HP];
-#pragma unroll
-      for (int h = 0; h < HP; ++h) inv[h] = 1.f / ssum[h];
-#pragma unroll
-      for (int q = 0; q < Q; ++q) {
-        const float iv = pick<HP>(inv, t.head[q]);
-#pragma unroll
-        for (int i = 0; i < VW; ++i) acc[q][i] *= iv;
-      }
-#pragma unroll
-      for (int h = 0; h < HP; ++h) {
-        if (lane == h && h < p.H) {
-          pol.seg_max[(size_t)s * pol.ld_attn + h] = m[h];
-          pol.seg_sum[(size_t)s * pol.ld_attn + h] = ssum[h];
-        }
-      }
-    }
-    t.store(p.out + (size_t)s * p.ld_out, lane, acc);
+    finish_segment<Policy, HP, Q, VEC>(p, pol, t, lane, s, acc, m, ssum);
   } else {
     const int s = ((int)blockIdx.x - boundary_blocks) * kThreadsPerCta + threadIdx.x;
     bool empty = false;
     if (s < p.g.nseg) empty = __ldg(p.g.ptr + s) == __ldg(p.g.ptr + s + 1);
+    // Segments without edges in this launch: the first launch gives them their defaults;
+    // a later, finalising launch normalises what earlier launches accumulated.
+    if (p.accumulate && !(SOFTMAX && p.finalize)) return;
     unsigned mask = __ballot_sync(kFull, empty);
     float z[Q][VW];
     t.zero(z);
@@ -365,11 +406,31 @@ wgather_fixup_kernel(WGatherParams p, Policy<HP> pol, int boundary_blocks) {
       const int src = __ffs(mask) - 1;
       mask &= mask - 1;
       const int se = s - lane + src;
-      t.store(p.out + (size_t)se * p.ld_out, lane, z);
-      if constexpr (SOFTMAX) {
-        if (lane < p.H) {
-          pol.seg_max[(size_t)se * pol.ld_attn + lane] = kNegBig;
-          pol.seg_sum[(size_t)se * pol.ld_attn + lane] = 0.f;
+      if (!p.accumulate) {
+        t.store(p.out + (size_t)se * p.ld_out, lane, z);
+        if constexpr (SOFTMAX) {
+          if (lane < p.H) {
+            pol.seg_max[(size_t)se * pol.ld_attn + lane] = kNegBig;
+            pol.seg_sum[(size_t)se * pol.ld_attn + lane] = 0.f;
+          }
+        }
+      } else {
+        if constexpr (SOFTMAX) {
+          float inv[HP];
+#pragma unroll
+          for (int h = 0; h < HP; ++h) {
+            const float sv = h < p.H ? pol.seg_sum[(size_t)se * pol.ld_attn + h] : 0.f;
+            inv[h] = sv > 0.f ? 1.f / sv : 0.f;
+          }
+          float v[Q][VW];
+          t.load_rw(p.out + (size_t)se * p.ld_out, lane, v);
+#pragma unroll
+          for (int q = 0; q < Q; ++q) {
+            const float iv = pick<HP>(inv, t.head[q]);
+#pragma unroll
+            for (int i = 0; i < VW; ++i) v[q][i] *= iv;
+          }
+          t.store(p.out + (size_t)se * p.ld_out, lane, v);
         }
       }
     }

@@ -30,6 +30,49 @@ def _check_graph(row_ptr, col_ind, dev, what="row_ptr/col_ind"):
     capi.require(col_ind, I32, f"{what}[1]", 1, dev)
 
 
+def gat_forward_part(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, out, edge_max,
+                     edge_sum, accumulate, finalize):
+    """gat_forward over one column block of the graph, into caller-provided ``out`` /
+    ``edge_max`` / ``edge_sum`` that carry the running state between blocks (first block:
+    accumulate=False; last block: finalize=True)."""
+    dev = in_feat.device
+    n_rows = row_ptr.numel() - 1
+    H, F = in_feat.shape[1], in_feat.shape[2]
+    nnz = col_ind.numel()
+    for name, t in (("attn_row", attn_row), ("attn_col", attn_col), ("edge_max", edge_max),
+                    ("edge_sum", edge_sum)):
+        capi.require(t, F32, name, 2, dev)
+    capi.require(in_feat, F32, "in_feat", 3, dev)
+    capi.require(out, F32, "out", 3, dev)
+    if out.shape[0] < n_rows or edge_max.shape[0] < n_rows or attn_row.shape[0] < n_rows:
+        raise ValueError("out / edge_max / attn_row need at least one row per CSR row")
+    nbytes = capi.workspace_bytes("gnn_gat_fwd_workspace_bytes", nnz, H, F)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_fwd_part", capi.ptr(row_ptr), capi.ptr(col_ind), n_rows, nnz,
+                  capi.ptr(attn_row), capi.ptr(attn_col), capi.ptr(in_feat), H, F,
+                  float(negative_slope), capi.ptr(out), capi.ptr(edge_max), capi.ptr(edge_sum),
+                  int(bool(accumulate)), int(bool(finalize)), capi.ptr(ws), ws.numel(),
+                  capi.stream_ptr(dev))
+
+
+def gat_backward_col_part(negative_slope, col_ptr, row_ind, in_feat, attn_col, rowpack, grad_out,
+                          grad_feat, grad_attn_col, accumulate):
+    """Column pass over one row block of the graph, into caller-provided ``grad_feat`` /
+    ``grad_attn_col`` (accumulate=False on the first block)."""
+    dev = in_feat.device
+    n_cols = col_ptr.numel() - 1
+    H, F = in_feat.shape[1], in_feat.shape[2]
+    nnz = row_ind.numel()
+    nbytes = capi.workspace_bytes("gnn_gat_bwd_col_workspace_bytes", nnz, H, F)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_bwd_col_part", capi.ptr(col_ptr), capi.ptr(row_ind), n_cols, nnz,
+                  capi.ptr(in_feat), capi.ptr(attn_col), capi.ptr(rowpack), capi.ptr(grad_out),
+                  H, F, float(negative_slope), capi.ptr(grad_feat), capi.ptr(grad_attn_col),
+                  int(bool(accumulate)), capi.ptr(ws), ws.numel(), capi.stream_ptr(dev))
+
+
 def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, pad_to=None):
     """(out, edge_max, edge_sum) — fused_gat_SM.gat_forward
     (src/fused_gat/fused_gat_SM.cu:536-558).  ``attn_row`` and the outputs have one

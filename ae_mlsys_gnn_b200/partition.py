@@ -7,20 +7,29 @@ The reference is single-GPU; nothing here has a counterpart in it.  Design:
   each (a row is never split).  Rank g owns block g: the CSR rows of the block (for
   the forward and the backward row pass) and the CSC columns of the block (for the
   backward column pass, which produces gradients of the sources the rank owns).
-* Every per-node tensor of a rank has ``max_n`` rows (the largest block, so that
-  all ranks contribute equally sized pieces to an all-gather); rows past the
-  rank's own count are zero padding.  Gathered tensors therefore have P*max_n rows,
-  and the column ids of the local CSR / row ids of the local CSC are remapped once
-  into that padded index space.
-* Per layer the only exchanges are: all-gather of the projected features h and of
-  attn_col (forward); all-gather of grad_out and of the per-row pack
-  {attn_row, max, 1/sum, S} (backward).  No reduction of feature gradients is
-  needed because the column pass sums over all destinations of an owned source.
-  Weight gradients are all-reduced after the backward (they are tiny).
+* Every per-node tensor of a rank has ``max_n = K * cn`` rows: the rank's own rows,
+  then zero padding; K is the number of exchange pieces and cn the rows per piece.
+  Piece c of a tensor is rows [c*cn, (c+1)*cn) of every rank; one all-gather moves piece c
+  of all ranks into rows [c*P*cn, (c+1)*P*cn) of the gathered tensor ("piece-major"
+  order).  The column ids of the local CSR / row ids of the local CSC are remapped once
+  into that gathered index space.
+* The local CSR is additionally split by the piece its source lies in (and the local CSC
+  by the piece of its destination).  The forward launches the fused kernel once per
+  piece, as soon as that piece of the projected features has arrived, merging the
+  online-softmax state between launches (gnn_gat_fwd_part); the backward column pass
+  does the same with the pieces of grad_out (gnn_gat_bwd_col_part).  The transfer of
+  piece c+1 therefore runs under the aggregation of piece c, and the gather of grad_out
+  also runs under the whole row pass.
+* Per layer the exchanges are: h and attn_col (forward); grad_out and the per-row pack
+  {attn_row, max, 1/sum, S} (backward).  The small tensors travel on a second
+  communicator so that they do not queue behind the large pieces.  No reduction of
+  feature gradients is needed because the column pass sums over all destinations of an
+  owned source.  Weight gradients are all-reduced after the backward (they are tiny).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+import dataclasses
+from dataclasses import dataclass, field
 
 import torch
 import torch.distributed as dist
@@ -29,6 +38,8 @@ from torch import nn
 
 from .layers.gatconv_layer import _GATBase
 from .operators import dense
+
+DEFAULT_PIECES = 4
 
 
 def edge_balanced_bounds(row_ptr: torch.Tensor, world: int) -> list[int]:
@@ -51,11 +62,16 @@ class RowBlockPartition:
     rank: int
     world: int
     bounds: list[int]          # global row boundaries, world+1 entries
-    max_n: int                 # rows of every per-rank tensor (largest block)
+    pieces: int                # K: exchange pieces per tensor
+    cn: int                    # rows per piece; max_n = pieces * cn
     row_ptr: torch.Tensor      # local CSR, int32 [n_local+1]
-    col_ind: torch.Tensor      # int32, ids in the padded gathered space
-    col_ptr: torch.Tensor      # local CSC of the owned sources, int32 [n_local+1]
-    row_ind: torch.Tensor      # int32, ids in the padded gathered space
+    col_ind: torch.Tensor      # int32, ids in the gathered (piece-major) space
+    csr_parts: list = field(default_factory=list)  # K x (row_ptr_c, col_ind_c): sources in piece c
+    csc_parts: list = field(default_factory=list)  # K x (col_ptr_c, row_ind_c): destinations in piece c
+
+    @property
+    def max_n(self) -> int:
+        return self.pieces * self.cn
 
     @property
     def n_local(self) -> int:
@@ -74,39 +90,108 @@ class RowBlockPartition:
     def local_slice(self, x_global: torch.Tensor) -> torch.Tensor:
         return x_global[self.bounds[self.rank]: self.bounds[self.rank + 1]]
 
+    def gathered_positions(self, rank: int) -> torch.Tensor:
+        """Rows of a gathered tensor that hold the local rows 0..n-1 of `rank`."""
+        n = self.bounds[rank + 1] - self.bounds[rank]
+        i = torch.arange(n)
+        c = i // self.cn
+        return c * (self.world * self.cn) + rank * self.cn + (i - c * self.cn)
 
-def _to_padded_ids(ids: torch.Tensor, bounds: list[int], max_n: int) -> torch.Tensor:
+    def index_tensors(self) -> dict:
+        d = {"row_ptr": self.row_ptr, "col_ind": self.col_ind}
+        for c, (a, b) in enumerate(self.csr_parts):
+            d[f"csr{c}_ptr"], d[f"csr{c}_idx"] = a, b
+        for c, (a, b) in enumerate(self.csc_parts):
+            d[f"csc{c}_ptr"], d[f"csc{c}_idx"] = a, b
+        return d
+
+    def with_index_tensors(self, d: dict) -> "RowBlockPartition":
+        return dataclasses.replace(
+            self, row_ptr=d["row_ptr"], col_ind=d["col_ind"],
+            csr_parts=[(d[f"csr{c}_ptr"], d[f"csr{c}_idx"]) for c in range(self.pieces)],
+            csc_parts=[(d[f"csc{c}_ptr"], d[f"csc{c}_idx"]) for c in range(self.pieces)])
+
+
+def _to_gathered_ids(ids: torch.Tensor, bounds: list[int], cn: int, world: int) -> torch.Tensor:
     b = torch.tensor(bounds, dtype=torch.long, device=ids.device)
     v = ids.long()
     owner = torch.bucketize(v, b[1:-1], right=True)
-    return (owner * max_n + (v - b[owner])).to(torch.int32)
+    local = v - b[owner]
+    c = torch.div(local, cn, rounding_mode="floor")
+    return c * (world * cn) + owner * cn + (local - c * cn)
+
+
+def _sort_within_segments(ptr: torch.Tensor, ids: torch.Tensor, id_span: int):
+    """Edge ids of every segment in ascending order (so that pieces are contiguous)."""
+    n = ptr.numel() - 1
+    p = ptr.long()
+    seg = torch.repeat_interleave(torch.arange(n, device=ptr.device), p[1:] - p[:-1])
+    order = torch.argsort(seg * id_span + ids, stable=True)
+    return ids[order], seg
+
+
+def _split_by_piece(ptr: torch.Tensor, ids_sorted: torch.Tensor, seg: torch.Tensor, pieces: int,
+                    span: int):
+    """Splits a segment array whose ids are piece-major (piece = id // span) and sorted
+    inside every segment into one segment array per piece."""
+    n = ptr.numel() - 1
+    piece = torch.div(ids_sorted, span, rounding_mode="floor")
+    key = piece * n + seg
+    order = torch.argsort(key, stable=True)
+    counts = torch.bincount(key, minlength=pieces * n).view(pieces, n)
+    by_piece = ids_sorted[order]
+    per_piece = counts.sum(1).tolist()
+    out, start = [], 0
+    for c in range(pieces):
+        ptr_c = torch.zeros(n + 1, dtype=torch.int64, device=ptr.device)
+        ptr_c[1:] = torch.cumsum(counts[c], 0)
+        out.append((ptr_c.to(torch.int32).contiguous(),
+                    by_piece[start: start + per_piece[c]].to(torch.int32).contiguous()))
+        start += per_piece[c]
+    return out
 
 
 def build_partition(row_ptr, col_ind, col_ptr, row_ind, rank: int, world: int,
-                    bounds: list[int] | None = None) -> RowBlockPartition:
+                    bounds: list[int] | None = None, pieces: int | None = None) -> RowBlockPartition:
     """Cuts the global CSR (row_ptr, col_ind) and CSC (col_ptr, row_ind) of a square
     graph into rank `rank`'s blocks."""
     bounds = edge_balanced_bounds(row_ptr, world) if bounds is None else bounds
-    max_n = max(bounds[g + 1] - bounds[g] for g in range(world))
+    pieces = (DEFAULT_PIECES if world > 1 else 1) if pieces is None else pieces
+    largest = max(bounds[g + 1] - bounds[g] for g in range(world))
+    cn = max(1, -(-largest // pieces))
     lo, hi = bounds[rank], bounds[rank + 1]
+    span = world * cn
 
     def cut(ptr, idx):
         p = ptr[lo: hi + 1].long()
         e0, e1 = int(p[0].item()), int(p[-1].item())
-        return (p - e0).to(torch.int32).contiguous(), _to_padded_ids(idx[e0:e1], bounds, max_n).contiguous()
+        lp = (p - e0).to(torch.int32).contiguous()
+        ids, seg = _sort_within_segments(lp, _to_gathered_ids(idx[e0:e1], bounds, cn, world),
+                                         pieces * span)
+        return lp, ids, seg
 
-    rp, ci = cut(row_ptr, col_ind)
-    cp, ri = cut(col_ptr, row_ind)
-    return RowBlockPartition(rank, world, bounds, max_n, rp, ci, cp, ri)
+    rp, ci, rseg = cut(row_ptr, col_ind)
+    cp, ri, cseg = cut(col_ptr, row_ind)
+    csr_parts = _split_by_piece(rp, ci, rseg, pieces, span)
+    csc_parts = _split_by_piece(cp, ri, cseg, pieces, span)
+    return RowBlockPartition(rank, world, bounds, pieces, cn, rp, ci.to(torch.int32).contiguous(),
+                             csr_parts, csc_parts)
 
 
-def all_gather_rows(x: torch.Tensor, world: int, group=None, async_op: bool = False):
-    """All-gather of equally sized row blocks: (max_n, ...) -> (world*max_n, ...)."""
-    if world == 1:
-        return (x, None) if async_op else x
-    out = x.new_empty((world * x.shape[0],) + tuple(x.shape[1:]))
-    work = dist.all_gather_into_tensor(out, x.contiguous(), group=group, async_op=async_op)
-    return (out, work) if async_op else out
+def gather_pieces(x: torch.Tensor, part: RowBlockPartition, group=None, async_op: bool = False):
+    """All-gather of a (max_n, ...) tensor, one collective per piece, into the piece-major
+    gathered tensor (P*max_n, ...).  Returns (gathered, [work per piece] or None)."""
+    P, K, cn = part.world, part.pieces, part.cn
+    if P == 1:
+        return x, None
+    x = x.contiguous()
+    out = x.new_empty((P * part.max_n,) + tuple(x.shape[1:]))
+    works = []
+    for c in range(K):
+        w = dist.all_gather_into_tensor(out[c * P * cn: (c + 1) * P * cn], x[c * cn: (c + 1) * cn],
+                                        group=group, async_op=async_op)
+        works.append(w)
+    return out, (works if async_op else None)
 
 
 class _CudaKernels:
@@ -126,10 +211,12 @@ class _CudaKernels:
         return gat_scores_backward(h, attn_l, attn_r, grad_attn_row, grad_attn_col, grad_feat)
 
     @staticmethod
-    def forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full, pad_to=None):
-        from .operators.fused_gat import gat_forward
+    def forward_part(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full, out, edge_max, edge_sum,
+                     accumulate, finalize):
+        from .operators.fused_gat import gat_forward_part
 
-        return gat_forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full, pad_to=pad_to)
+        gat_forward_part(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full, out, edge_max,
+                         edge_sum, accumulate, finalize)
 
     @staticmethod
     def backward_row(slope, row_ptr, col_ind, edge_max, edge_sum, h_full, attn_row, attn_col_full,
@@ -140,12 +227,12 @@ class _CudaKernels:
                                 attn_col_full, grad_out, pad_to=pad_to)
 
     @staticmethod
-    def backward_col(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full,
-                     pad_to=None):
-        from .operators.fused_gat import gat_backward_col
+    def backward_col_part(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full,
+                          grad_feat, grad_attn_col, accumulate):
+        from .operators.fused_gat import gat_backward_col_part
 
-        return gat_backward_col(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full,
-                                gout_full, pad_to=pad_to)
+        gat_backward_col_part(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full,
+                              gout_full, grad_feat, grad_attn_col, accumulate)
 
 
 class PartitionedGATFunction(torch.autograd.Function):
@@ -153,73 +240,94 @@ class PartitionedGATFunction(torch.autograd.Function):
     ``h`` and the output have max_n rows (the rank's rows, then zero padding)."""
 
     @staticmethod
-    def forward(ctx, h, attn_l, attn_r, part: RowBlockPartition, slope, kernels, group):
-        n, P = part.n_local, part.world
+    def forward(ctx, h, attn_l, attn_r, part: RowBlockPartition, slope, kernels, group, small_group):
+        n, K = part.n_local, part.pieces
         h, attn_l, attn_r = h.contiguous(), attn_l.contiguous(), attn_r.contiguous()
-        # start moving h while the scores are computed from the local copy
-        h_full, work = all_gather_rows(h, P, group, async_op=True)
+        H, Fo = h.shape[1], h.shape[2]
         attn_row, attn_col = kernels.scores_forward(h, attn_l, attn_r)
-        ac_full = all_gather_rows(attn_col, P, group)
-        if work is not None:
-            work.wait()
-        out, edge_max, edge_sum = kernels.forward(attn_row[:n], ac_full, part.row_ptr, part.col_ind,
-                                                  slope, h_full, pad_to=part.max_n)
+        ac_full, _ = gather_pieces(attn_col, part, small_group)
+        h_full, works = gather_pieces(h, part, group, async_op=True)
+        out = h.new_empty((part.max_n, H, Fo))
+        if n < part.max_n:
+            out[n:].zero_()
+        edge_max = h.new_empty((n, H))
+        edge_sum = h.new_empty((n, H))
+        for c in range(K):
+            if works is not None:
+                works[c].wait()
+            rp_c, ci_c = part.csr_parts[c]
+            kernels.forward_part(attn_row[:n], ac_full, rp_c, ci_c, slope, h_full, out, edge_max,
+                                 edge_sum, c > 0, c == K - 1)
         ctx.save_for_backward(attn_row, attn_col, h, h_full, ac_full, edge_max, edge_sum, attn_l,
                               attn_r)
-        ctx.part, ctx.slope, ctx.kernels, ctx.group = part, slope, kernels, group
+        ctx.part, ctx.slope, ctx.kernels = part, slope, kernels
+        ctx.group, ctx.small_group = group, small_group
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         (attn_row, attn_col, h, h_full, ac_full, edge_max, edge_sum, attn_l,
          attn_r) = ctx.saved_tensors
-        part, slope, kernels, group = ctx.part, ctx.slope, ctx.kernels, ctx.group
-        n, P = part.n_local, part.world
+        part, slope, kernels = ctx.part, ctx.slope, ctx.kernels
+        n, K = part.n_local, part.pieces
+        H, Fo = h.shape[1], h.shape[2]
         grad_out = grad_out.contiguous()
-        # the gather of grad_out does not depend on the row pass: run them together
-        gout_full, work = all_gather_rows(grad_out, P, group, async_op=True)
+        # the pieces of grad_out travel while the row pass runs on local data
+        gout_full, works = gather_pieces(grad_out, part, ctx.group, async_op=True)
         gar_l, rowpack = kernels.backward_row(slope, part.row_ptr, part.col_ind, edge_max, edge_sum,
                                               h_full, attn_row[:n], ac_full, grad_out[:n],
                                               pad_to=part.max_n)
-        rp_full = all_gather_rows(rowpack, P, group)
-        if work is not None:
-            work.wait()
-        gh, gac_l = kernels.backward_col(slope, part.col_ptr, part.row_ind, h[:n], attn_col[:n],
-                                         rp_full, gout_full, pad_to=part.max_n)
+        rp_full, _ = gather_pieces(rowpack, part, ctx.small_group)
+        gh = h.new_empty((part.max_n, H, Fo))
+        if n < part.max_n:
+            gh[n:].zero_()
+        gac_l = h.new_empty((n, H))
+        for c in range(K):
+            if works is not None:
+                works[c].wait()
+            cp_c, ri_c = part.csc_parts[c]
+            kernels.backward_col_part(slope, cp_c, ri_c, h[:n], attn_col[:n], rp_full, gout_full,
+                                      gh, gac_l, c > 0)
         gl, gr = kernels.scores_backward(h[:n], attn_l, attn_r, gar_l, gac_l, gh[:n])
-        return gh, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None
+        return gh, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None
 
 
 class PartitionedGATConv(_GATBase):
     """GATConv (same parameters, same state_dict) on a RowBlockPartition."""
 
     def __init__(self, in_feats, out_feats, num_heads, negative_slope=0.2, kernels=_CudaKernels,
-                 group=None):
+                 group=None, small_group=None):
         super().__init__(in_feats, out_feats, num_heads, negative_slope)
         self.kernels = kernels
         self.group = group
+        self.small_group = small_group
 
     def forward(self, part: RowBlockPartition, feat):
         h = dense.project(feat, self.W).view(-1, self.num_heads, self.out_feats)
         return PartitionedGATFunction.apply(h, self.attn_l, self.attn_r, part, self.negative_slope,
-                                            self.kernels, self.group)
+                                            self.kernels, self.group, self.small_group)
 
 
 class PartitionedGAT(nn.Module):
     """models.GAT on a partition: identical parameters; inputs/outputs hold the rank's
-    max_n (padded) rows."""
+    max_n (padded) rows.  ``small_group`` is a second communicator over the same ranks for
+    the small per-node tensors (created here when torch.distributed is initialised)."""
 
     def __init__(self, in_dim, hidden, heads, num_classes, out_heads=1, negative_slope=0.2,
-                 activation="elu", kernels=_CudaKernels, group=None):
+                 activation="elu", kernels=_CudaKernels, group=None, small_group=None):
         super().__init__()
+        if (small_group is None and dist.is_available() and dist.is_initialized()
+                and dist.get_world_size() > 1):
+            small_group = dist.new_group(ranks=list(range(dist.get_world_size())))
         if isinstance(hidden, int):
             hidden = [hidden] * len(heads)
         dims_in = [in_dim] + [h * f for h, f in zip(heads, hidden)]
         self.gat_layers = nn.ModuleList(
-            [PartitionedGATConv(dims_in[i], hidden[i], heads[i], negative_slope, kernels, group)
-             for i in range(len(heads))])
+            [PartitionedGATConv(dims_in[i], hidden[i], heads[i], negative_slope, kernels, group,
+                                small_group) for i in range(len(heads))])
         self.gat_layers.append(
-            PartitionedGATConv(dims_in[-1], num_classes, out_heads, negative_slope, kernels, group))
+            PartitionedGATConv(dims_in[-1], num_classes, out_heads, negative_slope, kernels, group,
+                               small_group))
         self.activation = activation
         self.group = group
 

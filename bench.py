@@ -172,12 +172,12 @@ class BytesLedger:
 
     @staticmethod
     def _bytes_of(name, a):
-        if name == "gnn_gat_fwd":
-            return algorithmic_bytes(name, a[2], a[3], a[7], a[8])
+        if name in ("gnn_gat_fwd", "gnn_gat_fwd_part"):
+            return algorithmic_bytes("gnn_gat_fwd", a[2], a[3], a[7], a[8])
         if name == "gnn_gat_bwd_row":
             return algorithmic_bytes(name, a[2], a[3], a[10], a[11])
-        if name == "gnn_gat_bwd_col":
-            return algorithmic_bytes(name, a[2], a[3], a[8], a[9])
+        if name in ("gnn_gat_bwd_col", "gnn_gat_bwd_col_part"):
+            return algorithmic_bytes("gnn_gat_bwd_col", a[2], a[3], a[8], a[9])
         if name == "gnn_edgeconv_fwd":
             return algorithmic_bytes(name, a[4], a[4] * a[0], 1, a[5])
         if name == "gnn_edgeconv_bwd":
@@ -531,8 +531,7 @@ def run_e2e(args, wl, d, model, opt, part, dev, world):
 
     kind = wl["kind"]
     if kind == "gat" and part is not None:
-        host = {k: pin(v) for k, v in dict(row_ptr=part.row_ptr, col_ind=part.col_ind, col_ptr=part.col_ptr,
-                                           row_ind=part.row_ind, x=d["x_l"], y=d["y_l"]).items()}
+        host = {k: pin(v) for k, v in dict(part.index_tensors(), x=d["x_l"], y=d["y_l"]).items()}
     elif kind == "edgeconv":
         host = {k: pin(v) for k, v in dict(points=d["points"], src=d["src"], y=d["labels"]).items()}
     else:
@@ -545,10 +544,7 @@ def run_e2e(args, wl, d, model, opt, part, dev, world):
     def one():
         t = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
         if kind == "gat" and part is not None:
-            import dataclasses
-
-            p2 = dataclasses.replace(part, row_ptr=t["row_ptr"], col_ind=t["col_ind"], col_ptr=t["col_ptr"],
-                                     row_ind=t["row_ind"])
+            p2 = part.with_index_tensors(t)
             out = model(p2, t["x"])
             loss = model.loss(p2, out, t["y"])
             opt.zero_grad(set_to_none=True)

@@ -80,6 +80,18 @@ int gnn_gat_fwd(const int* row_ptr, const int* col_ind, int64_t n_rows, int64_t 
                 float* edge_sum /*[n_rows,H]*/, void* workspace, size_t workspace_bytes,
                 cudaStream_t stream);
 
+/* gnn_gat_fwd over ONE column block of the graph: the CSR given holds only the edges whose
+ * sources lie in that block, and several calls build one result, so that a block can be
+ * aggregated as soon as its source rows have arrived from the other GPUs.  accumulate = 0
+ * on the first block, 1 afterwards (out, edge_max, edge_sum then carry the running,
+ * un-normalised state); finalize = 1 on the last block only.  accumulate = 0, finalize = 1
+ * is gnn_gat_fwd.  No counterpart in the reference (single GPU). */
+int gnn_gat_fwd_part(const int* row_ptr, const int* col_ind, int64_t n_rows, int64_t nnz,
+                     const float* attn_row, const float* attn_col, const float* in_feat, int H,
+                     int F, float negative_slope, float* out, float* edge_max, float* edge_sum,
+                     int accumulate, int finalize, void* workspace, size_t workspace_bytes,
+                     cudaStream_t stream);
+
 /* gnn_gat_fwd for callers that cannot allocate device memory when they run a layer (a
  * server whose memory pool took the whole GPU at start-up, a plugin inside another
  * program's memory plan, a latency-critical path).  Has no counterpart in the
@@ -148,6 +160,14 @@ int gnn_gat_scores_bwd(const float* feat, const float* attn_l, const float* attn
                        int F, float* grad_feat /*[n,H,F], updated in place*/,
                        float* grad_attn_l /*[H,F]*/, float* grad_attn_r /*[H,F]*/, void* workspace,
                        size_t workspace_bytes, cudaStream_t stream);
+
+/* Column pass over ONE row block of the graph (CSC restricted to destinations of that
+ * block); accumulate = 1 adds to the grad_feat / grad_attn_col of earlier calls. */
+int gnn_gat_bwd_col_part(const int* col_ptr, const int* row_ind, int64_t n_cols, int64_t nnz,
+                         const float* in_feat, const float* attn_col, const float* rowpack,
+                         const float* grad_out, int H, int F, float negative_slope,
+                         float* grad_feat, float* grad_attn_col, int accumulate, void* workspace,
+                         size_t workspace_bytes, cudaStream_t stream);
 
 /* Per-edge activated logits and normalised attention (E x H each), the tensors the
  * stash / fusescatter variants keep: fused_gat_stash.gat_forward and

@@ -211,3 +211,43 @@ def test_gat_layer_unfused_scores_path(cuda):
                     layer.attn_r.grad.clone()))
     for name, a, b in zip(("out", "x.grad", "W.grad", "attn_l.grad", "attn_r.grad"), *res):
         assert_close(a, b, name, scale_atol=True)
+
+
+@pytest.mark.parametrize("H,F", [(4, 128), (4, 64), (1, 47), (3, 12)])
+@pytest.mark.parametrize("pieces", [2, 5])
+def test_gat_column_pieces_match_single_launch(cuda, H, F, pieces):
+    """Forward and column pass launched once per column / row piece of the graph, with the
+    running state merged between launches, equal the single launch (same tolerance as
+    against the oracle; the order of summation differs)."""
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+    from ae_mlsys_gnn_b200.operators.fused_gat import (gat_backward_col, gat_backward_col_part,
+                                                       gat_backward_row, gat_forward, gat_forward_part)
+    from ae_mlsys_gnn_b200.partition import _split_by_piece
+
+    g = power_law_graph(2500, 45, seed=12)
+    # leave some rows without edges in some pieces, and some without any edge
+    attn_row, attn_col, feat, gout = _inputs(g, H, F, 12)
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    cp, ri, _ = csr2csc(rp, ci)
+    d = [t.to(cuda) for t in (attn_row, attn_col, feat, gout)]
+    out, m, s = gat_forward(d[0], d[1], rp, ci, 0.2, d[2])
+    span = -(-g.n // pieces)
+    seg = torch.repeat_interleave(torch.arange(g.n, device=cuda), (rp[1:] - rp[:-1]).long())
+    parts = _split_by_piece(rp, ci.long(), seg, pieces, span)
+    out2 = torch.full_like(out, float("nan"))
+    m2, s2 = torch.full_like(m, float("nan")), torch.full_like(s, float("nan"))
+    for c, (rp_c, ci_c) in enumerate(parts):
+        gat_forward_part(d[0], d[1], rp_c, ci_c, 0.2, d[2], out2, m2, s2, c > 0, c == pieces - 1)
+    assert_close(out2, out, "out by pieces")
+    assert_close(s2, s, "edge_sum by pieces")
+    assert torch.equal(m2, m)
+
+    _, rowpack = gat_backward_row(0.2, rp, ci, m, s, d[2], d[0], d[1], d[3])
+    gf, gac = gat_backward_col(0.2, cp, ri, d[2], d[1], rowpack, d[3])
+    cseg = torch.repeat_interleave(torch.arange(g.n, device=cuda), (cp[1:] - cp[:-1]).long())
+    cparts = _split_by_piece(cp, ri.long(), cseg, pieces, span)
+    gf2, gac2 = torch.full_like(gf, float("nan")), torch.full_like(gac, float("nan"))
+    for c, (cp_c, ri_c) in enumerate(cparts):
+        gat_backward_col_part(0.2, cp_c, ri_c, d[2], d[1], rowpack, d[3], gf2, gac2, c > 0)
+    assert_close(gf2, gf, "grad_feat by pieces", scale_atol=True)
+    assert_close(gac2, gac, "grad_attn_col by pieces", scale_atol=True)

@@ -34,9 +34,29 @@ class OracleKernels:
         return (gar[:, :, None] * h).sum(0), (gac[:, :, None] * h).sum(0)
 
     @staticmethod
-    def forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full, pad_to=None):
-        o, m, s = ref.gat_forward(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full)
-        return _pad(o.float(), pad_to), m.float(), s.float()
+    def forward_part(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full, out, edge_max, edge_sum,
+                     accumulate, finalize):
+        n, H = attn_row.shape
+        rows, cols = ref.rows_of(row_ptr), col_ind.long()
+        e = ref.leaky_relu(attn_row.double()[rows] + attn_col_full.double()[cols], slope)
+        m_p = torch.full((n, H), ref.NEG_BIG, dtype=torch.float64).scatter_reduce(
+            0, rows[:, None].expand(-1, H), e, "amax", include_self=True)
+        ex = torch.exp(e - m_p[rows])
+        s_p = torch.zeros(n, H, dtype=torch.float64).index_add_(0, rows, ex)
+        acc = torch.zeros((n,) + tuple(h_full.shape[1:]), dtype=torch.float64)
+        acc.index_add_(0, rows, ex[:, :, None] * h_full.double()[cols])
+        if accumulate:
+            m_o, s_o = edge_max.double(), edge_sum.double()
+            M = torch.maximum(m_o, m_p)
+            fo, fn = torch.exp(m_o - M), torch.exp(m_p - M)
+            acc = out[:n].double() * fo[:, :, None] + acc * fn[:, :, None]
+            s_p = s_o * fo + s_p * fn
+            m_p = M
+        if finalize:
+            acc = torch.where(s_p[:, :, None] > 0, acc / s_p[:, :, None].clamp_min(1e-300), acc)
+        out[:n] = acc.float()
+        edge_max.copy_(m_p.float())
+        edge_sum.copy_(s_p.float())
 
     @staticmethod
     def backward_row(slope, row_ptr, col_ind, edge_max, edge_sum, h_full, attn_row, attn_col_full, grad_out,
@@ -53,7 +73,8 @@ class OracleKernels:
         return gar.float(), _pad(pack.float(), pad_to)
 
     @staticmethod
-    def backward_col(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full, pad_to=None):
+    def backward_col_part(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full,
+                          grad_feat, grad_attn_col, accumulate):
         cols, rows = ref.rows_of(col_ptr), row_ind.long()   # segments are the owned sources
         rp = rowpack_full.double()
         x = rp[rows, 0] + attn_col_local.double()[cols]
@@ -66,7 +87,12 @@ class OracleKernels:
         ge = alpha * (g - rp[rows, 3])
         ge = torch.where(e < 0, ge * slope, ge)
         gac = torch.zeros(n, H, dtype=torch.float64).index_add_(0, cols, ge)
-        return _pad(gh.float(), pad_to), gac.float()
+        if accumulate:
+            grad_feat[:n] += gh.float()
+            grad_attn_col += gac.float()
+        else:
+            grad_feat[:n] = gh.float()
+            grad_attn_col.copy_(gac.float())
 
 
 def test_edge_balanced_bounds():
@@ -82,21 +108,38 @@ def test_edge_balanced_bounds():
         assert max(per) <= g.nnz / world + int((rp[1:] - rp[:-1]).max())
 
 
-def test_partition_blocks_cover_graph():
+@pytest.mark.parametrize("pieces", [1, 3])
+def test_partition_blocks_cover_graph(pieces):
     from ae_mlsys_gnn_b200.partition import build_partition
 
     g = power_law_graph(500, 12, seed=2)
     cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)
     world = 4
-    parts = [build_partition(g.row_ptr, g.col_ind, cp, ri, r, world) for r in range(world)]
-    max_n = parts[0].max_n
-    assert sum(p.n_local for p in parts) == g.n
-    assert sum(p.col_ind.numel() for p in parts) == g.nnz == sum(p.row_ind.numel() for p in parts)
-    # padded ids map back to the global ids
-    b = torch.tensor(parts[0].bounds)
-    glob = torch.cat([p.col_ind.long() for p in parts])
-    owner = glob // max_n
-    assert torch.equal(b[owner] + glob % max_n, g.col_ind.long())
+    parts = [build_partition(g.row_ptr, g.col_ind, cp, ri, r, world, pieces=pieces) for r in range(world)]
+    p0 = parts[0]
+    assert sum(p.n_local for p in parts) == g.n and p0.max_n == pieces * p0.cn
+    assert sum(p.col_ind.numel() for p in parts) == g.nnz
+    # position of every global node in the gathered (piece-major) index space
+    pos = torch.cat([p0.gathered_positions(r) for r in range(world)])
+    assert pos.unique().numel() == g.n and int(pos.max()) < world * p0.max_n
+    inv = torch.full((world * p0.max_n,), -1, dtype=torch.long)
+    inv[pos] = torch.arange(g.n)
+    for r, p in enumerate(parts):
+        lo, hi = p.bounds[r], p.bounds[r + 1]
+        rp = g.row_ptr.long()
+        # same edge set per row in the full local CSR and in the union of its pieces
+        want = g.col_ind.long()[rp[lo]:rp[hi]]
+        rows = ref.rows_of(p.row_ptr)
+        got = inv[p.col_ind.long()]
+        assert torch.equal(torch.sort(rows * g.n + got).values,
+                           torch.sort(ref.rows_of(g.row_ptr)[rp[lo]:rp[hi]].sub(lo) * g.n + want).values)
+        keys = []
+        for c, (ptr_c, idx_c) in enumerate(p.csr_parts):
+            assert ptr_c.numel() == p.n_local + 1
+            assert torch.all(idx_c.long() // (world * p.cn) == c)
+            keys.append(ref.rows_of(ptr_c) * g.n + inv[idx_c.long()])
+        assert torch.equal(torch.sort(torch.cat(keys)).values, torch.sort(rows * g.n + got).values)
+        assert sum(i.numel() for _, i in p.csc_parts) == int(cp.long()[hi] - cp.long()[lo])
 
 
 def _worker(rank, world, port, results):
@@ -111,7 +154,7 @@ def _worker(rank, world, port, results):
         cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)
         x = torch.randn(g.n, 12, generator=torch.Generator().manual_seed(1))
         y = torch.randint(0, 5, (g.n,), generator=torch.Generator().manual_seed(2))
-        part = build_partition(g.row_ptr, g.col_ind, cp, ri, rank, world)
+        part = build_partition(g.row_ptr, g.col_ind, cp, ri, rank, world, pieces=3)
         model = PartitionedGAT(12, [8], [2], 5, 1, kernels=OracleKernels)
         out = model(part, part.pad_rows(part.local_slice(x)))
         loss = model.loss(part, out, part.local_slice(y))
@@ -122,7 +165,7 @@ def _worker(rank, world, port, results):
         gathered = [torch.empty(part.max_n, out.shape[1]) for _ in range(world)]
         dist.all_gather(gathered, out.detach())
         if rank == 0:
-            full = torch.cat([gathered[r][: part.bounds[r + 1] - part.bounds[r]] for r in range(world)])
+            full = torch.cat([gathered[r][: part.bounds[r + 1] - part.bounds[r]] for r in range(world)])  # rank-major list
             results["out"] = full
             results["loss"] = total
             results["grads"] = {k: p.grad.clone() for k, p in model.named_parameters()}

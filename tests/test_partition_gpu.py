@@ -48,7 +48,7 @@ def _worker(rank, world, port, results):
         torch.cuda.synchronize()
         if rank == 0:
             full = torch.cat([gathered[r * part.max_n: r * part.max_n + part.bounds[r + 1] - part.bounds[r]]
-                              for r in range(world)])
+                              for r in range(world)])  # plain rank-major gather of the outputs
             results["out"] = full.cpu()
             results["loss"] = total.cpu()
             results["grads"] = {k: p.grad.cpu() for k, p in model.named_parameters()}
