@@ -39,7 +39,13 @@ from torch import nn
 from .layers.gatconv_layer import _GATBase
 from .operators import dense
 
-DEFAULT_PIECES = 4
+import os
+
+# exchange pieces per tensor when more than one rank takes part (GNN_B200_PIECES overrides)
+# Measured on 8 B200s (config-5 GAT): 4 pieces hide ~8 ms of transfer per epoch but the
+# per-piece launches (short row pieces, read-modify-write of the outputs) cost ~12 ms, so
+# the default is one piece; the piecewise path stays available for slower interconnects.
+DEFAULT_PIECES = int(os.environ.get("GNN_B200_PIECES", "1"))
 
 
 def edge_balanced_bounds(row_ptr: torch.Tensor, world: int) -> list[int]:
@@ -240,13 +246,17 @@ class PartitionedGATFunction(torch.autograd.Function):
     ``h`` and the output have max_n rows (the rank's rows, then zero padding)."""
 
     @staticmethod
-    def forward(ctx, h, attn_l, attn_r, part: RowBlockPartition, slope, kernels, group, small_group):
+    def forward(ctx, h, attn_l, attn_r, part: RowBlockPartition, slope, kernels, group, small_group,
+                h_full=None):
         n, K = part.n_local, part.pieces
         h, attn_l, attn_r = h.contiguous(), attn_l.contiguous(), attn_r.contiguous()
         H, Fo = h.shape[1], h.shape[2]
         attn_row, attn_col = kernels.scores_forward(h, attn_l, attn_r)
         ac_full, _ = gather_pieces(attn_col, part, small_group)
-        h_full, works = gather_pieces(h, part, group, async_op=True)
+        if h_full is None:
+            h_full, works = gather_pieces(h, part, group, async_op=True)
+        else:  # the caller projected the gathered inputs itself: nothing to move
+            works = None
         out = h.new_empty((part.max_n, H, Fo))
         if n < part.max_n:
             out[n:].zero_()
@@ -289,23 +299,41 @@ class PartitionedGATFunction(torch.autograd.Function):
             kernels.backward_col_part(slope, cp_c, ri_c, h[:n], attn_col[:n], rp_full, gout_full,
                                       gh, gac_l, c > 0)
         gl, gr = kernels.scores_backward(h[:n], attn_l, attn_r, gar_l, gac_l, gh[:n])
-        return gh, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None
+        return gh, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None, None
 
 
 class PartitionedGATConv(_GATBase):
-    """GATConv (same parameters, same state_dict) on a RowBlockPartition."""
+    """GATConv (same parameters, same state_dict) on a RowBlockPartition.
+
+    ``recompute_projection``: when the layer widens its input (in_feats well below
+    heads*out_feats, e.g. 100 -> 512) it is cheaper to all-gather the narrow inputs and
+    project all nodes on every rank than to all-gather the wide projected features.
+    "auto" does so when the projected row is at least twice as wide as the input row."""
 
     def __init__(self, in_feats, out_feats, num_heads, negative_slope=0.2, kernels=_CudaKernels,
-                 group=None, small_group=None):
+                 group=None, small_group=None, recompute_projection="auto"):
         super().__init__(in_feats, out_feats, num_heads, negative_slope)
         self.kernels = kernels
         self.group = group
         self.small_group = small_group
+        self.recompute_projection = recompute_projection
+
+    def _recompute(self, part) -> bool:
+        if part.world == 1 or part.pieces != 1:
+            return False
+        if self.recompute_projection == "auto":
+            return 2 * self.in_feats <= self.out_feats * self.num_heads
+        return bool(self.recompute_projection)
 
     def forward(self, part: RowBlockPartition, feat):
         h = dense.project(feat, self.W).view(-1, self.num_heads, self.out_feats)
+        h_full = None
+        if self._recompute(part):
+            with torch.no_grad():
+                x_full, _ = gather_pieces(feat.detach(), part, self.group)
+                h_full = dense.project(x_full, self.W.detach()).view(-1, self.num_heads, self.out_feats)
         return PartitionedGATFunction.apply(h, self.attn_l, self.attn_r, part, self.negative_slope,
-                                            self.kernels, self.group, self.small_group)
+                                            self.kernels, self.group, self.small_group, h_full)
 
 
 class PartitionedGAT(nn.Module):

@@ -142,7 +142,7 @@ def test_partition_blocks_cover_graph(pieces):
         assert sum(i.numel() for _, i in p.csc_parts) == int(cp.long()[hi] - cp.long()[lo])
 
 
-def _worker(rank, world, port, results):
+def _worker(rank, world, port, results, pieces=3):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -154,8 +154,11 @@ def _worker(rank, world, port, results):
         cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)
         x = torch.randn(g.n, 12, generator=torch.Generator().manual_seed(1))
         y = torch.randint(0, 5, (g.n,), generator=torch.Generator().manual_seed(2))
-        part = build_partition(g.row_ptr, g.col_ind, cp, ri, rank, world, pieces=3)
+        part = build_partition(g.row_ptr, g.col_ind, cp, ri, rank, world, pieces=pieces)
         model = PartitionedGAT(12, [8], [2], 5, 1, kernels=OracleKernels)
+        if pieces == 1:  # also exercise "gather the inputs, project everywhere"
+            for layer in model.gat_layers:
+                layer.recompute_projection = True
         out = model(part, part.pad_rows(part.local_slice(x)))
         loss = model.loss(part, out, part.local_slice(y))
         loss.backward()
@@ -175,7 +178,8 @@ def _worker(rank, world, port, results):
 
 
 @pytest.mark.timeout(300)
-def test_partitioned_gat_two_ranks_matches_single():
+@pytest.mark.parametrize("pieces", [3, 1])
+def test_partitioned_gat_two_ranks_matches_single(pieces):
     import socket
 
     s = socket.socket()
@@ -184,7 +188,7 @@ def test_partitioned_gat_two_ranks_matches_single():
     s.close()
     mgr = mp.Manager()
     results = mgr.dict()
-    mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, results, pieces), nprocs=2, join=True)
 
     g = power_law_graph(300, 10, seed=3)
     x = torch.randn(g.n, 12, generator=torch.Generator().manual_seed(1))

@@ -35,7 +35,7 @@ def _worker(rank, world, port, results):
         g, x, y = _inputs()
         g = g.to(dev)
         cp, ri, _ = csr2csc(g.row_ptr, g.col_ind)
-        part = build_partition(g.row_ptr, g.col_ind, cp, ri, rank, world)
+        part = build_partition(g.row_ptr, g.col_ind, cp, ri, rank, world, pieces=1 if world == 2 else 3)
         model = PartitionedGAT(20, [16, 16], [4, 4], 6, 1).to(dev)
         out = model(part, part.pad_rows(part.local_slice(x.to(dev))))
         loss = model.loss(part, out, part.local_slice(y.to(dev)))
