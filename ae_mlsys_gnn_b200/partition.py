@@ -308,10 +308,12 @@ class PartitionedGATConv(_GATBase):
     ``recompute_projection``: when the layer widens its input (in_feats well below
     heads*out_feats, e.g. 100 -> 512) it is cheaper to all-gather the narrow inputs and
     project all nodes on every rank than to all-gather the wide projected features.
-    "auto" does so when the projected row is at least twice as wide as the input row."""
+    "auto" does so when the projected row is at least twice as wide as the input row.
+    Off by default: on 8 B200s the 5 GB all-gather it avoids (config 5, layer 1) costs about
+    as much as the redundant 2.45 M x 100 x 512 projection."""
 
     def __init__(self, in_feats, out_feats, num_heads, negative_slope=0.2, kernels=_CudaKernels,
-                 group=None, small_group=None, recompute_projection="auto"):
+                 group=None, small_group=None, recompute_projection=False):
         super().__init__(in_feats, out_feats, num_heads, negative_slope)
         self.kernels = kernels
         self.group = group
