@@ -72,6 +72,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
 
+// Same for an operand stored K-blocked, [K/32][rows][32]: one tile is 16 KB contiguous in
+// global memory whatever the length of the reduction axis.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major tile with 128-byte rows and the
 // 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO), LBO unused (1),
 // descriptor version 1, layout type 2.
@@ -105,7 +114,10 @@ struct GemmParams {
   int M, N, K;
   float* C;
   int64_t ldc;
-  int* status;  // set to 1 by a CTA whose bounded wait expired
+  int* status;           // set to 1 by a CTA whose bounded wait expired
+  int kb_per_split;      // K blocks handled by one blockIdx.z (split-K); >= all of them when grid.z == 1
+  int64_t split_stride;  // floats between the partial outputs of consecutive splits
+  int blocked;           // operands are K-blocked (3-D tensor maps)
 };
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -124,7 +136,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int total_kb = (p.K + BK - 1) / BK;
+  const int kb_begin = blockIdx.z * p.kb_per_split;
+  const int num_kb = max(0, min(p.kb_per_split, total_kb - kb_begin));
+  float* const Cout = p.C + (size_t)blockIdx.z * p.split_stride;
   __shared__ int s_failed;
 
   if (threadIdx.x == 0) {
@@ -149,10 +164,19 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
         if (kb >= kStages && !mbar_wait(empty_bar(s), ((kb / kStages) - 1) & 1)) { s_failed = 1; break; }
         const uint32_t st = base + s * kStageBytes;
         mbar_expect_tx(full_bar(s), kStageBytes);
-        tma_load_2d(st + 0 * kTileBytes, &map_a_hi, kb * BK, m0, full_bar(s));
-        tma_load_2d(st + 1 * kTileBytes, &map_a_lo, kb * BK, m0, full_bar(s));
-        tma_load_2d(st + 2 * kTileBytes, &map_b_hi, kb * BK, n0, full_bar(s));
-        tma_load_2d(st + 3 * kTileBytes, &map_b_lo, kb * BK, n0, full_bar(s));
+        if (p.blocked) {
+          const int kblk = kb_begin + kb;
+          tma_load_3d(st + 0 * kTileBytes, &map_a_hi, 0, m0, kblk, full_bar(s));
+          tma_load_3d(st + 1 * kTileBytes, &map_a_lo, 0, m0, kblk, full_bar(s));
+          tma_load_3d(st + 2 * kTileBytes, &map_b_hi, 0, n0, kblk, full_bar(s));
+          tma_load_3d(st + 3 * kTileBytes, &map_b_lo, 0, n0, kblk, full_bar(s));
+        } else {
+          const int kc = (kb_begin + kb) * BK;
+          tma_load_2d(st + 0 * kTileBytes, &map_a_hi, kc, m0, full_bar(s));
+          tma_load_2d(st + 1 * kTileBytes, &map_a_lo, kc, m0, full_bar(s));
+          tma_load_2d(st + 2 * kTileBytes, &map_b_hi, kc, n0, full_bar(s));
+          tma_load_2d(st + 3 * kTileBytes, &map_b_lo, kc, n0, full_bar(s));
+        }
       }
     }
   } else if (warp == 1) {
@@ -198,8 +222,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
             : "r"(taddr) : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (num_kb == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;  // an empty split contributes nothing
+        }
         if (row < p.M) {
-          float* crow = p.C + (size_t)row * p.ldc + n0 + c * 32;
+          float* crow = Cout + (size_t)row * p.ldc + n0 + c * 32;
           const int ncols = min(32, p.N - (n0 + c * 32));
           if (ncols == 32 && ((uintptr_t)crow & 15) == 0) {
 #pragma unroll
@@ -256,20 +284,55 @@ __global__ void split_kernel(const float* __restrict__ x, int64_t n, float* __re
   }
 }
 
-// B given as K x N row-major -> hi/lo as N x K (K contiguous).
-__global__ void split_transpose_kernel(const float* __restrict__ b, int K, int N, float* __restrict__ hi,
-                                       float* __restrict__ lo) {
+// B given as K x N row-major -> hi/lo as N x K with leading dimension ld >= K (K contiguous).
+// blockIdx.x walks K (which may be millions of rows), blockIdx.y walks N.
+__global__ void split_transpose_kernel(const float* __restrict__ b, int64_t K, int N, int64_t ld,
+                                       float* __restrict__ hi, float* __restrict__ lo) {
   __shared__ float tile[32][33];
-  const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  const int64_t k0 = (int64_t)blockIdx.x * 32;
+  const int n0 = blockIdx.y * 32;
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-    const int k = k0 + r, n = n0 + threadIdx.x;
+    const int64_t k = k0 + r;
+    const int n = n0 + threadIdx.x;
     tile[r][threadIdx.x] = (k < K && n < N) ? b[(size_t)k * N + n] : 0.f;
   }
   __syncthreads();
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-    const int n = n0 + r, k = k0 + threadIdx.x;
-    if (n < N && k < K) split_tf32(tile[threadIdx.x][r], hi[(size_t)n * K + k], lo[(size_t)n * K + k]);
+    const int n = n0 + r;
+    const int64_t k = k0 + threadIdx.x;
+    if (n < N && k < K) split_tf32(tile[threadIdx.x][r], hi[(size_t)n * ld + k], lo[(size_t)n * ld + k]);
   }
+}
+
+// b given as K x N row-major -> hi/lo K-blocked: [ceil(K/32)][N][32] (positions past K zero).
+__global__ void split_transpose_blocked_kernel(const float* __restrict__ b, int64_t K, int N,
+                                               float* __restrict__ hi, float* __restrict__ lo) {
+  __shared__ float tile[32][33];
+  const int64_t k0 = (int64_t)blockIdx.x * 32;
+  const int n0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int64_t k = k0 + r;
+    const int n = n0 + threadIdx.x;
+    tile[r][threadIdx.x] = (k < K && n < N) ? b[(size_t)k * N + n] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int n = n0 + r;
+    if (n < N) {
+      const size_t o = ((size_t)blockIdx.x * N + n) * 32 + threadIdx.x;
+      split_tf32(tile[threadIdx.x][r], hi[o], lo[o]);
+    }
+  }
+}
+
+// out[i] = sum over splits of partial[z][i], in split order (deterministic).
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t count,
+                                     float* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  float s = 0.f;
+  for (int z = 0; z < splits; ++z) s += partial[(size_t)z * count + i];
+  out[i] = s;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -290,14 +353,28 @@ EncodeTiledFn encode_fn() {
 }
 
 // 2-D map over a row-major [rows, cols] fp32 matrix, box = 32 columns x 128 rows.
-bool make_map(CUtensorMap* m, const float* ptr, int64_t rows, int64_t cols) {
+bool make_map(CUtensorMap* m, const float* ptr, int64_t rows, int64_t cols, int64_t ld = 0) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
+  if (ld == 0) ld = cols;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 4};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
   cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
   cuuint32_t estr[2] = {1, 1};
   return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// 3-D map over a K-blocked operand [kblocks][rows][32]: box = 32 x 128 rows x 1 block.
+bool make_map_blocked(CUtensorMap* m, const float* ptr, int64_t rows, int64_t kblocks) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {32, (cuuint64_t)rows, (cuuint64_t)kblocks};
+  cuuint64_t strides[2] = {32 * 4, (cuuint64_t)rows * 32 * 4};
+  cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)BM, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)ptr, dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -350,8 +427,8 @@ extern "C" int gnn_gemm_tf32x3(const float* A, const float* B, int b_is_n_by_k, 
     const int64_t nb = N * K;
     split_kernel<<<(unsigned)((nb / 4 + 256) / 256), 256, 0, stream>>>(B, nb, b_hi, b_lo);
   } else {
-    dim3 grid((unsigned)((N + 31) / 32), (unsigned)((K + 31) / 32));
-    split_transpose_kernel<<<grid, dim3(32, 8), 0, stream>>>(B, (int)K, (int)N, b_hi, b_lo);
+    dim3 grid((unsigned)((K + 31) / 32), (unsigned)((N + 31) / 32));
+    split_transpose_kernel<<<grid, dim3(32, 8), 0, stream>>>(B, K, (int)N, K, b_hi, b_lo);
   }
   CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
   if (!make_map(&ma_hi, a_hi, M, K) || !make_map(&ma_lo, a_lo, M, K) || !make_map(&mb_hi, b_hi, N, K) ||
@@ -364,8 +441,86 @@ extern "C" int gnn_gemm_tf32x3(const float* A, const float* B, int b_is_n_by_k, 
     set_last_error("gnn_gemm_tf32x3: cannot reserve dynamic shared memory");
     return GNN_ERR_CUDA;
   }
-  GemmParams p{(int)M, (int)N, (int)K, C, N, status};
+  GemmParams p{(int)M, (int)N, (int)K, C, N, status, (int)((K + BK - 1) / BK), 0, 0};
   dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)((N + BN - 1) / BN));
   gemm_tf32x3_kernel<<<grid, kGemmThreads, kSmemBytes, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, p);
   return check_launch("gnn_gemm_tf32x3");
+}
+
+// ---- C[K1,N1] = A^T * B with A [M,K1], B [M,N1]: the weight gradient X^T * dH -------------
+// Both operands are transposed (and split) into [K1, M] / [N1, M] so that the reduction
+// dimension M is contiguous, then the same kernel runs with the M axis cut into `splits`
+// ranges (split-K) whose partial tiles are summed in order.
+
+namespace {
+int tn_splits(int64_t K1, int64_t N1, int64_t M) {
+  const int64_t tiles = ((K1 + BM - 1) / BM) * ((N1 + BN - 1) / BN);
+  int64_t s = (2 * 148 + tiles - 1) / tiles;
+  const int64_t total_kb = (M + BK - 1) / BK;
+  if (s > total_kb) s = total_kb;
+  if (s < 1) s = 1;
+  return (int)s;
+}
+}  // namespace
+
+extern "C" int gnn_gemm_tf32x3_tn_workspace_bytes(int64_t M, int64_t K1, int64_t N1, size_t* bytes) {
+  if (!bytes || M < 0 || K1 < 0 || N1 < 0) return bad("gnn_gemm_tf32x3_tn_workspace_bytes: bad argument");
+  const int64_t ld = (M + 31) / 32 * 32;  // K-blocked storage: whole blocks of 32
+  *bytes = 2 * align_up((size_t)K1 * ld * 4, 256) + 2 * align_up((size_t)N1 * ld * 4, 256) +
+           align_up((size_t)tn_splits(K1, N1, M) * K1 * N1 * 4, 256) + 512;
+  return GNN_OK;
+}
+
+extern "C" int gnn_gemm_tf32x3_tn(const float* A, const float* B, float* C, int64_t M, int64_t K1,
+                                  int64_t N1, void* workspace, size_t workspace_bytes, int* status,
+                                  cudaStream_t stream) {
+  if (M < 0 || K1 < 0 || N1 < 0) return bad("gnn_gemm_tf32x3_tn: negative size");
+  if (K1 == 0 || N1 == 0) return GNN_OK;
+  if (!C || !status || (M && (!A || !B))) return bad("gnn_gemm_tf32x3_tn: null pointer");
+  if (M >= (1LL << 31) || K1 >= (1LL << 31) || N1 >= (1LL << 31)) return bad("gnn_gemm_tf32x3_tn: size exceeds int32");
+  size_t need = 0;
+  gnn_gemm_tf32x3_tn_workspace_bytes(M, K1, N1, &need);
+  if (!workspace || workspace_bytes < need) {
+    set_last_error("gnn_gemm_tf32x3_tn: workspace too small");
+    return GNN_ERR_WORKSPACE;
+  }
+  if (M == 0) {
+    cudaMemsetAsync(C, 0, (size_t)K1 * N1 * 4, stream);
+    return check_launch("gnn_gemm_tf32x3_tn");
+  }
+  const int64_t ld = (M + 31) / 32 * 32;
+  const int64_t kblocks = ld / 32;
+  char* w = (char*)align_up((uintptr_t)workspace, 256);
+  const size_t ab = align_up((size_t)K1 * ld * 4, 256), bb = align_up((size_t)N1 * ld * 4, 256);
+  float* a_hi = (float*)w;
+  float* a_lo = (float*)(w + ab);
+  float* b_hi = (float*)(w + 2 * ab);
+  float* b_lo = (float*)(w + 2 * ab + bb);
+  float* partial = (float*)(w + 2 * ab + 2 * bb);
+  {
+    dim3 ga((unsigned)((M + 31) / 32), (unsigned)((K1 + 31) / 32));
+    split_transpose_blocked_kernel<<<ga, dim3(32, 8), 0, stream>>>(A, M, (int)K1, a_hi, a_lo);
+    dim3 gb((unsigned)((M + 31) / 32), (unsigned)((N1 + 31) / 32));
+    split_transpose_blocked_kernel<<<gb, dim3(32, 8), 0, stream>>>(B, M, (int)N1, b_hi, b_lo);
+  }
+  CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+  if (!make_map_blocked(&ma_hi, a_hi, K1, kblocks) || !make_map_blocked(&ma_lo, a_lo, K1, kblocks) ||
+      !make_map_blocked(&mb_hi, b_hi, N1, kblocks) || !make_map_blocked(&mb_lo, b_lo, N1, kblocks)) {
+    set_last_error("gnn_gemm_tf32x3_tn: cuTensorMapEncodeTiled failed");
+    return GNN_ERR_CUDA;
+  }
+  if (cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) !=
+      cudaSuccess) {
+    set_last_error("gnn_gemm_tf32x3_tn: cannot reserve dynamic shared memory");
+    return GNN_ERR_CUDA;
+  }
+  const int splits = tn_splits(K1, N1, M);
+  const int total_kb = (int)((M + BK - 1) / BK);
+  const int per = (total_kb + splits - 1) / splits;
+  GemmParams p{(int)K1, (int)N1, (int)M, partial, N1, status, per, K1 * N1, 1};
+  dim3 grid((unsigned)((K1 + BM - 1) / BM), (unsigned)((N1 + BN - 1) / BN), (unsigned)splits);
+  gemm_tf32x3_kernel<<<grid, kGemmThreads, kSmemBytes, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, p);
+  const int64_t count = K1 * N1;
+  splitk_reduce_kernel<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(partial, splits, count, C);
+  return check_launch("gnn_gemm_tf32x3_tn");
 }

@@ -61,6 +61,28 @@ def gemm(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool) -> torch.Tensor:
     return out
 
 
+def gemm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a^T @ b for a (M,K1), b (M,N1): the weight gradient of a projection."""
+    dev = a.device
+    capi.require(a, F32, "a", 2)
+    capi.require(b, F32, "b", 2, dev)
+    M, K1 = a.shape
+    if b.shape[0] != M:
+        raise ValueError("a and b must have the same number of rows")
+    N1 = b.shape[1]
+    out = torch.empty((K1, N1), dtype=F32, device=dev)
+    nbytes = capi.workspace_bytes("gnn_gemm_tf32x3_tn_workspace_bytes", M, K1, N1)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gemm_tf32x3_tn", capi.ptr(a), capi.ptr(b), capi.ptr(out), M, K1, N1, capi.ptr(ws),
+                  ws.numel(), capi.ptr(_status_word(dev)), capi.stream_ptr(dev))
+    return out
+
+
+# below this many rows the transposes + split-K launch cost more than the framework GEMM
+TN_MIN_ROWS = 4096
+
+
 class _MatmulFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, w_is_out_by_in):
@@ -83,7 +105,10 @@ class _MatmulFunction(torch.autograd.Function):
             else:
                 gx = g @ (w if ctx.w_is_out_by_in else w.t())
         if ctx.needs_input_grad[1]:
-            gw = (g.t() @ x) if ctx.w_is_out_by_in else (x.t() @ g)
+            if enabled and x.shape[0] >= TN_MIN_ROWS:
+                gw = gemm_tn(g, x) if ctx.w_is_out_by_in else gemm_tn(x, g)
+            else:
+                gw = (g.t() @ x) if ctx.w_is_out_by_in else (x.t() @ g)
         return gx, gw, None
 
 

@@ -232,6 +232,13 @@ int gnn_gemm_tf32x3(const float* A, const float* B, int b_is_n_by_k, float* C, i
                     int64_t K, void* workspace, size_t workspace_bytes, int* status,
                     cudaStream_t stream);
 
+/* C[K1,N1] = A^T * B with A [M,K1], B [M,N1] (the weight gradient X^T * dH of a projection;
+ * autograd's MmBackward in the reference, a cuBLAS SGEMM).  Same 3xTF32 tcgen05 kernel, the
+ * reduction axis M cut into ranges whose partial tiles are summed in a fixed order. */
+int gnn_gemm_tf32x3_tn_workspace_bytes(int64_t M, int64_t K1, int64_t N1, size_t* bytes);
+int gnn_gemm_tf32x3_tn(const float* A, const float* B, float* C, int64_t M, int64_t K1, int64_t N1,
+                       void* workspace, size_t workspace_bytes, int* status, cudaStream_t stream);
+
 /* ---- unfused operators that share the API ------------------------------------------------
  * gnn_mhspmm: mhspmm.mhspmm (src/spmm/mhspmm.cu:4-66) and, with H = 1, the
  * single-head csr_spmm / csr_spmm_no_edge_value that operators/spmm.py:35-41

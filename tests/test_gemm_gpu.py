@@ -58,3 +58,29 @@ def test_matmul_autograd_and_fallback(cuda):
         out = dense.linear(x.to(cuda), lin_w.to(cuda))
         assert_close(out, x.double() @ lin_w.double().t(), "linear", scale_atol=True)
     dense.check_status()
+
+
+@pytest.mark.parametrize("M,K1,N1", [(5000, 100, 512), (4099, 512, 47), (70001, 64, 64), (33, 8, 130), (1, 5, 3)])
+def test_gemm_tn_weight_gradient(cuda, M, K1, N1):
+    from ae_mlsys_gnn_b200.operators import dense
+
+    gen = torch.Generator().manual_seed(M + K1)
+    a, b = torch.randn(M, K1, generator=gen), torch.randn(M, N1, generator=gen)
+    out = dense.gemm_tn(a.to(cuda), b.to(cuda))
+    dense.check_status()
+    assert_close(out, a.double().t() @ b.double(), f"gemm_tn {M}x{K1}x{N1}", scale_atol=True)
+
+
+def test_matmul_autograd_large_uses_tensor_core_weight_gradient(cuda):
+    from ae_mlsys_gnn_b200.operators import dense
+
+    gen = torch.Generator().manual_seed(11)
+    x, w, g = torch.randn(9000, 64, generator=gen), torch.randn(64, 96, generator=gen), torch.randn(9000, 96, generator=gen)
+    xd, wd = x.to(cuda).requires_grad_(True), w.to(cuda).requires_grad_(True)
+    dense.project(xd, wd).backward(g.to(cuda))
+    dense.check_status()
+    assert_close(wd.grad, x.double().t() @ g.double(), "grad_w", scale_atol=True)
+    assert_close(xd.grad, g.double() @ w.double().t(), "grad_x", scale_atol=True)
+    lw = torch.randn(96, 64, generator=gen).to(cuda).requires_grad_(True)
+    dense.linear(x.to(cuda), lw).backward(g.to(cuda))
+    assert_close(lw.grad, g.double().t() @ x.double(), "linear grad_w", scale_atol=True)
