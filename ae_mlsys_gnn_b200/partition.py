@@ -374,7 +374,8 @@ class PartitionedGAT(nn.Module):
         divided by the global node count), so that summing gradients over ranks gives
         the single-GPU gradient."""
         n = part.n_local
-        return F.cross_entropy(logits[:n], labels_local, reduction="sum") / part.n_global
+        picked = F.log_softmax(logits[:n], dim=1).gather(1, labels_local.view(-1, 1))
+        return -picked.sum() / part.n_global
 
     def all_reduce_grads(self, world: int):
         if world == 1:
