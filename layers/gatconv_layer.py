@@ -1,2 +1,4 @@
+"""Reference-style import path for ae_mlsys_gnn_b200.layers.gatconv_layer."""
 from ae_mlsys_gnn_b200.layers import gatconv_layer as _impl
-globals().update({k: v for k, v in vars(_impl).items() if not k.startswith('__')})
+
+globals().update({k: v for k, v in vars(_impl).items() if not k.startswith("__")})

@@ -1,3 +1,4 @@
-from ae_mlsys_gnn_b200.operators.edge_softmax import *  # noqa: F401,F403
+"""Reference-style import path for ae_mlsys_gnn_b200.operators.edge_softmax."""
 from ae_mlsys_gnn_b200.operators import edge_softmax as _impl
-globals().update({k: v for k, v in vars(_impl).items() if not k.startswith('__')})
+
+globals().update({k: v for k, v in vars(_impl).items() if not k.startswith("__")})
