@@ -156,22 +156,27 @@ void launch_row(const GatBwdRowParams& p, cudaStream_t stream) {
     gat_bwd_row_fixup_kernel<HP><<<bblocks + sblocks, kThreadsPerCta, 0, stream>>>(p, bblocks);
 }
 
+template <int HP, int Q, bool VEC, bool ACC>
+void launch_col_main(const GatBwdColParams& p, cudaStream_t stream) {
+  const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
+  if constexpr (VEC) {
+    if (p.width == 128 * Q) {  // every slot fully used: heads are aligned with the tile slots
+      if constexpr (Q <= HP) {
+        if (p.F == 128) { gat_bwd_col_kernel<HP, Q, VEC, 1, ACC><<<blocks, kThreadsPerCta, 0, stream>>>(p); return; }
+      }
+      if constexpr (2 * Q <= HP) {
+        if (p.F == 64) { gat_bwd_col_kernel<HP, Q, VEC, 2, ACC><<<blocks, kThreadsPerCta, 0, stream>>>(p); return; }
+      }
+    }
+  }
+  gat_bwd_col_kernel<HP, Q, VEC, 0, ACC><<<blocks, kThreadsPerCta, 0, stream>>>(p);
+}
+
 template <int HP, int Q, bool VEC>
 void launch_col(const GatBwdColParams& p, cudaStream_t stream) {
   if (p.g.num_chunks > 0) {
-    const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
-    bool done = false;
-    if constexpr (VEC) {
-      if (p.width == 128 * Q) {  // every slot fully used: heads are aligned with the tile slots
-        if constexpr (Q <= HP) {
-          if (p.F == 128) { gat_bwd_col_kernel<HP, Q, VEC, 1><<<blocks, kThreadsPerCta, 0, stream>>>(p); done = true; }
-        }
-        if constexpr (2 * Q <= HP) {
-          if (p.F == 64) { gat_bwd_col_kernel<HP, Q, VEC, 2><<<blocks, kThreadsPerCta, 0, stream>>>(p); done = true; }
-        }
-      }
-    }
-    if (!done) gat_bwd_col_kernel<HP, Q, VEC><<<blocks, kThreadsPerCta, 0, stream>>>(p);
+    if (p.accumulate) launch_col_main<HP, Q, VEC, true>(p, stream);
+    else launch_col_main<HP, Q, VEC, false>(p, stream);
   }
   const int nbound = p.g.num_chunks > 1 ? p.g.num_chunks - 1 : 0;
   const int bblocks = (nbound + kWarpsPerCta - 1) / kWarpsPerCta;

@@ -248,7 +248,10 @@ struct GatBwdColParams {
   int accumulate = 0;      // 1: add to the grad_feat / grad_attn_col left by earlier launches
 };
 
-template <int HP, int Q, bool VEC, int HPS = 0>
+// ACC is p.accumulate as a compile-time constant: the plain launch keeps the exact code of
+// a kernel without the read-modify-write epilogue (the run-time branch alone changed the
+// register allocation of the gather loop and halved its throughput for F = 64).
+template <int HP, int Q, bool VEC, int HPS = 0, bool ACC = false>
 __global__ void __launch_bounds__(kThreadsPerCta)
 gat_bwd_col_kernel(GatBwdColParams p) {
   static_assert(HPS == 0 || Q * HPS <= HP, "slot-aligned heads need Q * HPS <= HP");
@@ -353,7 +356,7 @@ gat_bwd_col_kernel(GatBwdColParams p) {
     constexpr int LPH = 32 / HP;
     if (first && last) {
       float* grow = p.grad_feat + (size_t)s * p.ld_gfeat;
-      if (p.accumulate) {
+      if constexpr (ACC) {
         float old[Q][VW];
         t.load_rw(grow, lane, old);
 #pragma unroll
@@ -364,7 +367,7 @@ gat_bwd_col_kernel(GatBwdColParams p) {
       t.store(grow, lane, acc);
       if ((lane & (LPH - 1)) == 0 && lane / LPH < p.H) {
         float* ga = p.grad_attn_seg + (size_t)s * p.ld_attn + lane / LPH;
-        *ga = p.accumulate ? *ga + B[0] : B[0];
+        if constexpr (ACC) *ga += B[0]; else *ga = B[0];
       }
     } else {
       float* slot = p.scratch + slot_index(chunk_id, first) * p.slot_stride;

@@ -482,8 +482,9 @@ def main():
     # ---- roofline of the dominant entry point (rank 0's view) ------------------------------
     peak, peak_kind = measured_peak_gbs()
     roof = None
-    if per:
-        name = max(per, key=lambda k: per[k]["ms"])
+    hbm_bound = {k: v for k, v in per.items() if v["bytes"] > 0}  # the GEMM entries carry no byte count
+    if hbm_bound:
+        name = max(hbm_bound, key=lambda k: hbm_bound[k]["ms"])
         p = per[name]
         achieved = p["bytes"] / (p["ms"] * 1e-3) / 1e9 if p["ms"] > 0 else 0.0
         roof = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak,
