@@ -12,7 +12,45 @@ import json
 
 import torch
 
-OPS = ("gat_fwd", "gat_bwd_row", "gat_bwd_col", "csr2csc", "edgeconv_fwd", "gmm_fwd", "mhspmm", "mhsddmm")
+OPS = ("gat_fwd", "gat_bwd_row", "gat_bwd_col", "csr2csc", "edgeconv_fwd", "gmm_fwd", "mhspmm", "mhsddmm",
+       "gemm", "gemm_tn")
+
+
+def dense_main(a):
+    """Projection GEMM x (nodes, in) @ w (in, out), or its weight gradient x^T @ g."""
+    import importlib
+
+    D = importlib.import_module(".operators.dense", __package__)
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(a.seed)
+    M, K, N = a.nodes, a.in_dim, a.out_dim
+    x = torch.randn(M, K, device=dev, generator=gen)
+    w = torch.randn(K, N, device=dev, generator=gen)
+    g = torch.randn(M, N, device=dev, generator=gen)
+    if a.op == "gemm":
+        fn = lambda: D.gemm(x, w, False)
+        nbytes = 4.0 * (M * K + K * N + M * N)
+    else:
+        fn = lambda: D.gemm_tn(x, g)
+        nbytes = 4.0 * (M * K + M * N + K * N)
+    flush = torch.empty(64 * 1024 * 1024, device=dev)
+    for _ in range(a.warmup):
+        fn()
+    times = []
+    for _ in range(a.iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    D.check_status()
+    times.sort()
+    med = times[len(times) // 2]
+    print(json.dumps({"op": a.op, "nodes": M, "in_dim": K, "out_dim": N, "ms_median": med, "ms_min": times[0],
+                      "algorithmic_gb": nbytes / 1e9, "gbs": nbytes / (med * 1e-3) / 1e9,
+                      "tflops_fp32_equiv": 2.0 * M * K * N / (med * 1e-3) / 1e12}))
 
 
 def main():
@@ -27,7 +65,11 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--in-dim", type=int, default=512, help="gemm / gemm_tn: input width of the projection")
+    ap.add_argument("--out-dim", type=int, default=512, help="gemm / gemm_tn: output width of the projection")
     a = ap.parse_args()
+    if a.op in ("gemm", "gemm_tn"):
+        return dense_main(a)
 
     from . import graphs as G
     import importlib

@@ -3,8 +3,8 @@ reference, which calls torch.matmul / nn.Linear: layers/gatconv_layer.py:50,
 layers/edgeconv_layer.py:37-38, layers/gmmconv_layer.py:68).
 
 ``matmul_tf32x3(x, w)`` computes ``x @ w`` with the error-compensated 3xTF32 tcgen05
-kernel (fp32-level accuracy); its backward uses the same kernel for grad_x and the
-framework GEMM for the small grad_w.  ``project`` picks it whenever the shape is
+kernel (fp32-level accuracy); its backward uses the same kernel for grad_x and, with the
+node axis as the reduction axis, for grad_w.  ``project`` picks it whenever the shape is
 supported and falls back to ``torch.matmul`` (cuBLAS fp32) otherwise.
 """
 from __future__ import annotations
@@ -105,7 +105,7 @@ class _MatmulFunction(torch.autograd.Function):
             else:
                 gx = g @ (w if ctx.w_is_out_by_in else w.t())
         if ctx.needs_input_grad[1]:
-            if enabled and x.shape[0] >= TN_MIN_ROWS:
+            if enabled and x.shape[0] >= TN_MIN_ROWS and x.data_ptr() % 16 == 0 and g.data_ptr() % 16 == 0:
                 gw = gemm_tn(g, x) if ctx.w_is_out_by_in else gemm_tn(x, g)
             else:
                 gw = (g.t() @ x) if ctx.w_is_out_by_in else (x.t() @ g)

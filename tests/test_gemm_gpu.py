@@ -8,7 +8,9 @@ from tests.util import assert_close
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(128, 128, 32), (1000, 512, 100), (300, 47, 512), (4097, 512, 512), (130, 70, 36), (5, 3, 4),
-          (257, 256, 64), (2048, 64, 128), (999, 41, 256)]
+          (257, 256, 64), (2048, 64, 128), (999, 41, 256),
+          (40000, 512, 64),   # more output tiles than SMs: every CTA walks several tiles
+          (150 * 128 + 5, 200, 96)]
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -60,7 +62,8 @@ def test_matmul_autograd_and_fallback(cuda):
     dense.check_status()
 
 
-@pytest.mark.parametrize("M,K1,N1", [(5000, 100, 512), (4099, 512, 47), (70001, 64, 64), (33, 8, 130), (1, 5, 3)])
+@pytest.mark.parametrize("M,K1,N1", [(5000, 100, 512), (4099, 512, 47), (70001, 64, 64), (33, 8, 130), (1, 5, 3),
+                                     (300000, 512, 512), (9000, 47, 512), (64, 256, 384)])
 def test_gemm_tn_weight_gradient(cuda, M, K1, N1):
     from ae_mlsys_gnn_b200.operators import dense
 
@@ -84,3 +87,22 @@ def test_matmul_autograd_large_uses_tensor_core_weight_gradient(cuda):
     lw = torch.randn(96, 64, generator=gen).to(cuda).requires_grad_(True)
     dense.linear(x.to(cuda), lw).backward(g.to(cuda))
     assert_close(lw.grad, g.double().t() @ x.double(), "linear grad_w", scale_atol=True)
+
+
+def test_gemm_tn_long_reduction(cuda):
+    """Millions of rows: the tensor core truncates when it adds into its accumulator, so the
+    kernel must not leave one accumulator running over the whole reduction (an unbroken
+    chain comes out low by several 1e-4 of the value).  fp64 reference on the device."""
+    from ae_mlsys_gnn_b200.operators import dense
+
+    gen = torch.Generator(device=cuda).manual_seed(3)
+    M = 2_000_003
+    a = torch.randn(M, 128, device=cuda, generator=gen)
+    b = torch.randn(M, 256, device=cuda, generator=gen).abs_()  # same-sign products in half of the rows
+    a[: M // 2].abs_()
+    out = dense.gemm_tn(a, b)
+    dense.check_status()
+    exp = a.double().t() @ b.double()
+    assert_close(out, exp, "gemm_tn long reduction", scale_atol=True)
+    bias = ((out.double() - exp) / exp)[exp.abs() > 0.1 * exp.abs().max()].mean().item()
+    assert abs(bias) < 3e-5, f"systematic relative error {bias:.2e}"
