@@ -156,27 +156,32 @@ void launch_row(const GatBwdRowParams& p, cudaStream_t stream) {
     gat_bwd_row_fixup_kernel<HP><<<bblocks + sblocks, kThreadsPerCta, 0, stream>>>(p, bblocks);
 }
 
-template <int HP, int Q, bool VEC, bool ACC>
+template <int HP, int Q, bool VEC, bool ACC, bool EDGES>
 void launch_col_main(const GatBwdColParams& p, cudaStream_t stream) {
   const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
   if constexpr (VEC) {
     if (p.width == 128 * Q) {  // every slot fully used: heads are aligned with the tile slots
       if constexpr (Q <= HP) {
-        if (p.F == 128) { gat_bwd_col_kernel<HP, Q, VEC, 1, ACC><<<blocks, kThreadsPerCta, 0, stream>>>(p); return; }
+        if (p.F == 128) { gat_bwd_col_kernel<HP, Q, VEC, 1, ACC, EDGES><<<blocks, kThreadsPerCta, 0, stream>>>(p); return; }
       }
       if constexpr (2 * Q <= HP) {
-        if (p.F == 64) { gat_bwd_col_kernel<HP, Q, VEC, 2, ACC><<<blocks, kThreadsPerCta, 0, stream>>>(p); return; }
+        if (p.F == 64) { gat_bwd_col_kernel<HP, Q, VEC, 2, ACC, EDGES><<<blocks, kThreadsPerCta, 0, stream>>>(p); return; }
       }
     }
   }
-  gat_bwd_col_kernel<HP, Q, VEC, 0, ACC><<<blocks, kThreadsPerCta, 0, stream>>>(p);
+  gat_bwd_col_kernel<HP, Q, VEC, 0, ACC, EDGES><<<blocks, kThreadsPerCta, 0, stream>>>(p);
 }
 
 template <int HP, int Q, bool VEC>
 void launch_col(const GatBwdColParams& p, cudaStream_t stream) {
   if (p.g.num_chunks > 0) {
-    if (p.accumulate) launch_col_main<HP, Q, VEC, true>(p, stream);
-    else launch_col_main<HP, Q, VEC, false>(p, stream);
+    if (p.edge_grad) {
+      if (p.accumulate) launch_col_main<HP, Q, VEC, true, true>(p, stream);
+      else launch_col_main<HP, Q, VEC, false, true>(p, stream);
+    } else {
+      if (p.accumulate) launch_col_main<HP, Q, VEC, true, false>(p, stream);
+      else launch_col_main<HP, Q, VEC, false, false>(p, stream);
+    }
   }
   const int nbound = p.g.num_chunks > 1 ? p.g.num_chunks - 1 : 0;
   const int bblocks = (nbound + kWarpsPerCta - 1) / kWarpsPerCta;
@@ -272,6 +277,18 @@ extern "C" int gnn_gat_bwd_col_part(const int* col_ptr, const int* row_ind, int6
                                     float negative_slope, float* grad_feat, float* grad_attn_col,
                                     int accumulate, void* workspace, size_t workspace_bytes,
                                     cudaStream_t stream) {
+  return gnn_gat_bwd_col_edges(col_ptr, row_ind, n_cols, nnz, in_feat, attn_col, rowpack, grad_out, H, F,
+                               negative_slope, grad_feat, grad_attn_col, nullptr, accumulate, workspace,
+                               workspace_bytes, stream);
+}
+
+extern "C" int gnn_gat_bwd_col_edges(const int* col_ptr, const int* row_ind, int64_t n_cols,
+                                     int64_t nnz, const float* in_feat, const float* attn_col,
+                                     const float* rowpack, const float* grad_out, int H, int F,
+                                     float negative_slope, float* grad_feat, float* grad_attn_col,
+                                     float* edge_grad, int accumulate, void* workspace,
+                                     size_t workspace_bytes, cudaStream_t stream) {
+  if (edge_grad && !aligned16(edge_grad)) return bad("gnn_gat_bwd_col: edge_grad must be 16-byte aligned");
   if (n_cols < 0 || nnz < 0 || H <= 0 || F <= 0) return bad("gnn_gat_bwd_col: negative size");
   if (n_cols > INT32_MAX - 1 || nnz > INT32_MAX - 4096) return bad("gnn_gat_bwd_col: size exceeds int32 indexing");
   if (n_cols == 0) return GNN_OK;
@@ -305,6 +322,7 @@ extern "C" int gnn_gat_bwd_col_part(const int* col_ptr, const int* row_ind, int6
   p.aux_off = round_up4((int)HF);
   p.slot_stride = p.aux_off + round_up4(2 * pl.HP);
   p.accumulate = accumulate ? 1 : 0;
+  p.edge_grad = edge_grad;
   bool ok = dispatch_tile(pl.HP, (int)HF, pl.vec, [&](auto hp, auto q, auto v) {
     launch_col<decltype(hp)::value, decltype(q)::value, decltype(v)::value>(p, stream);
   });

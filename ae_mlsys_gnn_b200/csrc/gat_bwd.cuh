@@ -246,19 +246,28 @@ struct GatBwdColParams {
   int slot_stride;
   int aux_off;
   int accumulate = 0;      // 1: add to the grad_feat / grad_attn_col left by earlier launches
+  float* edge_grad = nullptr;  // [nnz][H], position order of this CSC: gradient of every edge logit
 };
 
 // ACC is p.accumulate as a compile-time constant: the plain launch keeps the exact code of
 // a kernel without the read-modify-write epilogue (the run-time branch alone changed the
 // register allocation of the gather loop and halved its throughput for F = 64).
-template <int HP, int Q, bool VEC, int HPS = 0, bool ACC = false>
-__global__ void __launch_bounds__(kThreadsPerCta)
+// EDGES: also store the gradient of every edge logit, a(r,c) d(r,c) (<G[r],h[c]> - S[r]),
+// from which the caller sums grad_attn_row without a second gather pass.
+template <int Q, bool VEC>
+constexpr bool kColPipelined = Q * (VEC ? 4 : 1) <= 8;  // a row is at most 8 registers per lane
+
+// (Two CTAs per SM are requested only for the pipelined narrow tiles; the widest tile gets
+// there by itself, and with the explicit limit its gather loop is scheduled into spills.)
+template <int HP, int Q, bool VEC, int HPS = 0, bool ACC = false, bool EDGES = false>
+__global__ void __launch_bounds__(kThreadsPerCta, kColPipelined<Q, VEC> ? 2 : 0)
 gat_bwd_col_kernel(GatBwdColParams p) {
   static_assert(HPS == 0 || Q * HPS <= HP, "slot-aligned heads need Q * HPS <= HP");
   constexpr int VW = VEC ? 4 : 1;
   constexpr int U0 = Unroll<Q, VEC>::U;
   constexpr int U = (U0 * HP > 32) ? 32 / HP : U0;
   constexpr int V = U * HP;
+  constexpr bool PIPE = kColPipelined<Q, VEC> && U == Unroll<Q, VEC>::U;  // both row buffers fit beside the accumulators
   __shared__ int cs_all[kWarpsPerCta][32];
   __shared__ float ws_all[kWarpsPerCta][32 * HP];
   __shared__ float gs_all[kWarpsPerCta][32 * HP];
@@ -310,6 +319,58 @@ gat_bwd_col_kernel(GatBwdColParams p) {
       __syncwarp();
       const int nb = min(32, b - base);
       const int nbr = (nb + U - 1) / U * U;
+      if constexpr (PIPE) {
+        // Two register buffers: the rows of the next U edges are requested before the
+        // current U are consumed (narrow tiles leave the registers for it; without it the
+        // throughput of this loop depended on what else the kernel variant contained).
+        auto load_rows = [&](float (&v)[U][Q][VW], int jj) {
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            t.load(p.gout + (size_t)cs[jj + u] * p.ld_gout, lane, v[u]);
+        };
+        auto process = [&](float (&v)[U][Q][VW], int jj) {
+          float pv[V];
+#pragma unroll
+          for (int i = 0; i < V; ++i) pv[i] = 0.f;
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+#pragma unroll
+            for (int q = 0; q < Q; ++q) {
+              const float wq = ws[(jj + u) * HP + (HPS > 0 ? q * HPS + lane_head : t.head[q])];
+              float d = 0.f;
+#pragma unroll
+              for (int i = 0; i < VW; ++i) {
+                acc[q][i] = fmaf(wq, v[u][q][i], acc[q][i]);
+                d = fmaf(fq[q][i], v[u][q][i], d);
+              }
+              if constexpr (HPS > 0) {
+#pragma unroll
+                for (int k = 0; k < HPS; ++k) pv[u * HP + q * HPS + k] = (lane_head == k) ? d : 0.f;
+              } else {
+#pragma unroll
+                for (int h = 0; h < HP; ++h)
+                  if (t.head[q] == h) pv[u * HP + h] += d;
+              }
+            }
+          }
+          warp_multi_sum<V>(pv, lane);
+          if ((lane & (32 / V - 1)) == 0) gs[jj * HP + lane / (32 / V)] = pv[0];
+        };
+        float va[U][Q][VW], vb[U][Q][VW];
+        load_rows(va, 0);
+#pragma unroll 1
+        for (int jj = 0; jj < nbr; jj += 2 * U) {
+          const bool more = jj + U < nbr;
+          if (more) load_rows(vb, jj + U);
+          process(va, jj);
+          if (more) {
+            if (jj + 2 * U < nbr) load_rows(va, jj + 2 * U);
+            process(vb, jj + U);
+          }
+        }
+      } else
+      // (the wide tiles keep the plain loop, written out: their register allocation is at
+      // the two-CTA limit and changes with the form of this loop)
 #pragma unroll 1
       for (int jj = 0; jj < nbr; jj += U) {
         float v[U][Q][VW];
@@ -349,6 +410,19 @@ gat_bwd_col_kernel(GatBwdColParams p) {
         for (int h = 0; h < HP; ++h) {
           const float gd = gs[lane * HP + h];
           B[h] = fmaf(al[h] * dd[h], gd - sr[h], B[h]);
+        }
+        if constexpr (EDGES) {
+          float ge[HP];
+#pragma unroll
+          for (int h = 0; h < HP; ++h) ge[h] = al[h] * dd[h] * (gs[lane * HP + h] - sr[h]);
+          float* eg = p.edge_grad + (size_t)e * p.H;
+          if (HP == 4 && p.H == 4) {
+            *reinterpret_cast<float4*>(eg) = make_float4(ge[0], ge[1], ge[2], ge[3]);
+          } else {
+#pragma unroll
+            for (int h = 0; h < HP; ++h)
+              if (h < p.H) eg[h] = ge[h];
+          }
         }
       }
     }

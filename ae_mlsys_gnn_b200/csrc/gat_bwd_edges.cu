@@ -1,0 +1,229 @@
+// One-gather backward of the fused GAT.
+//
+// The two-pass backward (gat_bwd.cuh) gathers h[c] over all edges once more just to form
+//     S[r,h] = sum_j a_j <G[r,h,:], h[c_j,h,:]>      and      grad_attn_row.
+// With the forward output out[r,h,:] = sum_j a_j h[c_j,h,:] at hand, S needs no edge at all:
+//     S[r,h] = <G[r,h,:], out[r,h,:]>.
+// The column pass (one gather of G[r] over the CSC) then knows the gradient of every edge
+// logit, stores it (E x H floats, CSC order: gnn_gat_bwd_col_edges) while it forms grad_feat
+// and grad_attn_col, and grad_attn_row[r] is the sum of those values over row r's edges --
+// a pass over E x H scalars instead of E x H x F features.  The map from a CSR edge to its
+// position in the CSC is the inverse of csr2csc's permutation, a property of the graph.
+//
+//   gnn_gat_bwd_pack      rowpack[r] = {attn_row[r], max[r], 1/sum[r], S[r]}   (node-wise)
+//   gnn_gat_bwd_row_sum   grad_attn_row[r,h] = sum over CSR edges e of row r of
+//                         edge_grad[csr_pos[e], h]   (edge-balanced, deterministic)
+//   gnn_invert_permutation
+//
+// Replaces, for callers that keep `out`, the row pass that stands in for the reference's
+// mhspmm_backward_kernel + mhsddmm (src/fused_gat/fused_gat_SM.cu:560-607, :656-732).
+#include "common.cuh"
+
+using namespace gnn;
+
+namespace {
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+int bad(const char* m) {
+  set_last_error(m);
+  return GNN_ERR_INVALID_ARG;
+}
+
+__global__ void invert_permutation_kernel(const int* __restrict__ perm, int64_t n, int* __restrict__ inv) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) inv[perm[i]] = (int)i;
+}
+
+// One warp per row.  VEC: H*F is a multiple of 4 and both matrices are 16-byte aligned.
+template <bool VEC>
+__global__ void __launch_bounds__(kThreadsPerCta)
+pack_kernel(int64_t n_rows, const float* __restrict__ out, const float* __restrict__ gout,
+            const float* __restrict__ attn_row, const float* __restrict__ edge_max,
+            const float* __restrict__ edge_sum, int H, int F, float* __restrict__ rowpack) {
+  const int lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const float* o = out + (size_t)r * H * F;
+  const float* g = gout + (size_t)r * H * F;
+  float* rp = rowpack + (size_t)r * 4 * H;
+  for (int h = 0; h < H; ++h) {
+    float acc = 0.f;
+    if (VEC && F % 4 == 0) {
+      const float4* o4 = reinterpret_cast<const float4*>(o + (size_t)h * F);
+      const float4* g4 = reinterpret_cast<const float4*>(g + (size_t)h * F);
+      for (int i = lane; i < F / 4; i += 32) {
+        const float4 a = __ldg(o4 + i), b = __ldg(g4 + i);
+        acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc);
+        acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+      }
+    } else {
+      for (int i = lane; i < F; i += 32) acc = fmaf(__ldg(o + (size_t)h * F + i), __ldg(g + (size_t)h * F + i), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      const float sum = __ldg(edge_sum + (size_t)r * H + h);
+      const bool empty = !(sum > 0.f);  // a row without edges: same record as the two-pass backward writes
+      rp[h] = __ldg(attn_row + (size_t)r * H + h);
+      rp[H + h] = empty ? kNegBig : __ldg(edge_max + (size_t)r * H + h);
+      rp[2 * H + h] = empty ? 0.f : 1.f / sum;
+      rp[3 * H + h] = empty ? 0.f : acc;
+    }
+  }
+}
+
+struct RowSumParams {
+  ChunkGeom g;             // CSR: ptr = row_ptr, idx = csr_pos (position of the edge in the CSC)
+  const float* edge_grad;  // [nnz][H], CSC position order
+  int H;
+  float* grad_attn_row;    // [nseg][H]
+  float* scratch;          // 2 * num_chunks slots of HP floats
+};
+
+template <int HP>
+__global__ void __launch_bounds__(kThreadsPerCta)
+row_sum_kernel(RowSumParams p) {
+  const int lane = threadIdx.x & 31;
+  const int chunk_id = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (chunk_id >= p.g.num_chunks) return;
+  for_each_piece(p.g, chunk_id, [&](int s, int a, int b, bool first, bool last) {
+    float acc[HP];
+#pragma unroll
+    for (int h = 0; h < HP; ++h) acc[h] = 0.f;
+    for (int e = a + lane; e < b; e += 32) {
+      const float* eg = p.edge_grad + (size_t)__ldg(p.g.idx + e) * p.H;
+      if (HP == 4 && p.H == 4) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(eg));
+        acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+      } else {
+#pragma unroll
+        for (int h = 0; h < HP; ++h)
+          if (h < p.H) acc[h] += __ldg(eg + h);
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < HP; ++h) acc[h] = warp_sum(acc[h]);
+    if (lane == 0) {
+      float* dst = (first && last) ? p.grad_attn_row + (size_t)s * p.H
+                                   : p.scratch + slot_index(chunk_id, first) * HP;
+#pragma unroll
+      for (int h = 0; h < HP; ++h)
+        if (h < p.H) dst[h] = acc[h];
+    }
+  });
+}
+
+// Merges the pieces of rows that cross chunk boundaries (in chunk order) and zeroes rows
+// without edges.
+template <int HP>
+__global__ void __launch_bounds__(kThreadsPerCta)
+row_sum_fixup_kernel(RowSumParams p, int boundary_blocks) {
+  const int tid = blockIdx.x * kThreadsPerCta + threadIdx.x;
+  if ((int)blockIdx.x < boundary_blocks) {
+    const int bnd = 1 + tid;
+    if (bnd >= p.g.num_chunks) return;
+    const int x = bnd * p.g.chunk;
+    const int s = find_seg(p.g.ptr, p.g.nseg, x);
+    const int beg = __ldg(p.g.ptr + s);
+    if (!(beg < x && beg >= x - p.g.chunk)) return;  // no row starts in chunk bnd-1 and crosses x
+    const int end = __ldg(p.g.ptr + s + 1);
+    const int c0 = bnd - 1;
+    const int c1 = (end - 1) / p.g.chunk;
+    float tot[HP];
+#pragma unroll
+    for (int h = 0; h < HP; ++h) tot[h] = 0.f;
+    for (int c = c0; c <= c1; ++c) {
+      const float* slot = p.scratch + slot_index(c, c == c0) * HP;
+#pragma unroll
+      for (int h = 0; h < HP; ++h)
+        if (h < p.H) tot[h] += slot[h];
+    }
+#pragma unroll
+    for (int h = 0; h < HP; ++h)
+      if (h < p.H) p.grad_attn_row[(size_t)s * p.H + h] = tot[h];
+  } else {
+    const int s = tid - boundary_blocks * kThreadsPerCta;
+    if (s < p.g.nseg && __ldg(p.g.ptr + s) == __ldg(p.g.ptr + s + 1))
+      for (int h = 0; h < p.H; ++h) p.grad_attn_row[(size_t)s * p.H + h] = 0.f;
+  }
+}
+
+template <int HP>
+void launch_row_sum(const RowSumParams& p, cudaStream_t stream) {
+  if (p.g.num_chunks > 0) {
+    const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
+    row_sum_kernel<HP><<<blocks, kThreadsPerCta, 0, stream>>>(p);
+  }
+  const int nbound = p.g.num_chunks > 1 ? p.g.num_chunks - 1 : 0;
+  const int bblocks = (nbound + kThreadsPerCta - 1) / kThreadsPerCta;
+  const int sblocks = (p.g.nseg + kThreadsPerCta - 1) / kThreadsPerCta;
+  if (bblocks + sblocks > 0) row_sum_fixup_kernel<HP><<<bblocks + sblocks, kThreadsPerCta, 0, stream>>>(p, bblocks);
+}
+
+}  // namespace
+
+extern "C" int gnn_invert_permutation(const int* perm, int64_t n, int* inv, cudaStream_t stream) {
+  if (n < 0) return bad("gnn_invert_permutation: negative size");
+  if (n == 0) return GNN_OK;
+  if (!perm || !inv) return bad("gnn_invert_permutation: null pointer");
+  if (n > INT32_MAX) return bad("gnn_invert_permutation: size exceeds int32 indexing");
+  invert_permutation_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(perm, n, inv);
+  return check_launch("gnn_invert_permutation");
+}
+
+extern "C" int gnn_gat_bwd_pack(int64_t n_rows, const float* out, const float* grad_out,
+                                const float* attn_row, const float* edge_max, const float* edge_sum,
+                                int H, int F, float* rowpack, cudaStream_t stream) {
+  if (n_rows < 0 || H <= 0 || F <= 0) return bad("gnn_gat_bwd_pack: bad size");
+  if (n_rows == 0) return GNN_OK;
+  if (!out || !grad_out || !attn_row || !edge_max || !edge_sum || !rowpack)
+    return bad("gnn_gat_bwd_pack: null pointer");
+  const unsigned blocks = (unsigned)((n_rows + kWarpsPerCta - 1) / kWarpsPerCta);
+  const bool vec = aligned16(out) && aligned16(grad_out) && ((int64_t)H * F) % 4 == 0;
+  if (vec)
+    pack_kernel<true><<<blocks, kThreadsPerCta, 0, stream>>>(n_rows, out, grad_out, attn_row, edge_max,
+                                                            edge_sum, H, F, rowpack);
+  else
+    pack_kernel<false><<<blocks, kThreadsPerCta, 0, stream>>>(n_rows, out, grad_out, attn_row, edge_max,
+                                                             edge_sum, H, F, rowpack);
+  return check_launch("gnn_gat_bwd_pack");
+}
+
+extern "C" int gnn_gat_bwd_row_sum_workspace_bytes(int64_t nnz, int H, size_t* bytes) {
+  if (!bytes || nnz < 0 || H <= 0) return bad("gnn_gat_bwd_row_sum_workspace_bytes: bad argument");
+  const int chunk = pick_chunk(nnz);
+  *bytes = (size_t)num_chunks_for(nnz, chunk) * 2 * 8 * sizeof(float) + 256;
+  return GNN_OK;
+}
+
+extern "C" int gnn_gat_bwd_row_sum(const int* row_ptr, const int* csr_pos, int64_t n_rows, int64_t nnz,
+                                   const float* edge_grad, int H, float* grad_attn_row, void* workspace,
+                                   size_t workspace_bytes, cudaStream_t stream) {
+  if (n_rows < 0 || nnz < 0 || H <= 0) return bad("gnn_gat_bwd_row_sum: bad size");
+  if (H > 8) {
+    set_last_error("gnn_gat_bwd_row_sum: H > 8 is not supported");
+    return GNN_ERR_UNSUPPORTED;
+  }
+  if (n_rows > INT32_MAX - 1 || nnz > INT32_MAX - 4096) return bad("gnn_gat_bwd_row_sum: size exceeds int32 indexing");
+  if (n_rows == 0) return GNN_OK;
+  if (!row_ptr || !grad_attn_row || (nnz && (!csr_pos || !edge_grad))) return bad("gnn_gat_bwd_row_sum: null pointer");
+  if (nnz && !aligned16(edge_grad)) return bad("gnn_gat_bwd_row_sum: edge_grad must be 16-byte aligned");
+  size_t need = 0;
+  gnn_gat_bwd_row_sum_workspace_bytes(nnz, H, &need);
+  if (nnz > 0 && (!workspace || workspace_bytes < need)) {
+    set_last_error("gnn_gat_bwd_row_sum: workspace too small");
+    return GNN_ERR_WORKSPACE;
+  }
+  const int chunk = pick_chunk(nnz);
+  RowSumParams p;
+  p.g = ChunkGeom{row_ptr, csr_pos, (int)n_rows, (int)nnz, chunk, num_chunks_for(nnz, chunk)};
+  p.edge_grad = edge_grad;
+  p.H = H;
+  p.grad_attn_row = grad_attn_row;
+  p.scratch = (float*)align_up((uintptr_t)workspace, 256);
+  if (H == 1) launch_row_sum<1>(p, stream);
+  else if (H == 2) launch_row_sum<2>(p, stream);
+  else if (H <= 4) launch_row_sum<4>(p, stream);
+  else launch_row_sum<8>(p, stream);
+  return check_launch("gnn_gat_bwd_row_sum");
+}

@@ -33,6 +33,10 @@ def csr2csc(rowptr, colind, n_cols=None):
         capi.call("gnn_csr2csc", capi.ptr(rowptr), capi.ptr(colind), n_rows, n_cols, nnz,
                   capi.ptr(col_ptr), capi.ptr(row_ind), capi.ptr(permute), capi.ptr(ws),
                   ws.numel(), capi.stream_ptr(dev))
+    if n_cols == n_rows:
+        from .fused_gat import note_csr2csc
+
+        note_csr2csc(rowptr, colind, col_ptr, row_ind, permute)
     return col_ptr, row_ind, permute
 
 

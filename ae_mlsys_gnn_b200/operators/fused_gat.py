@@ -188,6 +188,146 @@ def gat_backward_col(negative_slope, col_ptr, row_ind, in_feat, attn_col, rowpac
     return grad_feat, grad_attn_col
 
 
+def gat_backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=None):
+    """rowpack (n, 4, H) = {attn_row, edge_max, 1/edge_sum, S} with S = <grad_out, out> per
+    head: the per-row record of the column pass, from the forward output instead of a pass
+    over the edges."""
+    dev = out.device
+    capi.require(out, F32, "out", 3)
+    capi.require(grad_out, F32, "grad_out", 3, dev)
+    n, H, F = edge_max.shape[0], out.shape[1], out.shape[2]
+    for name, t in (("attn_row", attn_row), ("edge_max", edge_max), ("edge_sum", edge_sum)):
+        capi.require(t, F32, name, 2, dev)
+    if out.shape[0] < n or grad_out.shape[0] < n or attn_row.shape[0] < n:
+        raise ValueError("out / grad_out / attn_row need at least one row per edge_max row")
+    rowpack = _rows(n, pad_to, (4, H), dev)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_bwd_pack", n, capi.ptr(out), capi.ptr(grad_out), capi.ptr(attn_row),
+                  capi.ptr(edge_max), capi.ptr(edge_sum), H, F, capi.ptr(rowpack), capi.stream_ptr(dev))
+    return rowpack
+
+
+def gat_backward_col_edges(negative_slope, col_ptr, row_ind, in_feat, attn_col, rowpack, grad_out,
+                           pad_to=None):
+    """``gat_backward_col`` that also returns edge_grad (E, H): the gradient of every edge
+    logit, in the position order of this CSC."""
+    dev = in_feat.device
+    n_cols = col_ptr.numel() - 1
+    H, F = in_feat.shape[1], in_feat.shape[2]
+    nnz = row_ind.numel()
+    grad_feat = _rows(n_cols, pad_to, (H, F), dev)
+    grad_attn_col = torch.empty((n_cols, H), dtype=F32, device=dev)
+    edge_grad = torch.empty((nnz, H), dtype=F32, device=dev)
+    nbytes = capi.workspace_bytes("gnn_gat_bwd_col_workspace_bytes", nnz, H, F)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_bwd_col_edges", capi.ptr(col_ptr), capi.ptr(row_ind), n_cols, nnz,
+                  capi.ptr(in_feat), capi.ptr(attn_col), capi.ptr(rowpack), capi.ptr(grad_out),
+                  H, F, float(negative_slope), capi.ptr(grad_feat), capi.ptr(grad_attn_col),
+                  capi.ptr(edge_grad), 0, capi.ptr(ws), ws.numel(), capi.stream_ptr(dev))
+    return grad_feat, grad_attn_col, edge_grad
+
+
+def gat_backward_row_sum(row_ptr, csr_pos, edge_grad):
+    """grad_attn_row (n_rows, H): sum of edge_grad over each row's edges; ``csr_pos`` gives,
+    for every CSR edge, its row in ``edge_grad``."""
+    dev = edge_grad.device
+    capi.require(edge_grad, F32, "edge_grad", 2)
+    capi.require(row_ptr, I32, "row_ptr", 1, dev)
+    capi.require(csr_pos, I32, "csr_pos", 1, dev)
+    n_rows = row_ptr.numel() - 1
+    nnz, H = csr_pos.numel(), edge_grad.shape[1]
+    out = torch.empty((n_rows, H), dtype=F32, device=dev)
+    nbytes = capi.workspace_bytes("gnn_gat_bwd_row_sum_workspace_bytes", nnz, H)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_bwd_row_sum", capi.ptr(row_ptr), capi.ptr(csr_pos), n_rows, nnz,
+                  capi.ptr(edge_grad), H, capi.ptr(out), capi.ptr(ws), ws.numel(), capi.stream_ptr(dev))
+    return out
+
+
+def invert_permutation(perm):
+    capi.require(perm, I32, "perm", 1)
+    inv = torch.empty_like(perm)
+    with torch.cuda.device(perm.device):
+        capi.call("gnn_invert_permutation", capi.ptr(perm), perm.numel(), capi.ptr(inv),
+                  capi.stream_ptr(perm.device))
+    return inv
+
+
+# The one-gather backward needs, for every CSR edge, its position in the CSC: a property of
+# the graph, computed on first use and kept while the graph's index tensors are alive
+# (a few entries; the tensors are referenced so that their addresses stay theirs).
+one_gather_backward = True
+_CSR_POS: "dict[tuple, tuple]" = {}
+_CSR_POS_MAX = 4
+
+
+_CSC_PERM: "dict[tuple, tuple]" = {}
+
+
+def _graph_key(row_ptr, col_ind, col_ptr, row_ind):
+    return ((row_ptr.data_ptr(), col_ind.data_ptr(), col_ptr.data_ptr(), row_ind.data_ptr(),
+             col_ind.numel(), row_ptr.numel(), str(row_ptr.device)),
+            (row_ptr._version, col_ind._version, col_ptr._version, row_ind._version))
+
+
+def note_csr2csc(row_ptr, col_ind, col_ptr, row_ind, permute):
+    """Called by operators.csr2csc for every CSC it builds: the permutation it returns is
+    the one ``csr_positions`` would otherwise have to rebuild for that graph."""
+    key, vers = _graph_key(row_ptr, col_ind, col_ptr, row_ind)
+    if len(_CSC_PERM) >= _CSR_POS_MAX:
+        _CSC_PERM.pop(next(iter(_CSC_PERM)))
+    _CSC_PERM[key] = (vers, permute, (row_ptr, col_ind, col_ptr, row_ind))
+
+
+def csr_positions(row_ptr, col_ind, col_ptr, row_ind):
+    """int32 (E,) position of every CSR edge in the CSC (col_ptr, row_ind), or None when that
+    CSC is not the one csr2csc builds from the CSR (then the two-pass backward applies).
+    A permutation handed in by the caller is not trusted: the map is rebuilt and checked."""
+    key, vers = _graph_key(row_ptr, col_ind, col_ptr, row_ind)
+    hit = _CSR_POS.get(key)
+    if hit is not None and hit[0] == vers:
+        return hit[1]
+    from .csr2csc import csr2csc
+
+    pos = None
+    known = _CSC_PERM.pop(key, None)
+    if known is not None and known[0] == vers and known[1]._version == 0:
+        pos = invert_permutation(known[1])  # this very CSC came out of csr2csc
+    elif row_ptr.numel() == col_ptr.numel():
+        cp, ri, permute = csr2csc(row_ptr, col_ind)
+        if torch.equal(cp, col_ptr) and torch.equal(ri, row_ind):
+            pos = invert_permutation(permute)
+    if len(_CSR_POS) >= _CSR_POS_MAX:
+        _CSR_POS.pop(next(iter(_CSR_POS)))
+    _CSR_POS[key] = (vers, pos, (row_ptr, col_ind, col_ptr, row_ind))
+    return pos
+
+
+def gat_backward_with_output(negative_slope, row_ptr, col_ind, col_ptr, row_ind, csr_pos, edge_max,
+                             edge_sum, in_feat, attn_row, attn_col, out, grad_out):
+    """(grad_feat, grad_attn_row, grad_attn_col), the values of ``gat_backward``, with one
+    gather pass: needs the forward output ``out`` and ``csr_pos`` (see ``csr_positions``)."""
+    rowpack = gat_backward_pack(out, grad_out, attn_row, edge_max, edge_sum)
+    grad_feat, grad_attn_col, edge_grad = gat_backward_col_edges(negative_slope, col_ptr, row_ind, in_feat,
+                                                                 attn_col, rowpack, grad_out)
+    grad_attn_row = gat_backward_row_sum(row_ptr, csr_pos, edge_grad)
+    return grad_feat, grad_attn_row, grad_attn_col
+
+
+def _backward(negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, in_feat,
+              attn_row, attn_col, out, grad_out):
+    """Backward of the autograd nodes: one gather pass when the graph allows, else two."""
+    if one_gather_backward and in_feat.shape[1] <= 8:
+        pos = csr_positions(row_ptr, col_ind, col_ptr, row_ind)
+        if pos is not None:
+            return gat_backward_with_output(negative_slope, row_ptr, col_ind, col_ptr, row_ind, pos,
+                                            edge_max, edge_sum, in_feat, attn_row, attn_col, out, grad_out)
+    return gat_backward(negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum,
+                        in_feat, attn_row, attn_col, grad_out)
+
+
 def gat_edge_alpha(attn_row, attn_col, row_ptr, col_ind, edge_max, edge_sum, negative_slope):
     """(edge_relu_csr, edge_softmax_csr), each (E, H)."""
     dev = attn_row.device
@@ -257,17 +397,17 @@ class FusedGATLayerFunction(torch.autograd.Function):
         attn_row, attn_col = gat_scores_forward(h, attn_l, attn_r)
         out, edge_max, edge_sum = gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, h)
         ctx.save_for_backward(row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, h, attn_row,
-                              attn_col, attn_l, attn_r)
+                              attn_col, attn_l, attn_r, out)
         ctx.negative_slope = negative_slope
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         (row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, h, attn_row, attn_col, attn_l,
-         attn_r) = ctx.saved_tensors
-        grad_feat, gar, gac = gat_backward(ctx.negative_slope, row_ptr, col_ind, col_ptr, row_ind,
-                                           edge_max, edge_sum, h, attn_row, attn_col,
-                                           grad_out.contiguous())
+         attn_r, out) = ctx.saved_tensors
+        grad_feat, gar, gac = _backward(ctx.negative_slope, row_ptr, col_ind, col_ptr, row_ind,
+                                        edge_max, edge_sum, h, attn_row, attn_col, out,
+                                        grad_out.contiguous())
         gl, gr = gat_scores_backward(h, attn_l, attn_r, gar, gac, grad_feat)
         return grad_feat, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None
 
@@ -290,17 +430,17 @@ class FusedGATFunction_SM(torch.autograd.Function):
         out, edge_max, edge_sum = gat_forward(attn_row, attn_col, row_ptr, col_ind,
                                               negative_slope, in_feat)
         ctx.save_for_backward(row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, in_feat,
-                              attn_row, attn_col)
+                              attn_row, attn_col, out)
         ctx.negative_slope = negative_slope
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         (row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, in_feat, attn_row,
-         attn_col) = ctx.saved_tensors
-        grad_feat, grad_attn_row, grad_attn_col = gat_backward(
+         attn_col, out) = ctx.saved_tensors
+        grad_feat, grad_attn_row, grad_attn_col = _backward(
             ctx.negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, in_feat,
-            attn_row, attn_col, grad_out.contiguous())
+            attn_row, attn_col, out, grad_out.contiguous())
         return grad_attn_row, grad_attn_col, None, None, None, None, None, grad_feat
 
 
@@ -319,17 +459,17 @@ class FusedGATFunction_stash(torch.autograd.Function):
         edge_relu, edge_alpha = gat_edge_alpha(attn_row, attn_col, row_ptr, col_ind, edge_max,
                                                edge_sum, negative_slope)
         ctx.save_for_backward(row_ptr, col_ind, col_ptr, row_ind, permute, edge_alpha, edge_relu,
-                              edge_max, edge_sum, in_feat, attn_row, attn_col)
+                              edge_max, edge_sum, in_feat, attn_row, attn_col, out)
         ctx.negative_slope = negative_slope
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         (row_ptr, col_ind, col_ptr, row_ind, _permute, _edge_alpha, _edge_relu, edge_max,
-         edge_sum, in_feat, attn_row, attn_col) = ctx.saved_tensors
-        grad_feat, grad_attn_row, grad_attn_col = gat_backward(
+         edge_sum, in_feat, attn_row, attn_col, out) = ctx.saved_tensors
+        grad_feat, grad_attn_row, grad_attn_col = _backward(
             ctx.negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, in_feat,
-            attn_row, attn_col, grad_out.contiguous())
+            attn_row, attn_col, out, grad_out.contiguous())
         return grad_attn_row, grad_attn_col, None, None, None, None, None, grad_feat, None
 
 

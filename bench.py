@@ -133,6 +133,12 @@ def algorithmic_bytes(name: str, n: int, e: int, H: int, Fw: int, D: int = 0) ->
         return 4.0 * e * (1 + H + HF) + 4.0 * n * (1 + HF + 3 * H)
     if name == "gnn_gat_bwd_col":
         return 4.0 * e * (1 + 3 * H + HF) + 4.0 * n * (1 + HF + 3 * H)
+    if name == "gnn_gat_bwd_col_edges":  # the column pass plus the E x H store of the edge gradients
+        return 4.0 * e * (1 + 4 * H + HF) + 4.0 * n * (1 + HF + 3 * H)
+    if name == "gnn_gat_bwd_pack":
+        return 4.0 * n * (2 * HF + 7 * H)
+    if name == "gnn_gat_bwd_row_sum":
+        return 4.0 * e * (1 + H) + 4.0 * n * (1 + H)
     if name == "gnn_edgeconv_fwd":
         return 4.0 * e * (1 + Fw) + 12.0 * n * Fw
     if name == "gnn_edgeconv_bwd":
@@ -184,6 +190,12 @@ class BytesLedger:
             return algorithmic_bytes(name, a[2], a[3], a[10], a[11])
         if name in ("gnn_gat_bwd_col", "gnn_gat_bwd_col_part"):
             return algorithmic_bytes("gnn_gat_bwd_col", a[2], a[3], a[8], a[9])
+        if name == "gnn_gat_bwd_col_edges":
+            return algorithmic_bytes(name if a[13] else "gnn_gat_bwd_col", a[2], a[3], a[8], a[9])
+        if name == "gnn_gat_bwd_pack":
+            return algorithmic_bytes(name, a[0], 0, a[6], a[7])
+        if name == "gnn_gat_bwd_row_sum":
+            return algorithmic_bytes(name, a[2], a[3], a[5], 1)
         if name == "gnn_edgeconv_fwd":
             return algorithmic_bytes(name, a[4], a[4] * a[0], 1, a[5])
         if name == "gnn_edgeconv_bwd":

@@ -169,6 +169,36 @@ int gnn_gat_bwd_col_part(const int* col_ptr, const int* row_ind, int64_t n_cols,
                          float* grad_feat, float* grad_attn_col, int accumulate, void* workspace,
                          size_t workspace_bytes, cudaStream_t stream);
 
+/* gnn_gat_bwd_col_part that also stores the gradient of every edge logit:
+ * edge_grad[p*H + h] for the p-th position of this CSC (16-byte aligned; NULL = do not
+ * store).  With gnn_gat_bwd_pack before and gnn_gat_bwd_row_sum after, this is the whole
+ * backward of fused_gat_SM.gat_backward (src/fused_gat/fused_gat_SM.cu:865-893) with one
+ * gather pass instead of two, for callers that kept the forward output. */
+int gnn_gat_bwd_col_edges(const int* col_ptr, const int* row_ind, int64_t n_cols, int64_t nnz,
+                          const float* in_feat, const float* attn_col, const float* rowpack,
+                          const float* grad_out, int H, int F, float negative_slope,
+                          float* grad_feat, float* grad_attn_col, float* edge_grad, int accumulate,
+                          void* workspace, size_t workspace_bytes, cudaStream_t stream);
+
+/* rowpack[r] = {attn_row[r,:], edge_max[r,:], 1/edge_sum[r,:], S[r,:]} (4*H floats per row)
+ * with S[r,h] = <grad_out[r,h,:], out[r,h,:]>, `out` being the forward output of
+ * gnn_gat_fwd for the same inputs: the per-row record the column pass reads, without the
+ * row pass over the edges. */
+int gnn_gat_bwd_pack(int64_t n_rows, const float* out, const float* grad_out, const float* attn_row,
+                     const float* edge_max, const float* edge_sum, int H, int F, float* rowpack,
+                     cudaStream_t stream);
+
+/* grad_attn_row[r,h] = sum over the CSR edges e of row r of edge_grad[csr_pos[e]*H + h];
+ * csr_pos[e] is the position of CSR edge e in the CSC whose column pass filled edge_grad
+ * (the inverse of the permutation gnn_csr2csc returns).  Deterministic. */
+int gnn_gat_bwd_row_sum_workspace_bytes(int64_t nnz, int H, size_t* bytes);
+int gnn_gat_bwd_row_sum(const int* row_ptr, const int* csr_pos, int64_t n_rows, int64_t nnz,
+                        const float* edge_grad, int H, float* grad_attn_row, void* workspace,
+                        size_t workspace_bytes, cudaStream_t stream);
+
+/* inv[perm[i]] = i for a permutation of 0..n-1 (e.g. gnn_csr2csc's permute -> csr_pos). */
+int gnn_invert_permutation(const int* perm, int64_t n, int* inv, cudaStream_t stream);
+
 /* Per-edge activated logits and normalised attention (E x H each), the tensors the
  * stash / fusescatter variants keep: fused_gat_stash.gat_forward and
  * fused_gat.gat_forward (src/fused_gat/fused_gat_stash.cu:193-288,

@@ -251,3 +251,97 @@ def test_gat_column_pieces_match_single_launch(cuda, H, F, pieces):
         gat_backward_col_part(0.2, cp_c, ri_c, d[2], d[1], rowpack, d[3], gf2, gac2, c > 0)
     assert_close(gf2, gf, "grad_feat by pieces", scale_atol=True)
     assert_close(gac2, gac, "grad_attn_col by pieces", scale_atol=True)
+
+
+# ---- one-gather backward: forward output + per-edge gradients instead of the row pass ------
+
+def _one_gather(cuda, g, H, F, seed):
+    from ae_mlsys_gnn_b200.operators import fused_gat as G
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+
+    attn_row, attn_col, feat, gout = _inputs(g, H, F, seed)
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    cp, ri, pm = csr2csc(rp, ci)
+    d = [t.to(cuda) for t in (attn_row, attn_col, feat, gout)]
+    out, m, s = G.gat_forward(d[0], d[1], rp, ci, 0.2, d[2])
+    pos = G.csr_positions(rp, ci, cp, ri)
+    assert pos is not None and torch.equal(pm[pos.long()].cpu(), torch.arange(g.nnz, dtype=torch.int32))
+    got = G.gat_backward_with_output(0.2, rp, ci, cp, ri, pos, m, s, d[2], d[0], d[1], out, d[3])
+    two = G.gat_backward(0.2, rp, ci, cp, ri, m, s, d[2], d[0], d[1], d[3])
+    _, em, es = ref.gat_forward(attn_row, attn_col, g.row_ptr, g.col_ind, 0.2, feat)
+    exp = ref.gat_backward(0.2, g.row_ptr, g.col_ind, em, es, feat, attn_row, attn_col, gout)
+    return got, two, exp
+
+
+@pytest.mark.parametrize("name", list(crafted_graphs().keys()))
+@pytest.mark.parametrize("H,F", [(4, 64), (4, 128), (8, 8), (1, 7), (1, 47), (2, 16), (3, 12)])
+def test_gat_one_gather_backward_crafted(cuda, name, H, F):
+    g = _square(crafted_graphs()[name])
+    got, two, exp = _one_gather(cuda, g, H, F, 12)
+    for a, b, e, what in zip(got, two, exp, ("grad_feat", "grad_attn_row", "grad_attn_col")):
+        assert_close(a, e, f"{what}[{name}] vs oracle", scale_atol=True)
+        assert_close(a, b, f"{what}[{name}] vs two-pass", scale_atol=True)
+
+
+@pytest.mark.parametrize("H,F", [(4, 64), (1, 41), (4, 128), (8, 16)])
+def test_gat_one_gather_backward_power_law(cuda, H, F):
+    got, two, exp = _one_gather(cuda, power_law_graph(3000, 60, seed=3), H, F, 13)
+    for a, b, e, what in zip(got, two, exp, ("grad_feat", "grad_attn_row", "grad_attn_col")):
+        assert_close(a, e, f"{what} vs oracle", scale_atol=True)
+        assert_close(a, b, f"{what} vs two-pass", scale_atol=True)
+
+
+def test_gat_one_gather_pieces(cuda):
+    """The three steps on their own: the per-row record, the per-edge gradients, the row sums."""
+    from ae_mlsys_gnn_b200.operators import fused_gat as G
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+
+    g = power_law_graph(1500, 40, seed=9)
+    H, F = 4, 32
+    attn_row, attn_col, feat, gout = _inputs(g, H, F, 14)
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    cp, ri, pm = csr2csc(rp, ci)
+    d = [t.to(cuda) for t in (attn_row, attn_col, feat, gout)]
+    out, m, s = G.gat_forward(d[0], d[1], rp, ci, 0.2, d[2])
+    pack = G.gat_backward_pack(out, d[3], d[0], m, s)
+    _, old_pack = G.gat_backward_row(0.2, rp, ci, m, s, d[2], d[0], d[1], d[3])
+    assert_close(pack, old_pack, "rowpack", scale_atol=True)
+    S = (out.double() * d[3].double()).sum(-1)
+    assert_close(pack[:, 3], S, "S = <grad_out, out>", scale_atol=True)
+    gf, gac, eg = G.gat_backward_col_edges(0.2, cp, ri, d[2], d[1], pack, d[3])
+    gf2, gac2 = G.gat_backward_col(0.2, cp, ri, d[2], d[1], pack, d[3])
+    assert torch.equal(gf, gf2) and torch.equal(gac, gac2)
+    # column sums of the per-edge gradients are grad_attn_col; row sums grad_attn_row
+    col_of = torch.repeat_interleave(torch.arange(g.n, device=cuda), (cp[1:] - cp[:-1]).long())
+    ref_col = torch.zeros(g.n, H, dtype=torch.float64, device=cuda).index_add_(0, col_of, eg.double())
+    assert_close(gac, ref_col, "grad_attn_col from edge_grad", scale_atol=True)
+    ref_row = torch.zeros(g.n, H, dtype=torch.float64, device=cuda).index_add_(0, ri.long(), eg.double())
+    pos = G.invert_permutation(pm)
+    assert_close(G.gat_backward_row_sum(rp, pos, eg), ref_row, "row sums", scale_atol=True)
+    again = G.gat_backward_row_sum(rp, pos, eg)
+    assert torch.equal(again, G.gat_backward_row_sum(rp, pos, eg)), "row sums are deterministic"
+
+
+def test_gat_autograd_falls_back_for_foreign_csc(cuda):
+    """A CSC that is not the one csr2csc builds (rows of a column in another order) is still
+    handled: the autograd node takes the two-pass backward."""
+    from ae_mlsys_gnn_b200.operators import fused_gat as G
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+
+    g = power_law_graph(400, 12, seed=21)
+    H, F = 2, 16
+    attn_row, attn_col, feat, gout = _inputs(g, H, F, 15)
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    cp, ri, _ = csr2csc(rp, ci)
+    ri2 = ri.clone()
+    for c in range(g.n):  # reverse the rows inside every column
+        a, b = int(cp[c]), int(cp[c + 1])
+        ri2[a:b] = ri[a:b].flip(0)
+    assert G.csr_positions(rp, ci, cp, ri2) is None
+    d = [t.to(cuda).requires_grad_(True) for t in (attn_row, attn_col, feat)]
+    G.fused_gat_op(d[0], d[1], rp, ci, cp, ri2, 0.2, d[2]).backward(gout.to(cuda))
+    _, em, es = ref.gat_forward(attn_row, attn_col, g.row_ptr, g.col_ind, 0.2, feat)
+    ef, ear, eac = ref.gat_backward(0.2, g.row_ptr, g.col_ind, em, es, feat, attn_row, attn_col, gout)
+    assert_close(d[2].grad, ef, "grad_feat", scale_atol=True)
+    assert_close(d[0].grad, ear, "grad_attn_row", scale_atol=True)
+    assert_close(d[1].grad, eac, "grad_attn_col", scale_atol=True)
