@@ -169,6 +169,9 @@ __device__ __forceinline__ size_t slot_index(int chunk_id, bool first_piece) {
   return (size_t)chunk_id * 2 + (first_piece ? 1 : 0);
 }
 
+// Empty segments walked one by one before the traversal searches for the end of the run.
+constexpr int kEmptyRunWalk = 8;
+
 template <class Body>
 __device__ __forceinline__ void for_each_piece(const ChunkGeom& g, int chunk_id,
                                                Body&& body) {
@@ -176,8 +179,21 @@ __device__ __forceinline__ void for_each_piece(const ChunkGeom& g, int chunk_id,
   const int hi = min(lo + g.chunk, g.nnz);
   int s = find_seg(g.ptr, g.nseg, lo);
   int beg = __ldg(g.ptr + s);
+  int empties = 0;
   while (s < g.nseg && beg < hi) {
     const int end = __ldg(g.ptr + s + 1);
+    if (end == beg) {
+      // a segment without positions; after a few in a row, jump over the rest of the run
+      // (one warp would otherwise walk a run of hundreds of thousands one by one)
+      if (++empties > kEmptyRunWalk) {
+        s = find_seg(g.ptr, g.nseg, beg);
+        empties = 0;
+      } else {
+        ++s;
+      }
+      continue;
+    }
+    empties = 0;
     const int a = max(beg, lo);
     const int b = min(end, hi);
     if (b > a) body(s, a, b, /*first=*/beg >= lo, /*last=*/end <= hi);

@@ -80,37 +80,88 @@ struct RowSumParams {
   float* scratch;          // 2 * num_chunks slots of HP floats
 };
 
+// One warp per chunk of consecutive CSR positions.  The chunk is consumed in windows of 32
+// positions: every lane gathers the value of its own edge (32 independent gathers in flight,
+// the next window's requested before the current one is reduced), then the rows that
+// overlap the window are summed one after the other with masked warp reductions.  Rows
+// average a few dozen edges, so gathering per row instead would leave most lanes idle and
+// expose one gather latency per row.
 template <int HP>
 __global__ void __launch_bounds__(kThreadsPerCta)
 row_sum_kernel(RowSumParams p) {
   const int lane = threadIdx.x & 31;
   const int chunk_id = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
   if (chunk_id >= p.g.num_chunks) return;
-  for_each_piece(p.g, chunk_id, [&](int s, int a, int b, bool first, bool last) {
-    float acc[HP];
+  const int lo = chunk_id * p.g.chunk;
+  const int hi = min(lo + p.g.chunk, p.g.nnz);
+  constexpr int LPH = 32 / HP;  // after warp_multi_sum head h sits on lanes [h*LPH, (h+1)*LPH)
+
+  auto gather = [&](int e, float (&v)[HP]) {
 #pragma unroll
-    for (int h = 0; h < HP; ++h) acc[h] = 0.f;
-    for (int e = a + lane; e < b; e += 32) {
+    for (int h = 0; h < HP; ++h) v[h] = 0.f;
+    if (e < hi) {
       const float* eg = p.edge_grad + (size_t)__ldg(p.g.idx + e) * p.H;
       if (HP == 4 && p.H == 4) {
-        const float4 v = __ldg(reinterpret_cast<const float4*>(eg));
-        acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+        const float4 t = __ldg(reinterpret_cast<const float4*>(eg));
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
       } else {
 #pragma unroll
         for (int h = 0; h < HP; ++h)
-          if (h < p.H) acc[h] += __ldg(eg + h);
+          if (h < p.H) v[h] = __ldg(eg + h);
       }
     }
-#pragma unroll
-    for (int h = 0; h < HP; ++h) acc[h] = warp_sum(acc[h]);
-    if (lane == 0) {
+  };
+  // this lane's head of the finished (or cut) row s goes to the output or to a scratch slot
+  auto emit = [&](int s, float total, bool first, bool last) {
+    if ((lane & (LPH - 1)) == 0 && lane / LPH < p.H) {
       float* dst = (first && last) ? p.grad_attn_row + (size_t)s * p.H
                                    : p.scratch + slot_index(chunk_id, first) * HP;
-#pragma unroll
-      for (int h = 0; h < HP; ++h)
-        if (h < p.H) dst[h] = acc[h];
+      dst[lane / LPH] = total;
     }
-  });
+  };
+
+  int s = find_seg(p.g.ptr, p.g.nseg, lo);
+  int beg = __ldg(p.g.ptr + s);
+  float acc = 0.f;  // running sum of row s, head lane / LPH
+  float cur[HP], nxt[HP];
+  int empties = 0;
+  gather(lo + lane, cur);
+  for (int base = lo; base < hi; base += 32) {
+    gather(base + 32 + lane, nxt);
+    const int wend = min(base + 32, hi);
+    while (s < p.g.nseg) {
+      const int end = __ldg(p.g.ptr + s + 1);
+      if (end == beg) {  // rows without edges: walk a few, then jump over the rest of the run
+        if (++empties > kEmptyRunWalk) {
+          s = find_seg(p.g.ptr, p.g.nseg, beg);
+          empties = 0;
+        } else {
+          ++s;
+        }
+        continue;
+      }
+      empties = 0;
+      const int a = max(beg, base), b = min(end, wend);
+      if (b > a) {
+        const bool mine = lane >= a - base && lane < b - base;
+        float t[HP];
+#pragma unroll
+        for (int h = 0; h < HP; ++h) t[h] = mine ? cur[h] : 0.f;
+        warp_multi_sum<HP>(t, lane);
+        acc += t[0];
+      }
+      if (end > wend) break;  // the row goes on in the next window (or the next chunk)
+      emit(s, acc, beg >= lo, true);
+      acc = 0.f;
+      beg = end;
+      ++s;
+      if (beg >= wend) break;
+    }
+#pragma unroll
+    for (int h = 0; h < HP; ++h) cur[h] = nxt[h];
+  }
+  // a row that runs past the end of the chunk leaves its piece in a slot
+  if (s < p.g.nseg && beg < hi && __ldg(p.g.ptr + s + 1) > hi) emit(s, acc, beg >= lo, false);
 }
 
 // Merges the pieces of rows that cross chunk boundaries (in chunk order) and zeroes rows

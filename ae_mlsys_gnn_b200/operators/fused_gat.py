@@ -228,6 +228,25 @@ def gat_backward_col_edges(negative_slope, col_ptr, row_ind, in_feat, attn_col, 
     return grad_feat, grad_attn_col, edge_grad
 
 
+def gat_backward_col_edges_part(negative_slope, col_ptr, row_ind, in_feat, attn_col, rowpack, grad_out,
+                                grad_feat, grad_attn_col, accumulate):
+    """``gat_backward_col_part`` that also returns edge_grad (E, H) of this block."""
+    dev = in_feat.device
+    n_cols = col_ptr.numel() - 1
+    H, F = in_feat.shape[1], in_feat.shape[2]
+    nnz = row_ind.numel()
+    edge_grad = torch.empty((nnz, H), dtype=F32, device=dev)
+    nbytes = capi.workspace_bytes("gnn_gat_bwd_col_workspace_bytes", nnz, H, F)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_bwd_col_edges", capi.ptr(col_ptr), capi.ptr(row_ind), n_cols, nnz,
+                  capi.ptr(in_feat), capi.ptr(attn_col), capi.ptr(rowpack), capi.ptr(grad_out),
+                  H, F, float(negative_slope), capi.ptr(grad_feat), capi.ptr(grad_attn_col),
+                  capi.ptr(edge_grad), int(bool(accumulate)), capi.ptr(ws), ws.numel(),
+                  capi.stream_ptr(dev))
+    return edge_grad
+
+
 def gat_backward_row_sum(row_ptr, csr_pos, edge_grad):
     """grad_attn_row (n_rows, H): sum of edge_grad over each row's edges; ``csr_pos`` gives,
     for every CSR edge, its row in ``edge_grad``."""

@@ -5,8 +5,8 @@ The reference is single-GPU; nothing here has a counterpart in it.  Design:
 
 * Rows (destination nodes) are cut into P contiguous blocks with about nnz/P edges
   each (a row is never split).  Rank g owns block g: the CSR rows of the block (for
-  the forward and the backward row pass) and the CSC columns of the block (for the
-  backward column pass, which produces gradients of the sources the rank owns).
+  the forward) and the CSC columns of the block (for the backward column pass, which
+  produces gradients of the sources the rank owns).
 * Every per-node tensor of a rank has ``max_n = K * cn`` rows: the rank's own rows,
   then zero padding; K is the number of exchange pieces and cn the rows per piece.
   Piece c of a tensor is rows [c*cn, (c+1)*cn) of every rank; one all-gather moves piece c
@@ -17,11 +17,16 @@ The reference is single-GPU; nothing here has a counterpart in it.  Design:
   by the piece of its destination).  The forward launches the fused kernel once per
   piece, as soon as that piece of the projected features has arrived, merging the
   online-softmax state between launches (gnn_gat_fwd_part); the backward column pass
-  does the same with the pieces of grad_out (gnn_gat_bwd_col_part).  The transfer of
-  piece c+1 therefore runs under the aggregation of piece c, and the gather of grad_out
-  also runs under the whole row pass.
-* Per layer the exchanges are: h and attn_col (forward); grad_out and the per-row pack
-  {attn_row, max, 1/sum, S} (backward).  The small tensors travel on a second
+  does the same with the pieces of grad_out (gnn_gat_bwd_col_edges).  The transfer of
+  piece c+1 therefore runs under the aggregation of piece c.
+* The backward makes one gather pass: the per-row pack {attn_row, max, 1/sum, S} is
+  node-wise (S = <grad_out, out>, gnn_gat_bwd_pack), the column pass over the owned sources
+  also stores the gradient of every edge logit, and those are summed by destination row
+  (gnn_gat_bwd_row_sum over the transposed index of the rank's CSC block) into a partial
+  grad_attn_row for ALL rows, which a reduce-scatter (N x H floats) turns into the owned
+  rows' sums.
+* Per layer the exchanges are: h and attn_col (forward); grad_out, the per-row pack and the
+  reduce-scatter of grad_attn_row (backward).  The small tensors travel on a second
   communicator so that they do not queue behind the large pieces.  No reduction of
   feature gradients is needed because the column pass sums over all destinations of an
   owned source.  Weight gradients are all-reduced after the backward (they are tiny).
@@ -74,6 +79,9 @@ class RowBlockPartition:
     col_ind: torch.Tensor      # int32, ids in the gathered (piece-major) space
     csr_parts: list = field(default_factory=list)  # K x (row_ptr_c, col_ind_c): sources in piece c
     csc_parts: list = field(default_factory=list)  # K x (col_ptr_c, row_ind_c): destinations in piece c
+    # K x (ptr_c, pos_c): for every destination row of piece c (P*cn rows of the gathered
+    # space) the positions of its edges inside csc_parts[c] -- the transposed index of the block
+    rowsum_parts: list = field(default_factory=list)
 
     @property
     def max_n(self) -> int:
@@ -109,13 +117,16 @@ class RowBlockPartition:
             d[f"csr{c}_ptr"], d[f"csr{c}_idx"] = a, b
         for c, (a, b) in enumerate(self.csc_parts):
             d[f"csc{c}_ptr"], d[f"csc{c}_idx"] = a, b
+        for c, (a, b) in enumerate(self.rowsum_parts):
+            d[f"rs{c}_ptr"], d[f"rs{c}_idx"] = a, b
         return d
 
     def with_index_tensors(self, d: dict) -> "RowBlockPartition":
         return dataclasses.replace(
             self, row_ptr=d["row_ptr"], col_ind=d["col_ind"],
             csr_parts=[(d[f"csr{c}_ptr"], d[f"csr{c}_idx"]) for c in range(self.pieces)],
-            csc_parts=[(d[f"csc{c}_ptr"], d[f"csc{c}_idx"]) for c in range(self.pieces)])
+            csc_parts=[(d[f"csc{c}_ptr"], d[f"csc{c}_idx"]) for c in range(self.pieces)],
+            rowsum_parts=[(d[f"rs{c}_ptr"], d[f"rs{c}_idx"]) for c in range(self.pieces)])
 
 
 def _to_gathered_ids(ids: torch.Tensor, bounds: list[int], cn: int, world: int) -> torch.Tensor:
@@ -157,6 +168,16 @@ def _split_by_piece(ptr: torch.Tensor, ids_sorted: torch.Tensor, seg: torch.Tens
     return out
 
 
+def _transposed_index(row_ids: torch.Tensor, first: int, span: int):
+    """(ptr [span+1], pos [E]) int32: the positions 0..E-1 of an edge array grouped by their
+    row id (row_ids - first, in [0, span)), ascending inside every row."""
+    r = row_ids.long() - first
+    pos = torch.argsort(r, stable=True).to(torch.int32).contiguous()
+    ptr = torch.zeros(span + 1, dtype=torch.int64, device=row_ids.device)
+    ptr[1:] = torch.cumsum(torch.bincount(r, minlength=span), 0)
+    return ptr.to(torch.int32).contiguous(), pos
+
+
 def build_partition(row_ptr, col_ind, col_ptr, row_ind, rank: int, world: int,
                     bounds: list[int] | None = None, pieces: int | None = None) -> RowBlockPartition:
     """Cuts the global CSR (row_ptr, col_ind) and CSC (col_ptr, row_ind) of a square
@@ -180,8 +201,9 @@ def build_partition(row_ptr, col_ind, col_ptr, row_ind, rank: int, world: int,
     cp, ri, cseg = cut(col_ptr, row_ind)
     csr_parts = _split_by_piece(rp, ci, rseg, pieces, span)
     csc_parts = _split_by_piece(cp, ri, cseg, pieces, span)
+    rowsum_parts = [_transposed_index(ri_c, c * span, span) for c, (_, ri_c) in enumerate(csc_parts)]
     return RowBlockPartition(rank, world, bounds, pieces, cn, rp, ci.to(torch.int32).contiguous(),
-                             csr_parts, csc_parts)
+                             csr_parts, csc_parts, rowsum_parts)
 
 
 def gather_pieces(x: torch.Tensor, part: RowBlockPartition, group=None, async_op: bool = False):
@@ -198,6 +220,26 @@ def gather_pieces(x: torch.Tensor, part: RowBlockPartition, group=None, async_op
                                         group=group, async_op=async_op)
         works.append(w)
     return out, (works if async_op else None)
+
+
+def reduce_scatter_pieces(x_full: torch.Tensor, part: RowBlockPartition, group=None) -> torch.Tensor:
+    """Inverse of ``gather_pieces`` for sums: (P*max_n, ...) per-rank partial values in the
+    gathered order -> (max_n, ...) totals of the rank's own rows."""
+    P, K, cn = part.world, part.pieces, part.cn
+    if P == 1:
+        return x_full
+    x_full = x_full.contiguous()
+    out = x_full.new_empty((part.max_n,) + tuple(x_full.shape[1:]))
+    backend = dist.get_backend(group)
+    for c in range(K):
+        src = x_full[c * P * cn: (c + 1) * P * cn]
+        if backend == "gloo":  # no reduce-scatter there: reduce everything, keep the own slice
+            tmp = src.clone()
+            dist.all_reduce(tmp, group=group)
+            out[c * cn: (c + 1) * cn] = tmp[part.rank * cn: (part.rank + 1) * cn]
+        else:
+            dist.reduce_scatter_tensor(out[c * cn: (c + 1) * cn], src, group=group)
+    return out
 
 
 class _CudaKernels:
@@ -225,20 +267,24 @@ class _CudaKernels:
                          edge_sum, accumulate, finalize)
 
     @staticmethod
-    def backward_row(slope, row_ptr, col_ind, edge_max, edge_sum, h_full, attn_row, attn_col_full,
-                     grad_out, pad_to=None):
-        from .operators.fused_gat import gat_backward_row
+    def backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=None):
+        from .operators.fused_gat import gat_backward_pack
 
-        return gat_backward_row(slope, row_ptr, col_ind, edge_max, edge_sum, h_full, attn_row,
-                                attn_col_full, grad_out, pad_to=pad_to)
+        return gat_backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=pad_to)
 
     @staticmethod
-    def backward_col_part(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full,
-                          grad_feat, grad_attn_col, accumulate):
-        from .operators.fused_gat import gat_backward_col_part
+    def backward_col_edges_part(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full,
+                                grad_feat, grad_attn_col, accumulate):
+        from .operators.fused_gat import gat_backward_col_edges_part
 
-        gat_backward_col_part(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full,
-                              gout_full, grad_feat, grad_attn_col, accumulate)
+        return gat_backward_col_edges_part(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full,
+                                           gout_full, grad_feat, grad_attn_col, accumulate)
+
+    @staticmethod
+    def backward_row_sum(ptr, pos, edge_grad):
+        from .operators.fused_gat import gat_backward_row_sum
+
+        return gat_backward_row_sum(ptr, pos, edge_grad)
 
 
 class PartitionedGATFunction(torch.autograd.Function):
@@ -268,36 +314,36 @@ class PartitionedGATFunction(torch.autograd.Function):
             rp_c, ci_c = part.csr_parts[c]
             kernels.forward_part(attn_row[:n], ac_full, rp_c, ci_c, slope, h_full, out, edge_max,
                                  edge_sum, c > 0, c == K - 1)
-        ctx.save_for_backward(attn_row, attn_col, h, h_full, ac_full, edge_max, edge_sum, attn_l,
-                              attn_r)
+        ctx.save_for_backward(attn_row, attn_col, h, ac_full, edge_max, edge_sum, attn_l, attn_r, out)
         ctx.part, ctx.slope, ctx.kernels = part, slope, kernels
         ctx.group, ctx.small_group = group, small_group
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        (attn_row, attn_col, h, h_full, ac_full, edge_max, edge_sum, attn_l,
-         attn_r) = ctx.saved_tensors
+        attn_row, attn_col, h, ac_full, edge_max, edge_sum, attn_l, attn_r, out = ctx.saved_tensors
         part, slope, kernels = ctx.part, ctx.slope, ctx.kernels
-        n, K = part.n_local, part.pieces
+        n, K, P, cn = part.n_local, part.pieces, part.world, part.cn
         H, Fo = h.shape[1], h.shape[2]
         grad_out = grad_out.contiguous()
-        # the pieces of grad_out travel while the row pass runs on local data
+        # the pieces of grad_out travel while the per-row pack (node-wise) is formed and exchanged
         gout_full, works = gather_pieces(grad_out, part, ctx.group, async_op=True)
-        gar_l, rowpack = kernels.backward_row(slope, part.row_ptr, part.col_ind, edge_max, edge_sum,
-                                              h_full, attn_row[:n], ac_full, grad_out[:n],
-                                              pad_to=part.max_n)
+        rowpack = kernels.backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=part.max_n)
         rp_full, _ = gather_pieces(rowpack, part, ctx.small_group)
         gh = h.new_empty((part.max_n, H, Fo))
         if n < part.max_n:
             gh[n:].zero_()
         gac_l = h.new_empty((n, H))
+        gar_part = h.new_empty((P * part.max_n, H))  # this rank's share of every row's grad_attn_row
         for c in range(K):
             if works is not None:
                 works[c].wait()
             cp_c, ri_c = part.csc_parts[c]
-            kernels.backward_col_part(slope, cp_c, ri_c, h[:n], attn_col[:n], rp_full, gout_full,
-                                      gh, gac_l, c > 0)
+            edge_grad = kernels.backward_col_edges_part(slope, cp_c, ri_c, h[:n], attn_col[:n], rp_full,
+                                                        gout_full, gh, gac_l, c > 0)
+            rs_ptr, rs_pos = part.rowsum_parts[c]
+            gar_part[c * P * cn: (c + 1) * P * cn] = kernels.backward_row_sum(rs_ptr, rs_pos, edge_grad)
+        gar_l = reduce_scatter_pieces(gar_part, part, ctx.small_group)[:n]
         gl, gr = kernels.scores_backward(h[:n], attn_l, attn_r, gar_l, gac_l, gh[:n])
         return gh, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None, None
 

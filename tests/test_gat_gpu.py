@@ -345,3 +345,23 @@ def test_gat_autograd_falls_back_for_foreign_csc(cuda):
     assert_close(d[2].grad, ef, "grad_feat", scale_atol=True)
     assert_close(d[0].grad, ear, "grad_attn_row", scale_atol=True)
     assert_close(d[1].grad, eac, "grad_attn_col", scale_atol=True)
+
+
+def test_gat_long_run_of_isolated_nodes(cuda):
+    """Thousands of consecutive rows (and columns) without edges in the middle of the graph:
+    the chunk traversal jumps over the run instead of walking it; values are unchanged."""
+    from ae_mlsys_gnn_b200.graphs import Graph
+
+    base = power_law_graph(300, 10, seed=31)
+    gap, n = 20000, 300 + 20000
+    deg = (base.row_ptr[1:] - base.row_ptr[:-1]).long()
+    full_deg = torch.cat([deg[:150], torch.zeros(gap, dtype=torch.long), deg[150:]])
+    rp = torch.zeros(n + 1, dtype=torch.int32)
+    rp[1:] = torch.cumsum(full_deg, 0).to(torch.int32)
+    ci = base.col_ind.clone()
+    ci[ci >= 150] += gap   # sources keep away from the gap as well
+    g = Graph(n, rp.contiguous(), ci.contiguous())
+    got, two, exp = _one_gather(cuda, g, 4, 16, 32)
+    for a, b, e, what in zip(got, two, exp, ("grad_feat", "grad_attn_row", "grad_attn_col")):
+        assert_close(a, e, f"{what} vs oracle", scale_atol=True)
+        assert_close(b, e, f"{what} two-pass vs oracle", scale_atol=True)

@@ -22,7 +22,7 @@ def _pad(t, rows):
 
 
 class OracleKernels:
-    """Same three methods as partition._CudaKernels, computed by the CPU oracle."""
+    """Same methods as partition._CudaKernels, computed by the CPU oracle."""
 
     @staticmethod
     def scores_forward(h, attn_l, attn_r):
@@ -59,22 +59,17 @@ class OracleKernels:
         edge_sum.copy_(s_p.float())
 
     @staticmethod
-    def backward_row(slope, row_ptr, col_ind, edge_max, edge_sum, h_full, attn_row, attn_col_full, grad_out,
-                     pad_to=None):
-        rows, cols = ref.rows_of(row_ptr), col_ind.long()
-        e, alpha = ref.gat_alpha(attn_row, attn_col_full, row_ptr, col_ind, slope, edge_max, edge_sum)
-        g = (grad_out.double()[rows] * h_full.double()[cols]).sum(-1)
-        n, H = attn_row.shape
-        S = torch.zeros(n, H, dtype=torch.float64).index_add_(0, rows, alpha * g)
-        ge = alpha * (g - S[rows])
-        ge = torch.where(e < 0, ge * slope, ge)
-        gar = torch.zeros(n, H, dtype=torch.float64).index_add_(0, rows, ge)
-        pack = torch.stack([attn_row.double(), edge_max.double(), 1.0 / edge_sum.double(), S], 1)
-        return gar.float(), _pad(pack.float(), pad_to)
+    def backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=None):
+        n = edge_max.shape[0]
+        S = (grad_out.double()[:n] * out.double()[:n]).sum(-1)
+        es = edge_sum.double()
+        inv = torch.where(es > 0, 1.0 / es.clamp_min(1e-300), torch.zeros_like(es))
+        pack = torch.stack([attn_row.double()[:n], edge_max.double(), inv, torch.where(es > 0, S, torch.zeros_like(S))], 1)
+        return _pad(pack.float(), pad_to)
 
     @staticmethod
-    def backward_col_part(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full,
-                          grad_feat, grad_attn_col, accumulate):
+    def backward_col_edges_part(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full,
+                                grad_feat, grad_attn_col, accumulate):
         cols, rows = ref.rows_of(col_ptr), row_ind.long()   # segments are the owned sources
         rp = rowpack_full.double()
         x = rp[rows, 0] + attn_col_local.double()[cols]
@@ -93,6 +88,15 @@ class OracleKernels:
         else:
             grad_feat[:n] = gh.float()
             grad_attn_col.copy_(gac.float())
+        return ge.float()
+
+    @staticmethod
+    def backward_row_sum(ptr, pos, edge_grad):
+        n = ptr.numel() - 1
+        seg = ref.rows_of(ptr)
+        out = torch.zeros(n, edge_grad.shape[1], dtype=torch.float64)
+        out.index_add_(0, seg, edge_grad.double()[pos.long()])
+        return out.float()
 
 
 def test_edge_balanced_bounds():
