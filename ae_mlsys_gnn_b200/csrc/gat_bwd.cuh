@@ -255,7 +255,7 @@ struct GatBwdColParams {
 // EDGES: also store the gradient of every edge logit, a(r,c) d(r,c) (<G[r],h[c]> - S[r]),
 // from which the caller sums grad_attn_row without a second gather pass.
 template <int Q, bool VEC>
-constexpr bool kColPipelined = Q * (VEC ? 4 : 1) <= 8;  // a row is at most 8 registers per lane
+constexpr bool kColPipelined = VEC && Q <= 2;  // 128-bit tiles of at most 8 registers per lane and row
 
 // (Two CTAs per SM are requested only for the pipelined narrow tiles; the widest tile gets
 // there by itself, and with the explicit limit its gather loop is scheduled into spills.)

@@ -12,7 +12,7 @@ import json
 
 import torch
 
-OPS = ("gat_fwd", "gat_bwd_row", "gat_bwd_col", "csr2csc", "edgeconv_fwd", "gmm_fwd", "mhspmm", "mhsddmm",
+OPS = ("gat_fwd", "gat_bwd_row", "gat_bwd_col", "gat_bwd_col_edges", "gat_bwd_row_sum", "gat_bwd_pack", "csr2csc", "edgeconv_fwd", "gmm_fwd", "mhspmm", "mhsddmm",
        "gemm", "gemm_tn")
 
 
@@ -107,6 +107,18 @@ def main():
     elif a.op == "gat_bwd_col":
         fn = lambda: GAT.gat_backward_col(0.2, cp, ri, feat, ac, rowpack, gout)
         nbytes = 4.0 * nnz * (1 + 3 * H + HF) + 4.0 * n * (1 + HF + 3 * H)
+    elif a.op == "gat_bwd_col_edges":
+        fn = lambda: GAT.gat_backward_col_edges(0.2, cp, ri, feat, ac, rowpack, gout)
+        nbytes = 4.0 * nnz * (1 + 4 * H + HF) + 4.0 * n * (1 + HF + 3 * H)
+    elif a.op == "gat_bwd_row_sum":
+        pos = GAT.invert_permutation(pm)
+        eg = torch.randn(nnz, H, device=dev, generator=gen)
+        fn = lambda: GAT.gat_backward_row_sum(g.row_ptr, pos, eg)
+        nbytes = 4.0 * nnz * (1 + H) + 4.0 * n * (1 + H)
+    elif a.op == "gat_bwd_pack":
+        out0 = GAT.gat_forward(ar, ac, g.row_ptr, g.col_ind, 0.2, feat)[0]
+        fn = lambda: GAT.gat_backward_pack(out0, gout, ar, m, s)
+        nbytes = 4.0 * n * (2 * HF + 7 * H)
     elif a.op == "csr2csc":
         fn = lambda: T.csr2csc(g.row_ptr, g.col_ind)
         passes = (max(1, (n - 1).bit_length()) + 7) // 8

@@ -39,8 +39,11 @@ def check_status(dev=None) -> None:
 
 
 def supported(m: int, n: int, k: int, a: torch.Tensor) -> bool:
-    return (enabled and a.is_cuda and a.dtype == F32 and a.is_contiguous()
-            and a.data_ptr() % 16 == 0 and bool(capi.lib().gnn_gemm_tf32x3_supported(m, n, k)))
+    """Whether ``gemm_any_k`` takes an (m, k) x (k, n) product of ``a``'s kind: fp32 on a GPU.
+    (The kernel itself wants k % 4 == 0 and 16-byte aligned rows; ``gemm_any_k`` pads.)"""
+    k4 = k + (-k) % 4
+    return (enabled and a.is_cuda and a.dtype == F32 and m > 0
+            and bool(capi.lib().gnn_gemm_tf32x3_supported(m, n, k4)))
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool) -> torch.Tensor:
@@ -59,6 +62,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool) -> torch.Tensor:
         capi.call("gnn_gemm_tf32x3", capi.ptr(a), capi.ptr(b), int(b_is_n_by_k), capi.ptr(out), M, N, K,
                   capi.ptr(ws), ws.numel(), capi.ptr(_status_word(dev)), capi.stream_ptr(dev))
     return out
+
+
+def gemm_any_k(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool) -> torch.Tensor:
+    """``gemm`` for any inner dimension: TMA reads rows whose length is a multiple of 4 floats,
+    so other lengths (an input width of 602, a gradient with 47 columns) are padded with zero
+    columns first -- one copy of ``a``, far cheaper than leaving the product to an fp32 SIMT GEMM."""
+    pad = (-a.shape[1]) % 4
+    if pad or a.data_ptr() % 16 or not a.is_contiguous():
+        a = torch.nn.functional.pad(a, (0, pad))
+        b = torch.nn.functional.pad(b, (0, pad) if b_is_n_by_k else (0, 0, 0, pad))
+    return gemm(a, b.contiguous(), b_is_n_by_k)
 
 
 def gemm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
@@ -90,7 +104,7 @@ class _MatmulFunction(torch.autograd.Function):
         w = w.contiguous()
         ctx.save_for_backward(x, w)
         ctx.w_is_out_by_in = w_is_out_by_in
-        return gemm(x, w, w_is_out_by_in)
+        return gemm_any_k(x, w, w_is_out_by_in)
 
     @staticmethod
     def backward(ctx, g):
@@ -101,7 +115,7 @@ class _MatmulFunction(torch.autograd.Function):
             # grad_x = g @ w^T (w given K x N) or g @ w (w given N x K)
             n_out = g.shape[1]
             if supported(g.shape[0], x.shape[1], n_out, g):
-                gx = gemm(g, w, not ctx.w_is_out_by_in)
+                gx = gemm_any_k(g, w, not ctx.w_is_out_by_in)
             else:
                 gx = g @ (w if ctx.w_is_out_by_in else w.t())
         if ctx.needs_input_grad[1]:
@@ -118,14 +132,14 @@ def matmul_tf32x3(x, w):
 
 
 def project(x, w):
-    """x @ w, on the tensor cores when the shape allows (K % 4 == 0, contiguous CUDA fp32)."""
-    if x.dim() == 2 and supported(x.shape[0], w.shape[1], w.shape[0], x.contiguous()):
+    """x @ w, on the tensor cores for CUDA fp32 matrices."""
+    if x.dim() == 2 and supported(x.shape[0], w.shape[1], w.shape[0], x):
         return matmul_tf32x3(x, w)
     return torch.matmul(x, w)
 
 
 def linear(x, weight):
     """nn.Linear without bias: x (M,K) @ weight(N,K)^T."""
-    if x.dim() == 2 and supported(x.shape[0], weight.shape[0], weight.shape[1], x.contiguous()):
+    if x.dim() == 2 and supported(x.shape[0], weight.shape[0], weight.shape[1], x):
         return _MatmulFunction.apply(x, weight, True)
     return torch.nn.functional.linear(x, weight)

@@ -42,11 +42,11 @@ def test_gemm_large_magnitude_spread(cuda):
     assert_close(out, a.double() @ b.double(), "gemm spread", scale_atol=True)
 
 
-def test_matmul_autograd_and_fallback(cuda):
+def test_matmul_autograd_any_inner_dimension(cuda):
     from ae_mlsys_gnn_b200.operators import dense
 
     gen = torch.Generator().manual_seed(9)
-    for K in (64, 30):  # 30 is not a multiple of 4: falls back to the framework GEMM
+    for K in (64, 30, 47):  # 30 and 47 are not multiples of 4: the operands are padded with zero columns
         x = torch.randn(700, K, generator=gen)
         w = torch.randn(K, 48, generator=gen)
         g = torch.randn(700, 48, generator=gen)
@@ -59,6 +59,12 @@ def test_matmul_autograd_and_fallback(cuda):
         lin_w = torch.randn(48, K, generator=gen)
         out = dense.linear(x.to(cuda), lin_w.to(cuda))
         assert_close(out, x.double() @ lin_w.double().t(), "linear", scale_atol=True)
+    # an output width of 47: the input gradient g (M x 47) @ w^T has the odd inner dimension
+    x, w, g = torch.randn(5000, 64, generator=gen), torch.randn(64, 47, generator=gen), torch.randn(5000, 47, generator=gen)
+    xd, wd = x.to(cuda).requires_grad_(True), w.to(cuda).requires_grad_(True)
+    dense.project(xd, wd).backward(g.to(cuda))
+    assert_close(xd.grad, g.double() @ w.double().t(), "grad_x (47 columns)", scale_atol=True)
+    assert_close(wd.grad, x.double().t() @ g.double(), "grad_w (47 columns)", scale_atol=True)
     dense.check_status()
 
 
