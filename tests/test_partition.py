@@ -210,3 +210,27 @@ def test_partitioned_gat_two_ranks_matches_single(pieces):
     assert_close(results["loss"], loss, "loss")
     for k, gval in results["grads"].items():
         assert_close(gval, st[k].grad, f"grad {k}", scale_atol=True)
+
+
+@pytest.mark.parametrize("pieces", [1, 3])
+def test_partition_transposed_block_index(pieces):
+    """rowsum_parts[c] lists, for every destination row of piece c (gathered order), the
+    positions of its edges inside csc_parts[c], ascending."""
+    from ae_mlsys_gnn_b200.partition import build_partition
+
+    g = power_law_graph(400, 9, seed=4)
+    cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)
+    world = 3
+    for r in range(world):
+        p = build_partition(g.row_ptr, g.col_ind, cp, ri, r, world, pieces=pieces)
+        span = world * p.cn
+        assert len(p.rowsum_parts) == pieces
+        for c, ((_, ri_c), (ptr, pos)) in enumerate(zip(p.csc_parts, p.rowsum_parts)):
+            assert ptr.numel() == span + 1 and int(ptr[-1]) == ri_c.numel() == pos.numel()
+            assert torch.equal(torch.sort(pos.long()).values, torch.arange(pos.numel()))
+            rows_of_pos = ri_c.long()[pos.long()] - c * span
+            seg = ref.rows_of(ptr)
+            assert torch.equal(rows_of_pos, seg)
+            for s in range(span):  # ascending inside every row
+                a, b = int(ptr[s]), int(ptr[s + 1])
+                assert torch.all(pos[a + 1: b] > pos[a: b - 1]) if b - a > 1 else True

@@ -86,22 +86,27 @@ def test_gat_forward_three_way(cuda, kind, H, F):
                                       ("bounded", 4, 128)])
 def test_gat_backward_three_way(cuda, kind, H, F):
     from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
-    from ae_mlsys_gnn_b200.operators.fused_gat import gat_backward, gat_forward
+    from ae_mlsys_gnn_b200.operators.fused_gat import (csr_positions, gat_backward, gat_backward_with_output,
+                                                       gat_forward)
 
     m = _mod("fused_gat_SM")
     g = power_law_graph(1200, 30, seed=3) if kind == "powerlaw" else _bounded_graph(1200, 32, 3)
     ar, ac, x, go = _gat_inputs(g, H, F, 4)
     dv = [t.to(cuda) for t in (ar, ac, g.row_ptr, g.col_ind, x, go)]
     cp, ri, _ = csr2csc(dv[2], dv[3])
-    _, e_max, e_sum = gat_forward(dv[0], dv[1], dv[2], dv[3], 0.2, dv[4])
+    out, e_max, e_sum = gat_forward(dv[0], dv[1], dv[2], dv[3], 0.2, dv[4])
     r = m.gat_backward(0.2, dv[2], dv[3], cp, ri, e_max, e_sum, dv[4], dv[0], dv[1], dv[5])
     b = gat_backward(0.2, dv[2], dv[3], cp, ri, e_max, e_sum, dv[4], dv[0], dv[1], dv[5])
+    # the one-gather backward the autograd nodes use (forward output instead of the row pass)
+    b1 = gat_backward_with_output(0.2, dv[2], dv[3], cp, ri, csr_positions(dv[2], dv[3], cp, ri), e_max, e_sum,
+                                  dv[4], dv[0], dv[1], out, dv[5])
     _, om, os_ = ref.gat_forward(ar, ac, g.row_ptr, g.col_ind, 0.2, x)
     o = ref.gat_backward(0.2, g.row_ptr, g.col_ind, om, os_, x, ar, ac, go)
     torch.cuda.synchronize()
-    for name, rr, bb, oo in zip(("grad_feat", "grad_attn_row", "grad_attn_col"), r, b, o):
+    for name, rr, bb, b1b, oo in zip(("grad_feat", "grad_attn_row", "grad_attn_col"), r, b, b1, o):
         assert_close(rr, oo, f"reference vs oracle: {name}", scale_atol=True)
         assert_close(bb, rr, f"B200 vs reference: {name}", scale_atol=True)
+        assert_close(b1b, rr, f"B200 one-gather vs reference: {name}", scale_atol=True)
 
 
 @pytest.mark.parametrize("n,k,F", [(512, 20, 64), (300, 40, 128), (257, 20, 3), (100, 33, 40), (64, 20, 256)])
