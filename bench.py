@@ -409,10 +409,18 @@ def main():
         g = d["graph"]
         col_ptr, row_ind, _ = csr2csc(g.row_ptr, g.col_ind)
         if world > 1:
-            from ae_mlsys_gnn_b200.partition import PartitionedGAT, build_partition
+            # exchange scheme: "halo" (default) moves only the rows a rank's block references,
+            # "gather" all-gathers every rank's rows
+            if os.environ.get("GNN_B200_EXCHANGE", "halo") == "gather":
+                from ae_mlsys_gnn_b200.partition import PartitionedGAT, build_partition
 
-            part = build_partition(g.row_ptr, g.col_ind, col_ptr, row_ind, rank, world)
-            model = PartitionedGAT(wl["in_dim"], wl["hidden"], wl["heads"], wl["classes"], 1).to(dev)
+                part = build_partition(g.row_ptr, g.col_ind, col_ptr, row_ind, rank, world)
+                model = PartitionedGAT(wl["in_dim"], wl["hidden"], wl["heads"], wl["classes"], 1).to(dev)
+            else:
+                from ae_mlsys_gnn_b200.halo import HaloGAT, build_halo_partition
+
+                part = build_halo_partition(g.row_ptr, g.col_ind, col_ptr, row_ind, rank, world)
+                model = HaloGAT(wl["in_dim"], wl["hidden"], wl["heads"], wl["classes"], 1).to(dev)
             x_l = part.pad_rows(part.local_slice(d["x"]))
             y_l = part.local_slice(d["labels"]).contiguous()
             d["x_l"], d["y_l"] = x_l, y_l
@@ -518,7 +526,8 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{wl['name']}: {wl['desc']}", "nodes": n, "edges": nnz,
-                       "parallelism": f"row-block x{world}" if world > 1 else "single GPU",
+                       "parallelism": (f"row-block x{world}, {os.environ.get('GNN_B200_EXCHANGE', 'halo')} exchange"
+                                       if world > 1 else "single GPU"),
                        "l2": "flushed between steps (256 MB write)" if flush else "inputs exceed L2 (126 MB)",
                        "seed": args.seed},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roof, "cpu_baseline": cpu,

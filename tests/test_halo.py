@@ -1,0 +1,124 @@
+"""Halo partition (only the rows a block references are exchanged), on CPU: gloo ranks with
+the oracle standing in for the CUDA kernels.  Checked: the plans (who sends which rows to
+whom), the id remapping into [own | halo], the all-to-all exchanges in both directions, and
+that a partitioned GAT model reproduces the single-process logits, loss and gradients."""
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import ops as ref
+from tests.test_partition import OracleKernels
+from tests.util import assert_close, power_law_graph
+
+
+@pytest.mark.parametrize("world", [1, 2, 5])
+def test_halo_plans_cover_the_graph(world):
+    from ae_mlsys_gnn_b200.halo import build_halo_partition
+
+    g = power_law_graph(500, 12, seed=2)
+    cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)
+    parts = [build_halo_partition(g.row_ptr, g.col_ind, cp, ri, r, world) for r in range(world)]
+    assert sum(p.n_local for p in parts) == g.n
+    assert sum(p.col_ind.numel() for p in parts) == g.nnz == sum(p.row_ind.numel() for p in parts)
+    rp = g.row_ptr.long()
+    for r, p in enumerate(parts):
+        lo, hi = p.bounds[r], p.bounds[r + 1]
+        for plan, ptr, idx, gptr, gidx in ((p.fwd, p.row_ptr, p.col_ind, g.row_ptr, g.col_ind),
+                                           (p.bwd, p.col_ptr, p.row_ind, cp, ri)):
+            # what this rank receives from q is what q sends to it, in the same order
+            for q, other in enumerate(parts):
+                oplan = other.fwd if plan is p.fwd else other.bwd
+                assert plan.recv_splits[q] == oplan.send_splits[r]
+            # extended-space ids decode back to the global ids of the block's edges
+            halo_global = []
+            for q, other in enumerate(parts):
+                oplan = other.fwd if plan is p.fwd else other.bwd
+                off = sum(oplan.send_splits[:r])
+                halo_global.append(oplan.send_idx[off: off + oplan.send_splits[r]] + other.bounds[q])
+            table = torch.cat([torch.arange(lo, hi)] + halo_global)
+            e0, e1 = int(gptr.long()[lo]), int(gptr.long()[hi])
+            assert torch.equal(table[idx.long()], gidx.long()[e0:e1])
+            assert torch.equal(ptr.long(), gptr.long()[lo: hi + 1] - e0)
+            assert int(idx.max()) < p.n_local + plan.n_halo if idx.numel() else True
+        # transposed index of the local CSC
+        n_ext = p.n_local + p.bwd.n_halo
+        assert p.rs_ptr.numel() == n_ext + 1 and int(p.rs_ptr[-1]) == p.row_ind.numel()
+        assert torch.equal(p.row_ind.long()[p.rs_pos.long()], ref.rows_of(p.rs_ptr))
+
+
+def _worker(rank, world, port, results, recompute):
+    import os
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ae_mlsys_gnn_b200.halo import HaloGAT, build_halo_partition, halo_exchange, halo_return_sum
+
+        torch.manual_seed(0)
+        g = power_law_graph(300, 10, seed=3)
+        cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)
+        x = torch.randn(g.n, 12, generator=torch.Generator().manual_seed(1))
+        y = torch.randint(0, 5, (g.n,), generator=torch.Generator().manual_seed(2))
+        part = build_halo_partition(g.row_ptr, g.col_ind, cp, ri, rank, world)
+        # exchange round trip on a tensor whose value is its global row id
+        ids = torch.arange(part.bounds[rank], part.bounds[rank + 1], dtype=torch.float32).view(-1, 1)
+        ext, _ = halo_exchange(ids, part.fwd, part.n_local)
+        lo, hi = part.bounds[rank], part.bounds[rank + 1]
+        e0, e1 = int(g.row_ptr[lo]), int(g.row_ptr[hi])
+        assert torch.equal(ext[part.col_ind.long(), 0].long(), g.col_ind.long()[e0:e1])
+        back = halo_return_sum(torch.ones(part.n_local + part.bwd.n_halo, 1), part.bwd, part.n_local)
+        model = HaloGAT(12, [8], [2], 5, 1, kernels=OracleKernels)
+        for layer in model.gat_layers:
+            layer.recompute_projection = recompute
+        out = model(part, part.local_slice(x))
+        loss = model.loss(part, out, part.local_slice(y))
+        loss.backward()
+        model.all_reduce_grads(world)
+        total = loss.detach().clone()
+        dist.all_reduce(total)
+        outs = [None] * world
+        dist.all_gather_object(outs, out.detach())
+        backs = [None] * world
+        dist.all_gather_object(backs, back)
+        if rank == 0:
+            results["out"] = torch.cat(outs)
+            results["back"] = torch.cat(backs)
+            results["loss"] = total
+            results["grads"] = {k: p.grad.clone() for k, p in model.named_parameters()}
+            results["state"] = {k: v.clone() for k, v in model.state_dict().items()}
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("world,recompute", [(2, False), (3, True)])
+def test_halo_gat_matches_single(world, recompute):
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, port, results, recompute), nprocs=world, join=True)
+
+    g = power_law_graph(300, 10, seed=3)
+    cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)
+    # every node got 1 from its owner plus 1 from every other rank that has it in its backward halo
+    assert results["back"].min() >= 1 and results["back"].max() <= world
+    x = torch.randn(g.n, 12, generator=torch.Generator().manual_seed(1))
+    y = torch.randint(0, 5, (g.n,), generator=torch.Generator().manual_seed(2))
+    st = {k: v.double().requires_grad_(True) for k, v in results["state"].items()}
+    h = ref.gat_layer_dgl(g.row_ptr, g.col_ind, x.double(), st["gat_layers.0.W"], st["gat_layers.0.attn_l"],
+                          st["gat_layers.0.attn_r"], 0.2).flatten(1)
+    h = torch.nn.functional.elu(h)
+    out = ref.gat_layer_dgl(g.row_ptr, g.col_ind, h, st["gat_layers.1.W"], st["gat_layers.1.attn_l"],
+                            st["gat_layers.1.attn_r"], 0.2).mean(1)
+    loss = torch.nn.functional.cross_entropy(out, y)
+    loss.backward()
+    assert_close(results["out"], out, "partitioned logits")
+    assert_close(results["loss"], loss, "loss")
+    for k, gval in results["grads"].items():
+        assert_close(gval, st[k].grad, f"grad {k}", scale_atol=True)

@@ -1,5 +1,6 @@
 """Partitioned GAT on real GPUs (skipped with fewer than two): NCCL ranks running the
-CUDA kernels must reproduce the single-GPU model's logits, loss and gradients."""
+CUDA kernels must reproduce the single-GPU model's logits, loss and gradients, with both
+exchange schemes (all-gather of every rank's rows; halo: only the rows a block references)."""
 import os
 import socket
 
@@ -20,7 +21,7 @@ def _inputs():
     return g, x, y
 
 
-def _worker(rank, world, port, results):
+def _worker(rank, world, port, results, exchange="gather"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -35,19 +36,29 @@ def _worker(rank, world, port, results):
         g, x, y = _inputs()
         g = g.to(dev)
         cp, ri, _ = csr2csc(g.row_ptr, g.col_ind)
-        part = build_partition(g.row_ptr, g.col_ind, cp, ri, rank, world, pieces=1 if world == 2 else 3)
-        model = PartitionedGAT(20, [16, 16], [4, 4], 6, 1).to(dev)
+        if exchange == "halo":
+            from ae_mlsys_gnn_b200.halo import HaloGAT, build_halo_partition
+
+            part = build_halo_partition(g.row_ptr, g.col_ind, cp, ri, rank, world)
+            model = HaloGAT(20, [16, 16], [4, 4], 6, 1).to(dev)
+            max_n = max(part.bounds[r + 1] - part.bounds[r] for r in range(world))
+        else:
+            part = build_partition(g.row_ptr, g.col_ind, cp, ri, rank, world, pieces=1 if world == 2 else 3)
+            model = PartitionedGAT(20, [16, 16], [4, 4], 6, 1).to(dev)
+            max_n = part.max_n
         out = model(part, part.pad_rows(part.local_slice(x.to(dev))))
         loss = model.loss(part, out, part.local_slice(y.to(dev)))
         loss.backward()
         model.all_reduce_grads(world)
         total = loss.detach().clone()
         dist.all_reduce(total)
-        gathered = torch.empty(world * part.max_n, out.shape[1], device=dev)
-        dist.all_gather_into_tensor(gathered, out.detach().contiguous())
+        padded = out.detach().new_zeros(max_n, out.shape[1])
+        padded[: out.shape[0]] = out.detach()
+        gathered = torch.empty(world * max_n, out.shape[1], device=dev)
+        dist.all_gather_into_tensor(gathered, padded)
         torch.cuda.synchronize()
         if rank == 0:
-            full = torch.cat([gathered[r * part.max_n: r * part.max_n + part.bounds[r + 1] - part.bounds[r]]
+            full = torch.cat([gathered[r * max_n: r * max_n + part.bounds[r + 1] - part.bounds[r]]
                               for r in range(world)])  # plain rank-major gather of the outputs
             results["out"] = full.cpu()
             results["loss"] = total.cpu()
@@ -58,8 +69,9 @@ def _worker(rank, world, port, results):
 
 
 @pytest.mark.timeout(600)
+@pytest.mark.parametrize("exchange", ["gather", "halo"])
 @pytest.mark.parametrize("world", [2, 4])
-def test_partitioned_gat_matches_single_gpu(cuda, world):
+def test_partitioned_gat_matches_single_gpu(cuda, world, exchange):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from ae_mlsys_gnn_b200.models import GAT
@@ -70,7 +82,7 @@ def test_partitioned_gat_matches_single_gpu(cuda, world):
     port = s.getsockname()[1]
     s.close()
     results = mp.Manager().dict()
-    mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, results, exchange), nprocs=world, join=True)
 
     g, x, y = _inputs()
     g = g.to(cuda)
