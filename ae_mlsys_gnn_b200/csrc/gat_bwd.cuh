@@ -16,6 +16,11 @@
 //
 // Both passes are deterministic (no atomics): split segments are merged in
 // chunk order by one warp.
+//
+// A caller that kept the forward output does not need the row pass: S[r] is then
+// <G[r], out[r]> (node-wise, gat_bwd_edges.cu), the column pass runs with EDGES and stores
+// a(r,c) d(r,c) (<G[r],h[c]> - S[r]) for every edge, and grad_attn_row is the per-row sum of
+// those E x H values -- one gather of feature rows per edge instead of two.
 #pragma once
 #include "wgather.cuh"
 

@@ -16,7 +16,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-REFERENCE = os.environ.get("GNN_REFERENCE_ROOT", "/root/reference")
+REFERENCE = os.environ.get("GNN_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
 
 # module name (as bound by the reference) -> sources relative to <reference>/src
 MODULES = {

@@ -16,7 +16,9 @@ race-free and in-bounds:
     buffer with 32 spare rows; F % 32 == 0;
   * gaussian writes out of bounds unless E % 32 == 0 (gmmconv.cu:36,45) -> E % 32 == 0.
 GaussianBp, u_add_v backward and the EdgeConv backward are not compared: the reference
-kernels are wrong or racy there.
+kernels are wrong or racy there (GaussianBp reduces nothing and mixes dimensions,
+gmmconv.cu:154-184; u_add_v backward never zero-fills grad_col, u_add_v.cu:87; the EdgeConv
+backward scatters without clearing its output, fused_edgeconv.cu:184-185).
 """
 import numpy as np
 import pytest
