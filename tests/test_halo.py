@@ -94,7 +94,7 @@ def _worker(rank, world, port, results, recompute):
 
 
 @pytest.mark.timeout(300)
-@pytest.mark.parametrize("world,recompute", [(2, False), (3, True)])
+@pytest.mark.parametrize("world,recompute", [(2, False), (3, True), (8, "auto")])
 def test_halo_gat_matches_single(world, recompute):
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
