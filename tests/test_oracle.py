@@ -63,6 +63,33 @@ def test_gat_backward_matches_autograd(H, F):
     assert_close(gac, ac.grad, "grad_attn_col", rtol=1e-10, atol=1e-12)
 
 
+@pytest.mark.parametrize("H,F", [(1, 5), (4, 8)])
+def test_gat_one_gather_backward_identity(H, F):
+    """What the one-gather backward rests on, in fp64 on the CPU: S[r,h] = sum_e a_e <G[r],h[c_e]>
+    equals <G[r], out[r]>, and grad_attn_row / grad_attn_col are the row / column sums of the
+    per-edge logit gradients a_e d_e (g_e - S[r]) (fused_backward_kernel, fused_gat_SM.cu:734-801)."""
+    g = power_law_graph(150, 9, seed=4)
+    gen = torch.Generator().manual_seed(3)
+    ar = torch.randn(g.n, H, generator=gen, dtype=torch.float64)
+    ac = torch.randn(g.n, H, generator=gen, dtype=torch.float64)
+    x = torch.randn(g.n, H, F, generator=gen, dtype=torch.float64)
+    gout = torch.randn(g.n, H, F, generator=gen, dtype=torch.float64)
+    rows, cols = ref.rows_of(g.row_ptr), g.col_ind.long()
+    out, m, s = ref.gat_forward(ar, ac, g.row_ptr, g.col_ind, 0.2, x)
+    e, alpha = ref.gat_alpha(ar, ac, g.row_ptr, g.col_ind, 0.2, m, s)
+    dots = (gout[rows] * x[cols]).sum(-1)
+    S_edges = torch.zeros(g.n, H, dtype=torch.float64).index_add_(0, rows, alpha * dots)
+    S_nodes = (gout * out).sum(-1)
+    assert_close(S_nodes, S_edges, "S from the forward output", rtol=1e-10, atol=1e-12)
+    ge = alpha * (dots - S_nodes[rows])
+    ge = torch.where(e < 0, ge * 0.2, ge)
+    _, gar, gac = ref.gat_backward(0.2, g.row_ptr, g.col_ind, m, s, x, ar, ac, gout)
+    assert_close(torch.zeros(g.n, H, dtype=torch.float64).index_add_(0, rows, ge), gar, "row sums",
+                 rtol=1e-10, atol=1e-12)
+    assert_close(torch.zeros(g.n, H, dtype=torch.float64).index_add_(0, cols, ge), gac, "column sums",
+                 rtol=1e-10, atol=1e-12)
+
+
 def _bitrev5(x):
     return int(f"{x:05b}"[::-1], 2)
 
