@@ -69,9 +69,12 @@ def gemm_any_k(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool) -> torch.Ten
     so other lengths (an input width of 602, a gradient with 47 columns) are padded with zero
     columns first -- one copy of ``a``, far cheaper than leaving the product to an fp32 SIMT GEMM."""
     pad = (-a.shape[1]) % 4
-    if pad or a.data_ptr() % 16 or not a.is_contiguous():
+    if pad:
         a = torch.nn.functional.pad(a, (0, pad))
         b = torch.nn.functional.pad(b, (0, pad) if b_is_n_by_k else (0, 0, 0, pad))
+    a = a.contiguous()
+    if a.data_ptr() % 16:  # a view that starts at an odd offset of its storage
+        a = a.clone()
     return gemm(a, b.contiguous(), b_is_n_by_k)
 
 

@@ -112,3 +112,18 @@ def test_gemm_tn_long_reduction(cuda):
     assert_close(out, exp, "gemm_tn long reduction", scale_atol=True)
     bias = ((out.double() - exp) / exp)[exp.abs() > 0.1 * exp.abs().max()].mean().item()
     assert abs(bias) < 3e-5, f"systematic relative error {bias:.2e}"
+
+
+def test_gemm_misaligned_view(cuda):
+    """An operand that is a view starting 4 bytes into its storage cannot be read by TMA:
+    the operator copies it first."""
+    from ae_mlsys_gnn_b200.operators import dense
+
+    gen = torch.Generator().manual_seed(21)
+    buf = torch.randn(300 * 64 + 1, generator=gen).to(cuda)
+    a = buf[1:].view(300, 64)
+    assert a.data_ptr() % 16 != 0
+    w = torch.randn(64, 40, generator=gen).to(cuda)
+    out = dense.gemm_any_k(a, w, False)
+    dense.check_status()
+    assert_close(out, a.double() @ w.double(), "gemm on a misaligned view", scale_atol=True)
