@@ -122,3 +122,35 @@ def test_halo_gat_matches_single(world, recompute):
     assert_close(results["loss"], loss, "loss")
     for k, gval in results["grads"].items():
         assert_close(gval, st[k].grad, f"grad {k}", scale_atol=True)
+
+
+def test_halo_plans_with_empty_blocks_and_isolated_nodes():
+    """A star graph: one hub row holds almost all edges, so some ranks own no rows at all and
+    most nodes are referenced by nobody.  The plans must stay consistent."""
+    from ae_mlsys_gnn_b200.graphs import Graph
+    from ae_mlsys_gnn_b200.halo import build_halo_partition
+
+    n = 64
+    deg = torch.zeros(n, dtype=torch.long)
+    deg[5] = 40          # the hub: in-edges from nodes 10..49
+    deg[60] = 2          # a tail row
+    rp = torch.zeros(n + 1, dtype=torch.int32)
+    rp[1:] = torch.cumsum(deg, 0).to(torch.int32)
+    ci = torch.cat([torch.arange(10, 50), torch.tensor([5, 63])]).to(torch.int32)
+    g = Graph(n, rp, ci)
+    cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)
+    world = 4
+    parts = [build_halo_partition(g.row_ptr, g.col_ind, cp, ri, r, world) for r in range(world)]
+    assert sum(p.n_local for p in parts) == n
+    for r, p in enumerate(parts):
+        for q, other in enumerate(parts):
+            assert p.fwd.recv_splits[q] == other.fwd.send_splits[r]
+            assert p.bwd.recv_splits[q] == other.bwd.send_splits[r]
+        assert p.fwd.send_splits[r] == 0 and p.bwd.recv_splits[r] == 0
+        assert p.row_ptr.numel() == p.n_local + 1 == p.col_ptr.numel()
+        if p.col_ind.numel():
+            assert int(p.col_ind.max()) < p.n_local + p.fwd.n_halo
+        if p.row_ind.numel():
+            assert int(p.row_ind.max()) < p.n_local + p.bwd.n_halo
+        assert p.rs_ptr.numel() == p.n_local + p.bwd.n_halo + 1
+    assert sum(p.col_ind.numel() for p in parts) == g.nnz == sum(p.row_ind.numel() for p in parts)
