@@ -11,6 +11,7 @@
 // position in the CSC is the inverse of csr2csc's permutation, a property of the graph.
 //
 //   gnn_gat_bwd_pack      rowpack[r] = {attn_row[r], max[r], 1/sum[r], S[r]}   (node-wise)
+//   gnn_gat_bwd_pack_elu  the same, with the backward of an ELU on the layer's output folded in
 //   gnn_gat_bwd_row_sum   grad_attn_row[r,h] = sum over CSR edges e of row r of
 //                         edge_grad[csr_pos[e], h]   (edge-balanced, deterministic)
 //   gnn_invert_permutation
@@ -35,30 +36,46 @@ __global__ void invert_permutation_kernel(const int* __restrict__ perm, int64_t 
   if (i < n) inv[perm[i]] = (int)i;
 }
 
-// One warp per row.  VEC: H*F is a multiple of 4 and both matrices are 16-byte aligned.
-template <bool VEC>
+// One warp per row.  VEC: H*F is a multiple of 4 and the matrices are 16-byte aligned.
+// ELU: `gout` is the gradient with respect to elu(out) (the activation a model applies to the
+// layer's output); the kernel first turns it into the gradient with respect to out,
+//     g = gout * (out > 0 ? 1 : alpha * exp(out)),
+// stores it in grad_pre (the operand the column pass gathers) and uses it for S -- the
+// framework's separate elu-backward pass over the same two matrices disappears.
+template <bool VEC, bool ELU>
 __global__ void __launch_bounds__(kThreadsPerCta)
 pack_kernel(int64_t n_rows, const float* __restrict__ out, const float* __restrict__ gout,
             const float* __restrict__ attn_row, const float* __restrict__ edge_max,
-            const float* __restrict__ edge_sum, int H, int F, float* __restrict__ rowpack) {
+            const float* __restrict__ edge_sum, int H, int F, float alpha, float* __restrict__ grad_pre,
+            float* __restrict__ rowpack) {
   const int lane = threadIdx.x & 31;
   const int64_t r = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
   if (r >= n_rows) return;
   const float* o = out + (size_t)r * H * F;
   const float* g = gout + (size_t)r * H * F;
+  float* gp = ELU ? grad_pre + (size_t)r * H * F : nullptr;
   float* rp = rowpack + (size_t)r * 4 * H;
+  auto pre = [&](float ov, float gv) { return ELU ? gv * (ov > 0.f ? 1.f : alpha * expf(ov)) : gv; };
   for (int h = 0; h < H; ++h) {
     float acc = 0.f;
     if (VEC && F % 4 == 0) {
       const float4* o4 = reinterpret_cast<const float4*>(o + (size_t)h * F);
       const float4* g4 = reinterpret_cast<const float4*>(g + (size_t)h * F);
       for (int i = lane; i < F / 4; i += 32) {
-        const float4 a = __ldg(o4 + i), b = __ldg(g4 + i);
+        const float4 a = __ldg(o4 + i);
+        float4 b = __ldg(g4 + i);
+        b.x = pre(a.x, b.x); b.y = pre(a.y, b.y); b.z = pre(a.z, b.z); b.w = pre(a.w, b.w);
+        if (ELU) reinterpret_cast<float4*>(gp + (size_t)h * F)[i] = b;
         acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc);
         acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
       }
     } else {
-      for (int i = lane; i < F; i += 32) acc = fmaf(__ldg(o + (size_t)h * F + i), __ldg(g + (size_t)h * F + i), acc);
+      for (int i = lane; i < F; i += 32) {
+        const float a = __ldg(o + (size_t)h * F + i);
+        const float b = pre(a, __ldg(g + (size_t)h * F + i));
+        if (ELU) gp[(size_t)h * F + i] = b;
+        acc = fmaf(a, b, acc);
+      }
     }
     acc = warp_sum(acc);
     if (lane == 0) {
@@ -222,22 +239,43 @@ extern "C" int gnn_invert_permutation(const int* perm, int64_t n, int* inv, cuda
   return check_launch("gnn_invert_permutation");
 }
 
+namespace {
+int launch_pack(const char* what, int64_t n_rows, const float* out, const float* grad_out, const float* attn_row,
+                const float* edge_max, const float* edge_sum, int H, int F, bool elu, float alpha,
+                float* grad_pre, float* rowpack, cudaStream_t stream) {
+  if (n_rows < 0 || H <= 0 || F <= 0) return bad("gnn_gat_bwd_pack: bad size");
+  if (n_rows == 0) return GNN_OK;
+  if (!out || !grad_out || !attn_row || !edge_max || !edge_sum || !rowpack || (elu && !grad_pre))
+    return bad("gnn_gat_bwd_pack: null pointer");
+  const unsigned blocks = (unsigned)((n_rows + kWarpsPerCta - 1) / kWarpsPerCta);
+  const bool vec = aligned16(out) && aligned16(grad_out) && (!elu || aligned16(grad_pre)) &&
+                   ((int64_t)H * F) % 4 == 0;
+#define GNN_PACK(V, E)                                                                                     \
+  pack_kernel<V, E><<<blocks, kThreadsPerCta, 0, stream>>>(n_rows, out, grad_out, attn_row, edge_max,       \
+                                                          edge_sum, H, F, alpha, grad_pre, rowpack)
+  if (elu) {
+    if (vec) GNN_PACK(true, true); else GNN_PACK(false, true);
+  } else {
+    if (vec) GNN_PACK(true, false); else GNN_PACK(false, false);
+  }
+#undef GNN_PACK
+  return check_launch(what);
+}
+}  // namespace
+
 extern "C" int gnn_gat_bwd_pack(int64_t n_rows, const float* out, const float* grad_out,
                                 const float* attn_row, const float* edge_max, const float* edge_sum,
                                 int H, int F, float* rowpack, cudaStream_t stream) {
-  if (n_rows < 0 || H <= 0 || F <= 0) return bad("gnn_gat_bwd_pack: bad size");
-  if (n_rows == 0) return GNN_OK;
-  if (!out || !grad_out || !attn_row || !edge_max || !edge_sum || !rowpack)
-    return bad("gnn_gat_bwd_pack: null pointer");
-  const unsigned blocks = (unsigned)((n_rows + kWarpsPerCta - 1) / kWarpsPerCta);
-  const bool vec = aligned16(out) && aligned16(grad_out) && ((int64_t)H * F) % 4 == 0;
-  if (vec)
-    pack_kernel<true><<<blocks, kThreadsPerCta, 0, stream>>>(n_rows, out, grad_out, attn_row, edge_max,
-                                                            edge_sum, H, F, rowpack);
-  else
-    pack_kernel<false><<<blocks, kThreadsPerCta, 0, stream>>>(n_rows, out, grad_out, attn_row, edge_max,
-                                                             edge_sum, H, F, rowpack);
-  return check_launch("gnn_gat_bwd_pack");
+  return launch_pack("gnn_gat_bwd_pack", n_rows, out, grad_out, attn_row, edge_max, edge_sum, H, F, false, 0.f,
+                     nullptr, rowpack, stream);
+}
+
+extern "C" int gnn_gat_bwd_pack_elu(int64_t n_rows, const float* out, const float* grad_act,
+                                    const float* attn_row, const float* edge_max, const float* edge_sum,
+                                    int H, int F, float alpha, float* grad_pre, float* rowpack,
+                                    cudaStream_t stream) {
+  return launch_pack("gnn_gat_bwd_pack_elu", n_rows, out, grad_act, attn_row, edge_max, edge_sum, H, F, true,
+                     alpha, grad_pre, rowpack, stream);
 }
 
 extern "C" int gnn_gat_bwd_row_sum_workspace_bytes(int64_t nnz, int H, size_t* bytes) {

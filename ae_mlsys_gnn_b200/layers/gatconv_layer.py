@@ -43,18 +43,28 @@ class _GATBase(nn.Module):
 class GATConv(_GATBase):
     """``fuse_scores`` (default on) computes attn_row / attn_col and their gradients with
     the one-pass score kernels inside the same autograd node as the fused op; off, the
-    layer is composed exactly like the reference's (framework ops + fused_gat_op)."""
+    layer is composed exactly like the reference's (framework ops + fused_gat_op).
+
+    ``activation`` (None, as in the reference layer, or "elu"): applied to the layer's output;
+    inside the fused node its backward costs no pass of its own."""
 
     fuse_scores = True
+
+    def __init__(self, in_feats, out_feats, num_heads, negative_slope=0.2, activation=None):
+        super().__init__(in_feats, out_feats, num_heads, negative_slope)
+        if activation not in (None, "elu"):
+            raise ValueError("activation must be None or 'elu'")
+        self.activation = activation
 
     def forward(self, row_ptr, col_ind, col_ptr, row_ind, feat, save_memory=True):
         if self.fuse_scores and fused_scores_supported(self.num_heads, self.out_feats):
             h = dense.project(feat, self.W).view(-1, self.num_heads, self.out_feats)
             return fused_gat_layer_op(h, self.attn_l, self.attn_r, row_ptr, col_ind, col_ptr,
-                                      row_ind, self.negative_slope)
+                                      row_ind, self.negative_slope, self.activation)
         h, attn_row, attn_col = self.project(feat)
-        return fused_gat_op(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind,
-                            self.negative_slope, h, save_memory)
+        out = fused_gat_op(attn_row, attn_col, row_ptr, col_ind, col_ptr, row_ind,
+                           self.negative_slope, h, save_memory)
+        return torch.nn.functional.elu(out) if self.activation == "elu" else out
 
 
 class GATConv_stash(_GATBase):

@@ -28,8 +28,11 @@ class GAT(nn.Module):
         if isinstance(hidden, int):
             hidden = [hidden] * len(heads)
         dims_in = [in_dim] + [h * f for h, f in zip(heads, hidden)]
+        # the hidden layers apply the activation themselves (elementwise, so before or after
+        # the head concatenation is the same thing)
         self.gat_layers = nn.ModuleList(
-            [GATConv(dims_in[i], hidden[i], heads[i], negative_slope) for i in range(len(heads))])
+            [GATConv(dims_in[i], hidden[i], heads[i], negative_slope, activation)
+             for i in range(len(heads))])
         self.gat_layers.append(GATConv(dims_in[-1], num_classes, out_heads, negative_slope))
         self.activation = activation
 
@@ -37,8 +40,6 @@ class GAT(nn.Module):
         h = inputs
         for layer in self.gat_layers[:-1]:
             h = layer(row_ptr, col_ind, col_ptr, row_ind, h, save_memory).flatten(1)
-            if self.activation == "elu":
-                h = F.elu(h)
         return self.gat_layers[-1](row_ptr, col_ind, col_ptr, row_ind, h, save_memory).mean(1)
 
 

@@ -207,6 +207,26 @@ def gat_backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=None):
     return rowpack
 
 
+def gat_backward_pack_elu(out, grad_act, attn_row, edge_max, edge_sum, alpha=1.0):
+    """(grad_pre, rowpack) for a layer output that went through ELU: ``grad_act`` is the gradient
+    with respect to elu(out); grad_pre = grad_act * elu'(out) is what the column pass takes."""
+    dev = out.device
+    capi.require(out, F32, "out", 3)
+    capi.require(grad_act, F32, "grad_act", 3, dev)
+    n, H, F = edge_max.shape[0], out.shape[1], out.shape[2]
+    for name, t in (("attn_row", attn_row), ("edge_max", edge_max), ("edge_sum", edge_sum)):
+        capi.require(t, F32, name, 2, dev)
+    if out.shape[0] < n or grad_act.shape[0] < n or attn_row.shape[0] < n:
+        raise ValueError("out / grad_act / attn_row need at least one row per edge_max row")
+    grad_pre = torch.empty((n, H, F), dtype=F32, device=dev)
+    rowpack = torch.empty((n, 4, H), dtype=F32, device=dev)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_bwd_pack_elu", n, capi.ptr(out), capi.ptr(grad_act), capi.ptr(attn_row),
+                  capi.ptr(edge_max), capi.ptr(edge_sum), H, F, float(alpha), capi.ptr(grad_pre),
+                  capi.ptr(rowpack), capi.stream_ptr(dev))
+    return grad_pre, rowpack
+
+
 def gat_backward_col_edges(negative_slope, col_ptr, row_ind, in_feat, attn_col, rowpack, grad_out,
                            pad_to=None):
     """``gat_backward_col`` that also returns edge_grad (E, H): the gradient of every edge
@@ -336,13 +356,21 @@ def gat_backward_with_output(negative_slope, row_ptr, col_ind, col_ptr, row_ind,
 
 
 def _backward(negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, in_feat,
-              attn_row, attn_col, out, grad_out):
-    """Backward of the autograd nodes: one gather pass when the graph allows, else two."""
+              attn_row, attn_col, out, grad_out, activation=None):
+    """Backward of the autograd nodes: one gather pass when the graph allows, else two.
+    ``activation`` = "elu": ``grad_out`` is the gradient with respect to elu(out)."""
     if one_gather_backward and in_feat.shape[1] <= 8:
         pos = csr_positions(row_ptr, col_ind, col_ptr, row_ind)
         if pos is not None:
+            if activation == "elu":  # the elu backward rides on the per-row pack
+                grad_pre, rowpack = gat_backward_pack_elu(out, grad_out, attn_row, edge_max, edge_sum)
+                grad_feat, grad_attn_col, edge_grad = gat_backward_col_edges(
+                    negative_slope, col_ptr, row_ind, in_feat, attn_col, rowpack, grad_pre)
+                return grad_feat, gat_backward_row_sum(row_ptr, pos, edge_grad), grad_attn_col
             return gat_backward_with_output(negative_slope, row_ptr, col_ind, col_ptr, row_ind, pos,
                                             edge_max, edge_sum, in_feat, attn_row, attn_col, out, grad_out)
+    if activation == "elu":
+        grad_out = grad_out * torch.where(out > 0, torch.ones_like(out), torch.exp(out))
     return gat_backward(negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum,
                         in_feat, attn_row, attn_col, grad_out)
 
@@ -410,7 +438,10 @@ class FusedGATLayerFunction(torch.autograd.Function):
     go through framework elementwise kernels, and grad_h is accumulated in place."""
 
     @staticmethod
-    def forward(ctx, h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind, negative_slope):
+    def forward(ctx, h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind, negative_slope,
+                activation=None):
+        if activation not in (None, "elu"):
+            raise ValueError("activation must be None or 'elu'")
         h = h.contiguous()
         attn_l, attn_r = attn_l.contiguous(), attn_r.contiguous()
         attn_row, attn_col = gat_scores_forward(h, attn_l, attn_r)
@@ -418,7 +449,10 @@ class FusedGATLayerFunction(torch.autograd.Function):
         ctx.save_for_backward(row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, h, attn_row,
                               attn_col, attn_l, attn_r, out)
         ctx.negative_slope = negative_slope
-        return out
+        ctx.activation = activation
+        # with an activation the node returns elu(out) and keeps out: its backward folds the
+        # activation's derivative into the per-row pack instead of a separate pass
+        return torch.nn.functional.elu(out) if activation == "elu" else out
 
     @staticmethod
     def backward(ctx, grad_out):
@@ -426,14 +460,15 @@ class FusedGATLayerFunction(torch.autograd.Function):
          attn_r, out) = ctx.saved_tensors
         grad_feat, gar, gac = _backward(ctx.negative_slope, row_ptr, col_ind, col_ptr, row_ind,
                                         edge_max, edge_sum, h, attn_row, attn_col, out,
-                                        grad_out.contiguous())
+                                        grad_out.contiguous(), ctx.activation)
         gl, gr = gat_scores_backward(h, attn_l, attn_r, gar, gac, grad_feat)
-        return grad_feat, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None
+        return grad_feat, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None, None
 
 
-def fused_gat_layer_op(h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind, negative_slope):
+def fused_gat_layer_op(h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind, negative_slope,
+                       activation=None):
     return FusedGATLayerFunction.apply(h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind,
-                                       negative_slope)
+                                       negative_slope, activation)
 
 
 class FusedGATFunction_SM(torch.autograd.Function):

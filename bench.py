@@ -137,6 +137,8 @@ def algorithmic_bytes(name: str, n: int, e: int, H: int, Fw: int, D: int = 0) ->
         return 4.0 * e * (1 + 4 * H + HF) + 4.0 * n * (1 + HF + 3 * H)
     if name == "gnn_gat_bwd_pack":
         return 4.0 * n * (2 * HF + 7 * H)
+    if name == "gnn_gat_bwd_pack_elu":  # also writes the pre-activation gradient
+        return 4.0 * n * (3 * HF + 7 * H)
     if name == "gnn_gat_bwd_row_sum":
         return 4.0 * e * (1 + H) + 4.0 * n * (1 + H)
     if name == "gnn_edgeconv_fwd":
@@ -192,7 +194,7 @@ class BytesLedger:
             return algorithmic_bytes("gnn_gat_bwd_col", a[2], a[3], a[8], a[9])
         if name == "gnn_gat_bwd_col_edges":
             return algorithmic_bytes(name if a[13] else "gnn_gat_bwd_col", a[2], a[3], a[8], a[9])
-        if name == "gnn_gat_bwd_pack":
+        if name in ("gnn_gat_bwd_pack", "gnn_gat_bwd_pack_elu"):
             return algorithmic_bytes(name, a[0], 0, a[6], a[7])
         if name == "gnn_gat_bwd_row_sum":
             return algorithmic_bytes(name, a[2], a[3], a[5], 1)

@@ -188,6 +188,15 @@ int gnn_gat_bwd_pack(int64_t n_rows, const float* out, const float* grad_out, co
                      const float* edge_max, const float* edge_sum, int H, int F, float* rowpack,
                      cudaStream_t stream);
 
+/* gnn_gat_bwd_pack for a layer whose output went through ELU (alpha) before the loss:
+ * grad_act is the gradient with respect to elu(out); the kernel writes
+ * grad_pre = grad_act * (out > 0 ? 1 : alpha*exp(out)) (the grad_out the column pass takes)
+ * and uses it for S.  Replaces the framework's elu-backward pass over the same matrices
+ * (the reference applies its activations in the model, script/train/train_gatconv_our.py:47-53). */
+int gnn_gat_bwd_pack_elu(int64_t n_rows, const float* out, const float* grad_act, const float* attn_row,
+                         const float* edge_max, const float* edge_sum, int H, int F, float alpha,
+                         float* grad_pre, float* rowpack, cudaStream_t stream);
+
 /* grad_attn_row[r,h] = sum over the CSR edges e of row r of edge_grad[csr_pos[e]*H + h];
  * csr_pos[e] is the position of CSR edge e in the CSC whose column pass filled edge_grad
  * (the inverse of the permutation gnn_csr2csc returns).  Deterministic. */

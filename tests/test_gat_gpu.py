@@ -365,3 +365,57 @@ def test_gat_long_run_of_isolated_nodes(cuda):
     for a, b, e, what in zip(got, two, exp, ("grad_feat", "grad_attn_row", "grad_attn_col")):
         assert_close(a, e, f"{what} vs oracle", scale_atol=True)
         assert_close(b, e, f"{what} two-pass vs oracle", scale_atol=True)
+
+
+# ---- ELU on the layer output, its backward folded into the per-row pack ------------------------
+
+@pytest.mark.parametrize("H,F", [(4, 32), (1, 47), (2, 100)])
+def test_gat_pack_elu(cuda, H, F):
+    from ae_mlsys_gnn_b200.operators import fused_gat as G
+
+    g = power_law_graph(900, 20, seed=17)
+    attn_row, attn_col, feat, gact = _inputs(g, H, F, 18)
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    d = [t.to(cuda) for t in (attn_row, attn_col, feat, gact)]
+    out, m, s = G.gat_forward(d[0], d[1], rp, ci, 0.2, d[2])
+    grad_pre, pack = G.gat_backward_pack_elu(out, d[3], d[0], m, s)
+    o64, g64 = out.double(), d[3].double()
+    exp_pre = g64 * torch.where(o64 > 0, torch.ones_like(o64), torch.exp(o64))
+    assert_close(grad_pre, exp_pre, "grad_pre = grad_act * elu'(out)")
+    assert_close(pack, G.gat_backward_pack(out, exp_pre.float(), d[0], m, s), "rowpack", scale_atol=True)
+
+
+@pytest.mark.parametrize("foreign_csc", [False, True])
+def test_gat_autograd_layer_with_elu(cuda, foreign_csc):
+    """GATConv(activation="elu") against autograd of elu(DGL-style layer); also through the
+    two-pass fallback (a CSC with another row order inside the columns)."""
+    from ae_mlsys_gnn_b200.layers import GATConv
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+
+    torch.manual_seed(1)
+    g = power_law_graph(500, 20, seed=8)
+    layer = GATConv(24, 16, 4, activation="elu").to(cuda)
+    x = torch.randn(g.n, 24)
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    cp, ri, _ = csr2csc(rp, ci)
+    if foreign_csc:
+        ri = ri.clone()
+        for c in range(g.n):
+            a, b = int(cp[c]), int(cp[c + 1])
+            ri[a:b] = ri[a:b].flip(0)
+    xd = x.to(cuda).requires_grad_(True)
+    out = layer(rp, ci, cp, ri, xd)
+    gout = torch.randn(out.shape, generator=torch.Generator().manual_seed(2))
+    out.backward(gout.to(cuda))
+
+    W = layer.W.detach().cpu().double().requires_grad_(True)
+    al = layer.attn_l.detach().cpu().double().requires_grad_(True)
+    ar = layer.attn_r.detach().cpu().double().requires_grad_(True)
+    xr = x.double().requires_grad_(True)
+    eo = torch.nn.functional.elu(ref.gat_layer_dgl(g.row_ptr, g.col_ind, xr, W, al, ar, 0.2))
+    eo.backward(gout.double())
+    assert_close(out, eo, "layer out")
+    assert_close(layer.W.grad, W.grad, "W.grad", scale_atol=True)
+    assert_close(layer.attn_l.grad, al.grad, "attn_l.grad", scale_atol=True)
+    assert_close(layer.attn_r.grad, ar.grad, "attn_r.grad", scale_atol=True)
+    assert_close(xd.grad, xr.grad, "x.grad", scale_atol=True)
