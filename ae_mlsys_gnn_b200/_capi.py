@@ -25,6 +25,7 @@ _SZP = C.POINTER(C.c_size_t)
 PROTOTYPES = {
     "gnn_abi_version": [],
     "gnn_last_error_string": [],
+    "gnn_debug_set_chunk": [_INT],
     "gnn_csr2csc_workspace_bytes": [_I64, _SZP],
     "gnn_csr2csc": [_PTR, _PTR, _I64, _I64, _I64, _PTR, _PTR, _PTR, _PTR, _SZ, _PTR],
     "gnn_gat_fwd_workspace_bytes": [_I64, _INT, _INT, _SZP],

@@ -202,9 +202,14 @@ __device__ __forceinline__ void for_each_piece(const ChunkGeom& g, int chunk_id,
   }
 }
 
+// Chunk length forced by gnn_debug_set_chunk (0: none).  A test hook: it lets small graphs
+// run the chunk lengths that only graphs of 10^8 edges pick by themselves.
+extern int g_chunk_override;
+
 // Host-side choice of the chunk length: aim at ~8 resident waves of warps on
 // 148 SMs, never below one 32-edge batch nor above 4096 positions.
 inline int pick_chunk(int64_t nnz) {
+  if (g_chunk_override > 0) return g_chunk_override;
   const int64_t target_warps = 148LL * 64 * 4;
   int64_t c = (nnz + target_warps - 1) / target_warps;
   c = (c + 31) / 32 * 32;

@@ -51,6 +51,15 @@ typedef struct CUstream_st* cudaStream_t;
 const char* gnn_last_error_string(void);
 int gnn_abi_version(void);
 
+/* Test hook, no counterpart in the reference.  Every edge-balanced kernel cuts the nnz
+ * positions of its segment array into chunks of `chunk` consecutive positions, one warp
+ * each; the length is chosen from nnz (32 below ~1.2 M edges, up to 4096 at 10^8).  This
+ * call forces it for all later calls of the process (chunk = 0 restores the automatic
+ * choice), so that a test can run the long-chunk code paths on a graph small enough for
+ * a CPU oracle.  A multiple of 32 in [32, 4096].  Workspace sizes follow the forced
+ * length: query *_workspace_bytes after setting it.  Not thread-safe against running calls. */
+int gnn_debug_set_chunk(int chunk);
+
 /* ---- csr2csc -----------------------------------------------------------------
  * Replaces transpose.csr2csc (src/csr2csc/csr2csc.cu:7-43, bound in
  * src/csr2csc/csr2csc.cc) and the host SciPy transpose of the training scripts
