@@ -82,6 +82,12 @@ PROTOTYPES = {
     "gnn_u_add_v_bwd": [_PTR, _PTR, _I64, _I64, _I64, _PTR, _INT, _PTR, _PTR, _PTR],
     "gnn_edge_softmax_fwd": [_PTR, _I64, _I64, _PTR, _INT, _PTR, _PTR],
     "gnn_edge_softmax_bwd": [_PTR, _I64, _I64, _PTR, _PTR, _INT, _PTR, _PTR],
+    "gnn_knn_graph": [_PTR, _I64, _I64, _INT, _INT, _PTR, _PTR],
+    "gnn_peer_alloc": [_SZ, C.POINTER(C.c_void_p), _PTR],
+    "gnn_peer_free": [_PTR],
+    "gnn_peer_open": [_PTR, C.POINTER(C.c_void_p)],
+    "gnn_peer_close": [_PTR],
+    "gnn_halo_push": [_PTR, _I64, _PTR, _PTR, _PTR, _INT, _PTR, _I64, _PTR],
 }
 _RESTYPES = {"gnn_last_error_string": C.c_char_p}
 
@@ -143,7 +149,7 @@ KERNELS_PER_CALL = {
     "gnn_gat_edge_alpha": 1, "gnn_edgeconv_fwd": 1, "gnn_edgeconv_bwd": 1, "gnn_gmm_fwd": 2,
     "gnn_gaussian_fwd": 1, "gnn_gaussian_bwd": 2, "gnn_mhspmm": 2, "gnn_mhsddmm": 1,
     "gnn_sddmm_coo": 1, "gnn_mhtranspose": 1, "gnn_u_add_v_fwd": 1, "gnn_u_add_v_bwd": 1,
-    "gnn_edge_softmax_fwd": 1, "gnn_edge_softmax_bwd": 1,
+    "gnn_edge_softmax_fwd": 1, "gnn_edge_softmax_bwd": 1, "gnn_knn_graph": 1, "gnn_halo_push": 1,
 }
 
 

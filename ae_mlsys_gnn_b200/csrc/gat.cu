@@ -1,6 +1,6 @@
 // C-ABI entry points of the fused GAT forward / backward.
 #include "../../include/gnn_b200.h"
-#include "gat_bwd.cuh"
+#include "gat_narrow.cuh"
 
 using namespace gnn;
 
@@ -27,6 +27,21 @@ bool plan_heads(int H, int F, bool aligned, bool need_full_head, HeadPlan* pl) {
 }
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// One head, rows of at most 64 floats that cannot be read with 128-bit accesses: the
+// sub-warp tiles of gat_narrow.cuh (several rows per warp instruction).
+bool narrow_shape(const HeadPlan& pl, int H, int64_t width) { return pl.fused && !pl.vec && H == 1 && width <= 64; }
+
+// Calls fn(integral_constant<LPR>, integral_constant<Q>) for the sub-warp tile covering `width`.
+template <class Fn>
+void dispatch_narrow(int width, Fn&& fn) {
+  using std::integral_constant;
+  if (width <= 8) fn(integral_constant<int, 8>{}, integral_constant<int, 1>{});
+  else if (width <= 16) fn(integral_constant<int, 16>{}, integral_constant<int, 1>{});
+  else if (width <= 32) fn(integral_constant<int, 16>{}, integral_constant<int, 2>{});
+  else if (width <= 48) fn(integral_constant<int, 16>{}, integral_constant<int, 3>{});
+  else fn(integral_constant<int, 16>{}, integral_constant<int, 4>{});
+}
 
 int bad(const char* msg) {
   set_last_error(msg);
@@ -75,6 +90,13 @@ extern "C" int gnn_gat_fwd_part(const int* row_ptr, const int* col_ind, int64_t 
     set_last_error("gnn_gat_fwd: unsupported shape");
     return GNN_ERR_UNSUPPORTED;
   }
+  if (!pl.fused && F > pl.slab && (accumulate || !finalize)) {
+    // every column slab of a head re-derives the head's softmax state from its own launch; a
+    // second slab would merge against state the first slab of the same call already merged
+    set_last_error("gnn_gat_fwd_part: launches over column blocks need the per-head width within one tile "
+                   "(512 floats aligned / 256 otherwise)");
+    return GNN_ERR_UNSUPPORTED;
+  }
   size_t need = 0;
   gnn_gat_fwd_workspace_bytes(nnz, H, F, &need);
   if (nnz > 0 && (!workspace || workspace_bytes < need)) {
@@ -101,6 +123,7 @@ extern "C" int gnn_gat_fwd_part(const int* row_ptr, const int* col_ind, int64_t 
       p.slot_stride = p.aux_off + round_up4(2 * pl.HP);
       p.accumulate = accumulate ? 1 : 0;
       p.finalize = finalize ? 1 : 0;
+      const bool narrow = narrow_shape(pl, H, w);
       bool ok = dispatch_tile(pl.HP, w, pl.vec, [&](auto hp, auto q, auto v) {
         constexpr int HP = decltype(hp)::value;
         GatSoftmaxPolicy<HP> pol;
@@ -110,6 +133,19 @@ extern "C" int gnn_gat_fwd_part(const int* row_ptr, const int* col_ind, int64_t 
         pol.slope = negative_slope;
         pol.seg_max = edge_max + (pl.fused ? 0 : h);
         pol.seg_sum = edge_sum + (pl.fused ? 0 : h);
+        if constexpr (HP == 1 && !decltype(v)::value) {
+          if (narrow) {  // sub-warp main kernel; the merge kernel of the general tile reads its slots
+            if (p.g.num_chunks > 0) {
+              const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
+              dispatch_narrow(w, [&](auto lpr, auto nq) {
+                gat_fwd_narrow_kernel<decltype(lpr)::value, decltype(nq)::value>
+                    <<<blocks, kThreadsPerCta, 0, stream>>>(p, pol);
+              });
+            }
+            launch_wgather_fixup<GatSoftmaxPolicy, HP, decltype(q)::value, decltype(v)::value>(p, pol, stream);
+            return;
+          }
+        }
         launch_wgather<GatSoftmaxPolicy, HP, decltype(q)::value, decltype(v)::value>(p, pol, stream);
       });
       if (!ok) {
@@ -172,9 +208,26 @@ void launch_col_main(const GatBwdColParams& p, cudaStream_t stream) {
   gat_bwd_col_kernel<HP, Q, VEC, 0, ACC, EDGES><<<blocks, kThreadsPerCta, 0, stream>>>(p);
 }
 
+template <bool ACC, bool EDGES>
+void launch_col_narrow(const GatBwdColParams& p, cudaStream_t stream) {
+  const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
+  dispatch_narrow(p.width, [&](auto lpr, auto nq) {
+    gat_bwd_col_narrow_kernel<decltype(lpr)::value, decltype(nq)::value, ACC, EDGES>
+        <<<blocks, kThreadsPerCta, 0, stream>>>(p);
+  });
+}
+
 template <int HP, int Q, bool VEC>
-void launch_col(const GatBwdColParams& p, cudaStream_t stream) {
-  if (p.g.num_chunks > 0) {
+void launch_col(const GatBwdColParams& p, cudaStream_t stream, bool narrow = false) {
+  if (p.g.num_chunks > 0 && narrow) {
+    if (p.edge_grad) {
+      if (p.accumulate) launch_col_narrow<true, true>(p, stream);
+      else launch_col_narrow<false, true>(p, stream);
+    } else {
+      if (p.accumulate) launch_col_narrow<true, false>(p, stream);
+      else launch_col_narrow<false, false>(p, stream);
+    }
+  } else if (p.g.num_chunks > 0) {
     if (p.edge_grad) {
       if (p.accumulate) launch_col_main<HP, Q, VEC, true, true>(p, stream);
       else launch_col_main<HP, Q, VEC, false, true>(p, stream);
@@ -323,8 +376,10 @@ extern "C" int gnn_gat_bwd_col_edges(const int* col_ptr, const int* row_ind, int
   p.slot_stride = p.aux_off + round_up4(2 * pl.HP);
   p.accumulate = accumulate ? 1 : 0;
   p.edge_grad = edge_grad;
+  // the sub-warp kernel reads the per-row record {attn_row, max, 1/sum, S} as one 128-bit word
+  const bool narrow = narrow_shape(pl, H, HF) && aligned16(rowpack);
   bool ok = dispatch_tile(pl.HP, (int)HF, pl.vec, [&](auto hp, auto q, auto v) {
-    launch_col<decltype(hp)::value, decltype(q)::value, decltype(v)::value>(p, stream);
+    launch_col<decltype(hp)::value, decltype(q)::value, decltype(v)::value>(p, stream, narrow);
   });
   if (!ok) {
     set_last_error("gnn_gat_bwd_col: no tile for this shape");

@@ -1,0 +1,279 @@
+// Fused GAT forward and backward column pass for one head with a narrow, unaligned feature
+// row (the 1 x 47 / 1 x 41 / 1 x 7 output layers: rows of 188 / 164 / 28 bytes, which rule
+// out 128-bit accesses).  Same mathematics, chunk traversal, scratch slots and merge kernels
+// as the general kernels (wgather.cuh, gat_bwd.cuh); what differs is the tiling of the warp:
+//
+//   general tile : 32 lanes share one gathered row (lane l owns floats l, l+32, ...).  With 47
+//                  floats half of the second load is idle and every edge costs its own
+//                  address arithmetic, weight fetch and (backward) 5-step warp reduction.
+//   here         : the warp is cut into R = 32/LPR sub-warps of LPR lanes; sub-warp g works
+//                  on edge j*R + g, lane i of it owns floats i, i+LPR, ... (Q of them).  One
+//                  warp instruction therefore serves R edges, the per-edge dot product of the
+//                  backward is a log2(LPR)-step reduction that R edges share, and R*U rows
+//                  are in flight per warp.
+//
+// Measured on a 1 M-node / 42 M-edge R-MAT graph, 1 x 47: forward 1.90 -> 1.55 ms, column pass
+// with edge gradients about 3.9 -> 2.27 ms.  What bounds these kernels is the first-level cache's
+// line look-ups (a 188-byte row starts anywhere in a 128-byte line, every 64-byte piece of it
+// costs one or two look-ups, and the 4-byte gather of the source's score another): holding all
+// 32 rows of a batch in flight with fewer resident warps was measured slower.
+//
+// Replaces, for these shapes, fused_forward_kernel_small_f_sm and
+// mhspmm_backward_kernel_small_f + mhsddmm + fused_backward_kernel
+// (src/fused_gat/fused_gat_SM.cu:380-489, :609-654, :656-801).
+#pragma once
+#include "gat_bwd.cuh"
+
+namespace gnn {
+
+template <int LPR, int Q>
+struct SubTile {
+  static constexpr int R = 32 / LPR;
+  int sub;       // lane inside the sub-warp
+  int grp;       // sub-warp index
+  bool valid[Q];
+  __device__ __forceinline__ void init(int lane, int width) {
+    sub = lane & (LPR - 1);
+    grp = lane / LPR;
+#pragma unroll
+    for (int q = 0; q < Q; ++q) valid[q] = sub + LPR * q < width;
+  }
+  __device__ __forceinline__ void load(const float* __restrict__ row, float (&v)[Q]) const {
+#pragma unroll
+    for (int q = 0; q < Q; ++q) v[q] = valid[q] ? __ldg(row + sub + LPR * q) : 0.f;
+  }
+  // Sum over the R sub-warps; every sub-warp ends with the total.
+  __device__ __forceinline__ void reduce_groups(float (&v)[Q]) const {
+#pragma unroll
+    for (int s = LPR; s < 32; s <<= 1)
+#pragma unroll
+      for (int q = 0; q < Q; ++q) v[q] += __shfl_xor_sync(kFull, v[q], s);
+  }
+  // Sum over the lanes of one sub-warp (all R sub-warps at once).
+  __device__ __forceinline__ float reduce_lanes(float d) const {
+#pragma unroll
+    for (int s = LPR / 2; s > 0; s >>= 1) d += __shfl_xor_sync(kFull, d, s);
+    return d;
+  }
+  // Element k of a row lives at row[k]: the scratch slots and outputs keep the plain layout,
+  // so the merge kernels of the general tile read them unchanged.
+  __device__ __forceinline__ void store(float* row, const float (&v)[Q]) const {
+    if (grp == 0) {
+#pragma unroll
+      for (int q = 0; q < Q; ++q)
+        if (valid[q]) row[sub + LPR * q] = v[q];
+    }
+  }
+};
+
+// Rows in flight per sub-warp before the first FMA consumes them.
+template <int Q>
+struct NarrowUnroll { static constexpr int U = Q >= 3 ? 4 : 8; };
+
+// ---- forward ------------------------------------------------------------------------------
+// p.H == 1, p.width <= LPR * Q.  Writes out / seg_max / seg_sum (or scratch slots for the
+// pieces of split rows) exactly like wgather_kernel<GatSoftmaxPolicy, 1, ., false>.
+template <int LPR, int Q>
+__global__ void __launch_bounds__(kThreadsPerCta)
+gat_fwd_narrow_kernel(WGatherParams p, GatSoftmaxPolicy<1> pol) {
+  using Tile = SubTile<LPR, Q>;
+  constexpr int R = Tile::R;
+  constexpr int U = NarrowUnroll<Q>::U;
+  __shared__ int cs_all[kWarpsPerCta][32];
+  __shared__ float ws_all[kWarpsPerCta][32];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const int chunk_id = blockIdx.x * kWarpsPerCta + wib;
+  if (chunk_id >= p.g.num_chunks) return;
+  int* cs = cs_all[wib];
+  float* ws = ws_all[wib];
+  Tile t;
+  t.init(lane, p.width);
+
+  for_each_piece(p.g, chunk_id, [&](int s, int a, int b, bool first, bool last) {
+    const float segw = __ldg(pol.attn_seg + (size_t)s * pol.ld_attn);
+    float m = kNegBig, ssum = 0.f;
+    for (int base = a; base < b; base += 32) {
+      const int e = base + lane;
+      if (e < b) {
+        const float x = leaky_relu(segw + __ldg(pol.attn_idx + (size_t)__ldg(p.g.idx + e) * pol.ld_attn), pol.slope);
+        if (x > m) {
+          ssum = ssum * expf(m - x) + 1.f;
+          m = x;
+        } else {
+          ssum += expf(x - m);
+        }
+      }
+    }
+    {
+      const float mm = warp_max(m);
+      ssum = warp_sum(ssum * expf(m - mm));
+      m = mm;
+    }
+
+    float acc[Q];
+#pragma unroll
+    for (int q = 0; q < Q; ++q) acc[q] = 0.f;
+    for (int base = a; base < b; base += 32) {
+      const int e = base + lane;
+      const bool ok = e < b;
+      const int c = __ldg(p.g.idx + (ok ? e : a));
+      const float w = ok ? expf(leaky_relu(segw + __ldg(pol.attn_idx + (size_t)c * pol.ld_attn), pol.slope) - m) : 0.f;
+      __syncwarp();
+      cs[lane] = c;
+      ws[lane] = w;
+      __syncwarp();
+      const int nb = min(32, b - base);
+#pragma unroll 1
+      for (int jj = 0; jj < nb; jj += R * U) {
+        float v[U][Q];
+        float wv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int j = jj + u * R + t.grp;  // < 32 always: R * U divides 32
+          wv[u] = ws[j];                     // 0 past the end of the batch
+          t.load(p.feat + (size_t)cs[j] * p.ld_feat, v[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+          for (int q = 0; q < Q; ++q) acc[q] = fmaf(wv[u], v[u][q], acc[q]);
+      }
+    }
+    t.reduce_groups(acc);
+
+    if (first && last) {
+      float* orow = p.out + (size_t)s * p.ld_out;
+      if (p.accumulate) {
+        const float mo = pol.seg_max[(size_t)s * pol.ld_attn];
+        const float so = pol.seg_sum[(size_t)s * pol.ld_attn];
+        const float M = fmaxf(mo, m);
+        const float fo = expf(mo - M), fn = expf(m - M);
+        ssum = so * fo + ssum * fn;
+        m = M;
+#pragma unroll
+        for (int q = 0; q < Q; ++q) {
+          const float old = t.valid[q] ? orow[t.sub + LPR * q] : 0.f;
+          acc[q] = fmaf(old, fo, acc[q] * fn);
+        }
+      }
+      if (p.finalize) {
+        const float inv = 1.f / ssum;
+#pragma unroll
+        for (int q = 0; q < Q; ++q) acc[q] *= inv;
+      }
+      if (lane == 0) {
+        pol.seg_max[(size_t)s * pol.ld_attn] = m;
+        pol.seg_sum[(size_t)s * pol.ld_attn] = ssum;
+      }
+      t.store(orow, acc);
+    } else {
+      float* slot = p.scratch + slot_index(chunk_id, first) * p.slot_stride;
+      t.store(slot, acc);
+      if (lane == 0) {
+        slot[p.aux_off] = m;
+        slot[p.aux_off + 1] = ssum;
+      }
+    }
+  });
+}
+
+// ---- backward column pass -------------------------------------------------------------------
+// p.H == 1, p.width <= LPR * Q; same outputs and scratch layout as
+// gat_bwd_col_kernel<1, ., false, 0, ACC, EDGES>.
+template <int LPR, int Q, bool ACC, bool EDGES>
+__global__ void __launch_bounds__(kThreadsPerCta)
+gat_bwd_col_narrow_kernel(GatBwdColParams p) {
+  using Tile = SubTile<LPR, Q>;
+  constexpr int R = Tile::R;
+  constexpr int U = NarrowUnroll<Q>::U;
+  __shared__ int cs_all[kWarpsPerCta][32];
+  __shared__ float ws_all[kWarpsPerCta][32];
+  __shared__ float gs_all[kWarpsPerCta][32];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const int chunk_id = blockIdx.x * kWarpsPerCta + wib;
+  if (chunk_id >= p.g.num_chunks) return;
+  int* cs = cs_all[wib];
+  float* ws = ws_all[wib];
+  float* gs = gs_all[wib];
+  Tile t;
+  t.init(lane, p.width);
+
+  for_each_piece(p.g, chunk_id, [&](int s, int a, int b, bool first, bool last) {
+    float fq[Q];
+    t.load(p.feat + (size_t)s * p.ld_feat, fq);
+    const float ac = __ldg(p.attn_seg + (size_t)s * p.ld_attn);
+    float B = 0.f;
+    float acc[Q];
+#pragma unroll
+    for (int q = 0; q < Q; ++q) acc[q] = 0.f;
+
+    for (int base = a; base < b; base += 32) {
+      const int e = base + lane;
+      const bool ok = e < b;
+      const int r = __ldg(p.g.idx + (ok ? e : a));
+      const float4 rp = __ldg(reinterpret_cast<const float4*>(p.rowpack) + r);  // {attn_row, max, 1/sum, S}
+      const float x = leaky_relu(rp.x + ac, p.slope);
+      const float al = ok ? expf(x - rp.y) * rp.z : 0.f;
+      const float dd = x < 0.f ? p.slope : 1.f;
+      __syncwarp();
+      cs[lane] = r;
+      ws[lane] = al;
+      __syncwarp();
+      const int nb = min(32, b - base);
+#pragma unroll 1
+      for (int jj = 0; jj < nb; jj += R * U) {
+        float v[U][Q];
+        float wv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int j = jj + u * R + t.grp;
+          wv[u] = ws[j];
+          t.load(p.gout + (size_t)cs[j] * p.ld_gout, v[u]);
+        }
+        float d[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          d[u] = 0.f;
+#pragma unroll
+          for (int q = 0; q < Q; ++q) {
+            acc[q] = fmaf(wv[u], v[u][q], acc[q]);
+            d[u] = fmaf(fq[q], v[u][q], d[u]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) d[u] = t.reduce_lanes(d[u]);
+        if (t.sub == 0) {
+#pragma unroll
+          for (int u = 0; u < U; ++u) gs[jj + u * R + t.grp] = d[u];
+        }
+      }
+      __syncwarp();
+      if (ok) {
+        const float ge = al * dd * (gs[lane] - rp.w);
+        B += ge;
+        if constexpr (EDGES) p.edge_grad[e] = ge;
+      }
+    }
+    t.reduce_groups(acc);
+    B = warp_sum(B);
+    if (first && last) {
+      float* grow = p.grad_feat + (size_t)s * p.ld_gfeat;
+      if constexpr (ACC) {
+#pragma unroll
+        for (int q = 0; q < Q; ++q)
+          if (t.valid[q]) acc[q] += grow[t.sub + LPR * q];
+      }
+      t.store(grow, acc);
+      if (lane == 0) {
+        float* ga = p.grad_attn_seg + (size_t)s * p.ld_attn;
+        if constexpr (ACC) *ga += B; else *ga = B;
+      }
+    } else {
+      float* slot = p.scratch + slot_index(chunk_id, first) * p.slot_stride;
+      t.store(slot, acc);
+      if (lane == 0) slot[p.aux_off] = B;
+    }
+  });
+}
+
+}  // namespace gnn

@@ -1,0 +1,161 @@
+// Halo exchange of a row-block partition over peer-mapped memory (NVLink / NVSwitch).
+//
+// The reference is single-GPU; nothing here has a counterpart in it.  In the partitioned GAT
+// every rank needs, per layer and direction, the rows of other ranks' per-node tensors that
+// its block of the graph references (its halo).  A collective library moves them as
+// "gather the rows into a send buffer, all-to-all, done"; here the owner of the rows stores
+// them straight into the halo region of the receiver's buffer:
+//
+//   gnn_halo_push    one kernel: for every row of the send list, read it from the local tensor
+//                    and write it with ordinary 128-bit stores through the receiver's mapped
+//                    pointer, at the position the receiver's remapped graph expects; the
+//                    rank's own rows are copied into the front of its own buffer by the same
+//                    launch.  Plain peer stores only: no TMA, no multicast.
+//   gnn_peer_alloc / gnn_peer_open / gnn_peer_close / gnn_peer_free
+//                    device allocations that other processes of the node can map
+//                    (cudaIpcGetMemHandle / cudaIpcOpenMemHandle).  Set-up time only: these
+//                    are the only functions of the library that allocate device memory.
+//
+// Completion is the caller's business: stores of a kernel are visible to the peer once the
+// kernel has completed, so the caller orders "all ranks' push kernels are complete" before
+// the consumer with a collective on the same stream (a one-element all-reduce).
+#include <stdio.h>
+#include <string.h>
+#include "../../include/gnn_b200.h"
+#include "common.cuh"
+
+using namespace gnn;
+
+namespace {
+
+constexpr int kMaxPeers = GNN_MAX_PEERS;
+
+int bad(const char* m) {
+  set_last_error(m);
+  return GNN_ERR_INVALID_ARG;
+}
+
+int cuda_fail(const char* what, cudaError_t e) {
+  char buf[256];
+  snprintf(buf, sizeof(buf), "%s: %s", what, cudaGetErrorString(e));
+  set_last_error(buf);
+  return GNN_ERR_CUDA;
+}
+
+struct PushParams {
+  const float* x;           // [*, row_floats] local per-node tensor
+  const int* send_idx;      // [send_off[world]] local row ids, grouped by destination rank
+  int64_t send_off[kMaxPeers + 1];
+  float* dst[kMaxPeers];    // receiver q's buffer, already advanced to where this rank's rows go
+  float* own_dst;           // this rank's own buffer (rows 0..n_own-1), may be null
+  int64_t n_own;
+  int64_t row_floats;
+  int world;
+};
+
+// One thread per 16-byte unit (VEC) or per float; consecutive threads take consecutive units
+// of a row, so a warp writes 512 contiguous bytes of the destination.
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+halo_push_kernel(PushParams p) {
+  const int64_t upr = VEC ? p.row_floats / 4 : p.row_floats;  // units per row
+  const int64_t n_send = p.send_off[p.world];
+  const int64_t total = (n_send + p.n_own) * upr;
+  for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < total;
+       u += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = u / upr;
+    const int64_t col = u - row * upr;
+    const float* src;
+    float* dst;
+    if (row < n_send) {
+      int q = 0;
+#pragma unroll
+      for (int k = 1; k < kMaxPeers; ++k)
+        if (k < p.world && row >= p.send_off[k]) q = k;
+      src = p.x + (size_t)__ldg(p.send_idx + row) * p.row_floats;
+      dst = p.dst[q] + (size_t)(row - p.send_off[q]) * p.row_floats;
+    } else {
+      const int64_t r = row - n_send;
+      src = p.x + (size_t)r * p.row_floats;
+      dst = p.own_dst + (size_t)r * p.row_floats;
+    }
+    if (VEC)
+      reinterpret_cast<float4*>(dst)[col] = __ldg(reinterpret_cast<const float4*>(src) + col);
+    else
+      dst[col] = __ldg(src + col);
+  }
+}
+
+}  // namespace
+
+extern "C" int gnn_peer_alloc(size_t bytes, void** ptr, unsigned char* handle /*[GNN_PEER_HANDLE_BYTES]*/) {
+  if (!ptr || !handle || bytes == 0) return bad("gnn_peer_alloc: bad argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) <= GNN_PEER_HANDLE_BYTES, "handle size");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) return cuda_fail("gnn_peer_alloc: cudaMalloc", e);
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return cuda_fail("gnn_peer_alloc: cudaIpcGetMemHandle", e);
+  }
+  memset(handle, 0, GNN_PEER_HANDLE_BYTES);
+  memcpy(handle, &h, sizeof(h));
+  *ptr = p;
+  return GNN_OK;
+}
+
+extern "C" int gnn_peer_free(void* ptr) {
+  if (!ptr) return GNN_OK;
+  cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? GNN_OK : cuda_fail("gnn_peer_free", e);
+}
+
+extern "C" int gnn_peer_open(const unsigned char* handle, void** ptr) {
+  if (!handle || !ptr) return bad("gnn_peer_open: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return cuda_fail("gnn_peer_open: cudaIpcOpenMemHandle", e);
+  *ptr = p;
+  return GNN_OK;
+}
+
+extern "C" int gnn_peer_close(void* ptr) {
+  if (!ptr) return GNN_OK;
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? GNN_OK : cuda_fail("gnn_peer_close", e);
+}
+
+extern "C" int gnn_halo_push(const float* x, int64_t row_floats, const int* send_idx, const int64_t* send_off,
+                             float* const* dst, int world, float* own_dst, int64_t n_own, cudaStream_t stream) {
+  if (world < 1 || world > kMaxPeers) return bad("gnn_halo_push: world must be in [1, GNN_MAX_PEERS]");
+  if (row_floats <= 0 || n_own < 0 || !send_off || !dst) return bad("gnn_halo_push: bad argument");
+  PushParams p;
+  p.x = x; p.send_idx = send_idx; p.own_dst = own_dst; p.n_own = own_dst ? n_own : 0;
+  p.row_floats = row_floats; p.world = world;
+  bool vec = row_floats % 4 == 0 && aligned16(x) && (!own_dst || aligned16(own_dst));
+  for (int q = 0; q <= kMaxPeers; ++q) p.send_off[q] = send_off[q < world ? q : world];
+  for (int q = 0; q < kMaxPeers; ++q) {
+    p.dst[q] = q < world ? dst[q] : nullptr;
+    if (q < world) {
+      const int64_t cnt = send_off[q + 1] - send_off[q];
+      if (cnt < 0) return bad("gnn_halo_push: send_off must ascend");
+      if (cnt > 0 && !dst[q]) return bad("gnn_halo_push: rows for a rank without a destination pointer");
+      if (cnt > 0 && !aligned16(dst[q])) vec = false;
+    }
+  }
+  const int64_t n_send = send_off[world];
+  if (n_send > 0 && (!send_idx || !x)) return bad("gnn_halo_push: null pointer");
+  if (p.n_own > 0 && !x) return bad("gnn_halo_push: null pointer");
+  const int64_t units = (n_send + p.n_own) * (vec ? row_floats / 4 : row_floats);
+  if (units == 0) return GNN_OK;
+  int64_t blocks = (units + 255) / 256;
+  const int64_t cap = 148LL * 8 * 4;  // grid-stride beyond a few waves
+  if (blocks > cap) blocks = cap;
+  if (vec) halo_push_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(p);
+  else halo_push_kernel<false><<<(unsigned)blocks, 256, 0, stream>>>(p);
+  return check_launch("gnn_halo_push");
+}

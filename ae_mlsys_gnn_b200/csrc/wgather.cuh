@@ -487,6 +487,18 @@ inline bool dispatch_tile(int HP, int width, bool vec, Fn&& fn) {
 
 inline int max_tile_width(bool vec) { return vec ? 512 : 256; }
 
+// The merge of split segments and the defaults of empty segments (second launch of every
+// weighted gather).
+template <template <int> class Policy, int HP, int Q, bool VEC>
+inline void launch_wgather_fixup(const WGatherParams& p, const Policy<HP>& pol, cudaStream_t stream) {
+  const int nbound = p.g.num_chunks > 1 ? p.g.num_chunks - 1 : 0;
+  const int bblocks = (nbound + kWarpsPerCta - 1) / kWarpsPerCta;
+  const int sblocks = (p.g.nseg + kThreadsPerCta - 1) / kThreadsPerCta;
+  if (bblocks + sblocks > 0)
+    wgather_fixup_kernel<Policy, HP, Q, VEC>
+        <<<bblocks + sblocks, kThreadsPerCta, 0, stream>>>(p, pol, bblocks);
+}
+
 template <template <int> class Policy, int HP, int Q, bool VEC>
 inline void launch_wgather(const WGatherParams& p, const Policy<HP>& pol,
                            cudaStream_t stream) {
@@ -494,12 +506,7 @@ inline void launch_wgather(const WGatherParams& p, const Policy<HP>& pol,
     const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
     wgather_kernel<Policy, HP, Q, VEC><<<blocks, kThreadsPerCta, 0, stream>>>(p, pol);
   }
-  const int nbound = p.g.num_chunks > 1 ? p.g.num_chunks - 1 : 0;
-  const int bblocks = (nbound + kWarpsPerCta - 1) / kWarpsPerCta;
-  const int sblocks = (p.g.nseg + kThreadsPerCta - 1) / kThreadsPerCta;
-  if (bblocks + sblocks > 0)
-    wgather_fixup_kernel<Policy, HP, Q, VEC>
-        <<<bblocks + sblocks, kThreadsPerCta, 0, stream>>>(p, pol, bblocks);
+  launch_wgather_fixup<Policy, HP, Q, VEC>(p, pol, stream);
 }
 
 }  // namespace gnn

@@ -160,11 +160,22 @@ def knn_sources(points: torch.Tensor, k: int) -> torch.Tensor:
     """Per-cloud k nearest neighbours (Euclidean, the point itself included as the
     nearest).  ``points`` is (B, P, C); returns int32 source ids of shape (B*P*k,),
     the k sources of node i stored at [i*k, (i+1)*k) as the EdgeConv operator expects
-    (src/fused_edgeconv/fused_edgeconv.cu:29-30), ids global (cloud offset added)."""
-    B, P, _ = points.shape
-    d2 = torch.cdist(points.double(), points.double())  # (B,P,P)
-    idx = torch.topk(d2, k, dim=-1, largest=False, sorted=True).indices  # (B,P,k)
-    idx = idx + (torch.arange(B, device=points.device) * P).view(B, 1, 1)
+    (src/fused_edgeconv/fused_edgeconv.cu:29-30), ids global (cloud offset added).
+    On a GPU this is the kNN kernel (operators.knn); on the host (the CPU baseline's sample)
+    the same rule written with framework ops: squared distance in float64 summed coordinate by
+    coordinate, neighbours ordered by (distance, index)."""
+    if points.is_cuda:
+        from .operators.knn import knn_graph
+
+        return knn_graph(points.float().contiguous(), k)
+    B, P, C = points.shape
+    x = points.double()
+    d2 = torch.zeros(B, P, P, dtype=torch.float64)
+    for c in range(C):
+        diff = x[:, :, None, c] - x[:, None, :, c]
+        d2 = d2 + diff * diff
+    idx = torch.sort(d2, dim=-1, stable=True).indices[..., :k]
+    idx = idx + (torch.arange(B) * P).view(B, 1, 1)
     return idx.reshape(-1).to(torch.int32)
 
 

@@ -20,10 +20,19 @@ epoch that does not shrink with the number of GPUs.  Here:
   by peer in rank order (indices are unique per peer: no atomics, deterministic).
 * Kernels, autograd structure, loss normalisation and gradient all-reduce are those of
   ``partition.py`` (one gather pass in the backward, node-wise per-row pack).
+* Two ways to move the rows (``exchange=`` of the model):
+  "peer" (GPUs of one node): the owner stores the rows straight into the halo region of the
+  receiver's buffer through peer-mapped pointers (``peer.py``, gnn_halo_push: one kernel, plain
+  stores over NVLink), then a one-element all-reduce on the same stream orders "every rank's
+  stores are complete" before the consumer kernel.  Every exchange point of the model owns two
+  buffers used in turn, so a rank can never overwrite rows a slower peer still reads: between
+  two uses of the same buffer lies the completion all-reduce of the use in between.
+  "nccl": gather into a send buffer + ``all_to_all_single`` (also what the gloo tests run).
 """
 from __future__ import annotations
 
 import dataclasses
+import math
 from dataclasses import dataclass
 
 import torch
@@ -42,6 +51,16 @@ class ExchangePlan:
     send_idx: torch.Tensor   # int64, local row ids grouped by destination rank, ascending inside a group
     send_splits: list        # rows sent to rank q (0 for this rank)
     recv_splits: list        # rows received from rank q (0 for this rank)
+    # for the peer-store exchange: the halo size of EVERY rank, and for every destination rank q
+    # the row of q's halo region at which this rank's rows start (what q receives from the
+    # ranks before this one)
+    halo_sizes: list = None
+    dst_off: list = None
+    send_idx32: torch.Tensor = None  # send_idx as int32 (kernel argument)
+    # Whether ANY rank has rows to receive.  Every rank derives it from the replicated global
+    # graph, so all ranks agree on whether the collective of this plan is issued at all: a rank
+    # with nothing to send or receive itself (an empty block, only isolated nodes) still joins.
+    active: bool = True
 
     @property
     def n_halo(self) -> int:
@@ -80,14 +99,14 @@ class HaloPartition:
     def index_tensors(self) -> dict:
         return {"row_ptr": self.row_ptr, "col_ind": self.col_ind, "col_ptr": self.col_ptr,
                 "row_ind": self.row_ind, "rs_ptr": self.rs_ptr, "rs_pos": self.rs_pos,
-                "fwd_send": self.fwd.send_idx, "bwd_send": self.bwd.send_idx}
+                "fwd_send": self.fwd.send_idx32, "bwd_send": self.bwd.send_idx32}
 
     def with_index_tensors(self, d: dict) -> "HaloPartition":
         return dataclasses.replace(
             self, row_ptr=d["row_ptr"], col_ind=d["col_ind"], col_ptr=d["col_ptr"], row_ind=d["row_ind"],
             rs_ptr=d["rs_ptr"], rs_pos=d["rs_pos"],
-            fwd=dataclasses.replace(self.fwd, send_idx=d["fwd_send"]),
-            bwd=dataclasses.replace(self.bwd, send_idx=d["bwd_send"]))
+            fwd=dataclasses.replace(self.fwd, send_idx=d["fwd_send"], send_idx32=d["fwd_send"]),
+            bwd=dataclasses.replace(self.bwd, send_idx=d["bwd_send"], send_idx32=d["bwd_send"]))
 
 
 def _outside(ids: torch.Tensor, lo: int, hi: int) -> torch.Tensor:
@@ -120,13 +139,23 @@ def _plan(ptr: torch.Tensor, idx: torch.Tensor, bounds: list, rank: int, world: 
         send.append(rows)
         send_splits.append(int(rows.numel()))
     send_idx = torch.cat(send) if send else torch.zeros(0, dtype=torch.long, device=dev)
+    halo_sizes = [int(t.numel()) for t in needs]
+    dst_off = []
+    for q in range(world):
+        if q == rank or world == 1:
+            dst_off.append(0)
+        else:  # rows of q's halo owned by the ranks before this one
+            dst_off.append(int((needs[q] < lo).sum().item()))
     # local segments and ids in the extended space [own | halo]
     e0, e1 = int(p[lo].item()), int(p[hi].item())
     local_ptr = (p[lo: hi + 1] - e0).to(torch.int32).contiguous()
     v = idx[e0:e1].long()
     own = (v >= lo) & (v < hi)
     ext = torch.where(own, v - lo, (hi - lo) + torch.searchsorted(mine, v))
-    return ExchangePlan(send_idx.contiguous(), send_splits, recv_splits), local_ptr, ext.to(torch.int32).contiguous()
+    active = any(int(t.numel()) > 0 for t in needs)
+    plan = ExchangePlan(send_idx.contiguous(), send_splits, recv_splits, active=active, halo_sizes=halo_sizes,
+                        dst_off=dst_off, send_idx32=send_idx.to(torch.int32).contiguous())
+    return plan, local_ptr, ext.to(torch.int32).contiguous()
 
 
 def build_halo_partition(row_ptr, col_ind, col_ptr, row_ind, rank: int, world: int,
@@ -146,10 +175,10 @@ def build_halo_partition(row_ptr, col_ind, col_ptr, row_ind, rank: int, world: i
 # exchanges
 
 def halo_exchange(x: torch.Tensor, plan: ExchangePlan, n_local: int, group=None, async_op: bool = False):
-    """(n_local, ...) per-node rows -> (n_local + n_halo, ...) [own rows | rows of the halo].
-    Returns (extended tensor, work or None)."""
+    """(n_local, ...) per-node rows -> (n_local + n_halo, ...) [own rows | rows of the halo] with
+    one all-to-all.  Returns (extended tensor, work or None)."""
     x = x.contiguous()
-    if plan.n_halo == 0 and sum(plan.send_splits) == 0:
+    if not plan.active:  # no rank references a row outside its block: no collective anywhere
         return x[:n_local], None
     ext = x.new_empty((n_local + plan.n_halo,) + tuple(x.shape[1:]))
     ext[:n_local] = x[:n_local]
@@ -165,7 +194,7 @@ def halo_return_sum(x_ext: torch.Tensor, plan: ExchangePlan, n_local: int, group
     """Inverse direction for partial sums: the halo rows of ``x_ext`` go back to their owners
     and are added to the owners' rows, peer by peer in rank order."""
     total = x_ext[:n_local].clone()
-    if plan.n_halo == 0 and sum(plan.send_splits) == 0:
+    if not plan.active:
         return total
     back = x_ext.new_empty((int(sum(plan.send_splits)),) + tuple(x_ext.shape[1:]))
     dist.all_to_all_single(back, x_ext[n_local:].contiguous(), output_split_sizes=plan.send_splits,
@@ -179,24 +208,118 @@ def halo_return_sum(x_ext: torch.Tensor, plan: ExchangePlan, n_local: int, group
     return total
 
 
+class NcclExchange:
+    """Moves halo rows with ``all_to_all_single`` (any backend of torch.distributed)."""
+
+    def __init__(self, part: "HaloPartition", group=None, small_group=None):
+        self.group, self.small_group = group, small_group
+
+    def exchange(self, key, tensors, plan: ExchangePlan, n_local: int):
+        """Extended copies [own | halo] of all ``tensors`` (same plan).  The first, wide one
+        travels on the main communicator while the others use the second."""
+        if len(tensors) == 1:
+            return [halo_exchange(tensors[0], plan, n_local, self.group)[0]]
+        first, pending = halo_exchange(tensors[0], plan, n_local, self.group, async_op=True)
+        rest = [halo_exchange(t, plan, n_local, self.small_group)[0] for t in tensors[1:]]
+        if pending is not None:
+            pending[0].wait()
+        return [first] + rest
+
+
+class PeerStoreExchange:
+    """Moves halo rows with one store kernel per tensor into peer-mapped buffers (see the module
+    docstring).  ``exchange`` is collective and must be called by every rank with the same
+    sequence of keys; the buffers of a key are allocated at its first use."""
+
+    def __init__(self, part: "HaloPartition", group=None, small_group=None):
+        self.part = part
+        self.group, self.small_group = group, small_group
+        self.rank, self.world = part.rank, part.world
+        self.n_locals = [part.bounds[q + 1] - part.bounds[q] for q in range(part.world)]
+        self._slots = {}   # key -> [buffers of use 0, buffers of use 1, next use]
+        self._flag = None
+
+    # -- overridable pieces (a CPU stand-in for tests replaces them) -------------------------
+    def _alloc(self, nbytes, device):
+        from .peer import PeerBuffer
+
+        return PeerBuffer(nbytes, device, self.group)
+
+    def _push(self, x, plan, buf, row_bytes, n_local):
+        from .peer import halo_push
+
+        offs = [0]
+        for c in plan.send_splits:
+            offs.append(offs[-1] + int(c))
+        dst = [0 if q == self.rank or plan.send_splits[q] == 0
+               else buf.ptrs[q] + (self.n_locals[q] + plan.dst_off[q]) * row_bytes for q in range(self.world)]
+        halo_push(x, plan.send_idx32, offs, dst, buf.ptrs[self.rank], n_local)
+
+    def _complete(self, device):
+        """Every rank's push kernels are complete before anything enqueued after this call runs."""
+        if self._flag is None:
+            self._flag = torch.zeros(1, dtype=torch.float32, device=device)
+        dist.all_reduce(self._flag, group=self.small_group)
+
+    # ----------------------------------------------------------------------------------------
+    def exchange(self, key, tensors, plan: ExchangePlan, n_local: int):
+        tensors = [t.contiguous() for t in tensors]
+        if not plan.active:
+            return [t[:n_local] for t in tensors]
+        dev = tensors[0].device
+        rows_max = max(n + h for n, h in zip(self.n_locals, plan.halo_sizes))
+        rows = n_local + plan.n_halo
+        row_bytes = [4 * math.prod(t.shape[1:]) for t in tensors]
+        slot = self._slots.get(key)
+        if slot is None:
+            slot = [[self._alloc(rows_max * rb, dev) for rb in row_bytes] for _ in range(2)] + [0]
+            self._slots[key] = slot
+        bufs = slot[slot[2]]
+        slot[2] ^= 1
+        out = []
+        for t, buf, rb in zip(tensors, bufs, row_bytes):
+            if rows_max * rb > buf.nbytes:
+                raise ValueError(f"exchange {key!r}: rows changed width since its buffers were allocated")
+            self._push(t, plan, buf, rb, n_local)
+            out.append(buf.view((rows,) + tuple(t.shape[1:]), torch.float32))
+        self._complete(dev)
+        return out
+
+    def close(self):
+        for slot in self._slots.values():
+            for use in slot[:2]:
+                for buf in use:
+                    buf.close()
+        self._slots = {}
+
+
+def make_exchange(kind, part, group=None, small_group=None):
+    if kind in (None, "nccl", "halo"):
+        return NcclExchange(part, group, small_group)
+    if kind == "peer":
+        return PeerStoreExchange(part, group, small_group)
+    if callable(kind):
+        return kind(part, group, small_group)
+    raise ValueError(f"unknown exchange {kind!r}")
+
+
 class HaloGATFunction(torch.autograd.Function):
-    """Scores + fused GAT aggregation on a halo partition, one autograd node.
-    ``h`` and the output have n_local rows."""
+    """Scores + fused GAT aggregation (+ optional ELU) on a halo partition, one autograd node.
+    ``h`` and the output have n_local rows.  ``exch`` moves the halo rows; ``key`` names this
+    layer's exchange points."""
 
     @staticmethod
-    def forward(ctx, h, attn_l, attn_r, part: HaloPartition, slope, kernels, group, small_group,
+    def forward(ctx, h, attn_l, attn_r, part: HaloPartition, slope, kernels, exch, key, activation=None,
                 h_halo=None):
         n = part.n_local
         h, attn_l, attn_r = h.contiguous(), attn_l.contiguous(), attn_r.contiguous()
         H, Fo = h.shape[1], h.shape[2]
         attn_row, attn_col = kernels.scores_forward(h, attn_l, attn_r)
         if h_halo is None:
-            h_ext, pending = halo_exchange(h, part.fwd, n, group, async_op=True)
+            h_ext, ac_ext = exch.exchange((key, "fwd"), [h, attn_col], part.fwd, n)
         else:  # the caller projected the halo inputs itself: nothing wide to move
-            h_ext, pending = torch.cat([h, h_halo]), None
-        ac_ext, _ = halo_exchange(attn_col, part.fwd, n, small_group)
-        if pending is not None:
-            pending[0].wait()
+            h_ext = torch.cat([h, h_halo])
+            (ac_ext,) = exch.exchange((key, "fwd_attn"), [attn_col], part.fwd, n)
         out = h.new_empty((n, H, Fo))
         edge_max = h.new_empty((n, H))
         edge_sum = h.new_empty((n, H))
@@ -204,30 +327,29 @@ class HaloGATFunction(torch.autograd.Function):
                              edge_sum, False, True)
         ctx.save_for_backward(attn_row, attn_col, h, edge_max, edge_sum, attn_l, attn_r, out)
         ctx.part, ctx.slope, ctx.kernels = part, slope, kernels
-        ctx.group, ctx.small_group = group, small_group
-        return out
+        ctx.exch, ctx.key, ctx.activation = exch, key, activation
+        return F.elu(out) if activation == "elu" else out
 
     @staticmethod
     def backward(ctx, grad_out):
         attn_row, attn_col, h, edge_max, edge_sum, attn_l, attn_r, out = ctx.saved_tensors
-        part, slope, kernels = ctx.part, ctx.slope, ctx.kernels
+        part, slope, kernels, exch = ctx.part, ctx.slope, ctx.kernels, ctx.exch
         n = part.n_local
         H, Fo = h.shape[1], h.shape[2]
         grad_out = grad_out.contiguous()
-        # grad_out rows travel while the per-row pack (node-wise) is formed and exchanged
-        gout_ext, pending = halo_exchange(grad_out, part.bwd, n, ctx.group, async_op=True)
-        rowpack = kernels.backward_pack(out, grad_out, attn_row, edge_max, edge_sum)
-        rp_ext, _ = halo_exchange(rowpack, part.bwd, n, ctx.small_group)
-        if pending is not None:
-            pending[0].wait()
+        if ctx.activation == "elu":  # the ELU backward rides on the node-wise per-row pack
+            grad_out, rowpack = kernels.backward_pack_elu(out, grad_out, attn_row, edge_max, edge_sum)
+        else:
+            rowpack = kernels.backward_pack(out, grad_out, attn_row, edge_max, edge_sum)
+        gout_ext, rp_ext = exch.exchange((ctx.key, "bwd"), [grad_out, rowpack], part.bwd, n)
         gh = h.new_empty((n, H, Fo))
         gac = h.new_empty((n, H))
         edge_grad = kernels.backward_col_edges_part(slope, part.col_ptr, part.row_ind, h, attn_col, rp_ext,
                                                     gout_ext, gh, gac, False)
         gar_ext = kernels.backward_row_sum(part.rs_ptr, part.rs_pos, edge_grad)
-        gar = halo_return_sum(gar_ext, part.bwd, n, ctx.small_group)
+        gar = halo_return_sum(gar_ext, part.bwd, n, exch.small_group)
         gl, gr = kernels.scores_backward(h, attn_l, attn_r, gar, gac, gh)
-        return gh, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None, None
+        return gh, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None, None, None
 
 
 class HaloGATConv(_GATBase):
@@ -238,12 +360,12 @@ class HaloGATConv(_GATBase):
     receiving rank instead of exchanging the wide projected rows."""
 
     def __init__(self, in_feats, out_feats, num_heads, negative_slope=0.2, kernels=_CudaKernels,
-                 group=None, small_group=None, recompute_projection="auto"):
+                 recompute_projection="auto", activation=None, key=0):
         super().__init__(in_feats, out_feats, num_heads, negative_slope)
         self.kernels = kernels
-        self.group = group
-        self.small_group = small_group
         self.recompute_projection = recompute_projection
+        self.activation = activation
+        self.key = key
 
     def _recompute(self, part) -> bool:
         if part.world == 1:
@@ -252,25 +374,30 @@ class HaloGATConv(_GATBase):
             return 4 * self.in_feats <= self.out_feats * self.num_heads
         return bool(self.recompute_projection)
 
-    def forward(self, part: HaloPartition, feat):
-        h = dense.project(feat, self.W).view(-1, self.num_heads, self.out_feats)
+    def forward(self, part: HaloPartition, feat, exch):
         h_halo = None
         if self._recompute(part):
+            # the narrow inputs travel first; the own rows are projected while they do
             with torch.no_grad():
-                x_ext, _ = halo_exchange(feat.detach(), part.fwd, part.n_local, self.group)
+                (x_ext,) = exch.exchange((self.key, "fwd_x"), [feat.detach()], part.fwd, part.n_local)
+        h = dense.project(feat, self.W).view(-1, self.num_heads, self.out_feats)
+        if self._recompute(part):
+            with torch.no_grad():
                 h_halo = dense.project(x_ext[part.n_local:].contiguous(), self.W.detach()).view(
                     -1, self.num_heads, self.out_feats)
         return HaloGATFunction.apply(h, self.attn_l, self.attn_r, part, self.negative_slope,
-                                     self.kernels, self.group, self.small_group, h_halo)
+                                     self.kernels, exch, self.key, self.activation, h_halo)
 
 
 class HaloGAT(nn.Module):
     """models.GAT on a halo partition: identical parameters; inputs / outputs hold the rank's
-    n_local rows.  ``small_group`` is a second communicator over the same ranks for the small
-    per-node tensors (created here when torch.distributed is initialised)."""
+    n_local rows.  ``exchange``: "peer" (stores into peer-mapped buffers, GPUs of one node),
+    "nccl" (all-to-all; any backend), or a factory ``f(part, group, small_group)``.
+    ``small_group`` is a second communicator over the same ranks for the small per-node tensors
+    (created here when torch.distributed is initialised)."""
 
     def __init__(self, in_dim, hidden, heads, num_classes, out_heads=1, negative_slope=0.2,
-                 activation="elu", kernels=_CudaKernels, group=None, small_group=None):
+                 activation="elu", kernels=_CudaKernels, group=None, small_group=None, exchange="nccl"):
         super().__init__()
         if (small_group is None and dist.is_available() and dist.is_initialized()
                 and dist.get_world_size() > 1):
@@ -279,20 +406,33 @@ class HaloGAT(nn.Module):
             hidden = [hidden] * len(heads)
         dims_in = [in_dim] + [h * f for h, f in zip(heads, hidden)]
         self.gat_layers = nn.ModuleList(
-            [HaloGATConv(dims_in[i], hidden[i], heads[i], negative_slope, kernels, group, small_group)
+            [HaloGATConv(dims_in[i], hidden[i], heads[i], negative_slope, kernels, activation=activation, key=i)
              for i in range(len(heads))])
         self.gat_layers.append(
-            HaloGATConv(dims_in[-1], num_classes, out_heads, negative_slope, kernels, group, small_group))
+            HaloGATConv(dims_in[-1], num_classes, out_heads, negative_slope, kernels, key=len(heads)))
         self.activation = activation
-        self.group = group
+        self.group, self.small_group = group, small_group
+        self.exchange = exchange
+        self._exch = None  # created for the first partition seen
+
+    def exchanger(self, part: HaloPartition):
+        # (an end-to-end step hands in the same partition with freshly uploaded index tensors:
+        # the plan's sizes are what the buffers depend on, and those do not change)
+        if self._exch is None:
+            self._exch = make_exchange(self.exchange, part, self.group, self.small_group)
+        return self._exch
 
     def forward(self, part: HaloPartition, inputs):
+        exch = self.exchanger(part)
         h = inputs
         for layer in self.gat_layers[:-1]:
-            h = layer(part, h).flatten(1)
-            if self.activation == "elu":
-                h = F.elu(h)
-        return self.gat_layers[-1](part, h).mean(1)
+            h = layer(part, h, exch).flatten(1)
+        return self.gat_layers[-1](part, h, exch).mean(1)
+
+    def close(self):
+        if self._exch is not None and hasattr(self._exch, "close"):
+            self._exch.close()
+        self._exch = None
 
     def loss(self, part: HaloPartition, logits, labels_local):
         """Cross-entropy averaged over ALL nodes of the graph (sum over the owned rows divided

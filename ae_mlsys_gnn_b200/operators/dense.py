@@ -5,7 +5,14 @@ layers/edgeconv_layer.py:37-38, layers/gmmconv_layer.py:68).
 ``matmul_tf32x3(x, w)`` computes ``x @ w`` with the error-compensated 3xTF32 tcgen05
 kernel (fp32-level accuracy); its backward uses the same kernel for grad_x and, with the
 node axis as the reduction axis, for grad_w.  ``project`` picks it whenever the shape is
-supported and falls back to ``torch.matmul`` (cuBLAS fp32) otherwise.
+supported; the shapes it does not take (fewer rows than one tile pays for, non-fp32) go to
+the framework's fp32 GEMM, and every such call is counted (``fallback_calls``) so that a
+run can report how much of its dense work left the tensor-core kernel.
+
+Error contract of the kernel: every barrier wait inside it is bounded; when one expires the
+CTA gives up and sets a status word instead of hanging, and the output of that launch is
+incomplete.  ``check_status()`` reads the word (a device synchronisation) and raises; call it
+wherever the step synchronises anyway (after reading the loss, at the end of a timed loop).
 """
 from __future__ import annotations
 
@@ -17,6 +24,16 @@ F32 = torch.float32
 enabled = True  # set False to force the cuBLAS fp32 path
 
 _status: dict[int, torch.Tensor] = {}
+_fallbacks = {"calls": 0}
+
+
+def fallback_calls() -> int:
+    """Dense products that went to the framework GEMM instead of the tensor-core kernel so far."""
+    return _fallbacks["calls"]
+
+
+def _note_fallback():
+    _fallbacks["calls"] += 1
 
 
 def _status_word(dev: torch.device) -> torch.Tensor:
@@ -120,11 +137,13 @@ class _MatmulFunction(torch.autograd.Function):
             if supported(g.shape[0], x.shape[1], n_out, g):
                 gx = gemm_any_k(g, w, not ctx.w_is_out_by_in)
             else:
+                _note_fallback()
                 gx = g @ (w if ctx.w_is_out_by_in else w.t())
         if ctx.needs_input_grad[1]:
             if enabled and x.shape[0] >= TN_MIN_ROWS and x.data_ptr() % 16 == 0 and g.data_ptr() % 16 == 0:
                 gw = gemm_tn(g, x) if ctx.w_is_out_by_in else gemm_tn(x, g)
             else:
+                _note_fallback()
                 gw = (g.t() @ x) if ctx.w_is_out_by_in else (x.t() @ g)
         return gx, gw, None
 
@@ -138,6 +157,7 @@ def project(x, w):
     """x @ w, on the tensor cores for CUDA fp32 matrices."""
     if x.dim() == 2 and supported(x.shape[0], w.shape[1], w.shape[0], x):
         return matmul_tf32x3(x, w)
+    _note_fallback()
     return torch.matmul(x, w)
 
 
@@ -145,4 +165,5 @@ def linear(x, weight):
     """nn.Linear without bias: x (M,K) @ weight(N,K)^T."""
     if x.dim() == 2 and supported(x.shape[0], weight.shape[0], weight.shape[1], x):
         return _MatmulFunction.apply(x, weight, True)
+    _note_fallback()
     return torch.nn.functional.linear(x, weight)

@@ -273,6 +273,12 @@ class _CudaKernels:
         return gat_backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=pad_to)
 
     @staticmethod
+    def backward_pack_elu(out, grad_act, attn_row, edge_max, edge_sum):
+        from .operators.fused_gat import gat_backward_pack_elu
+
+        return gat_backward_pack_elu(out, grad_act, attn_row, edge_max, edge_sum)
+
+    @staticmethod
     def backward_col_edges_part(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full,
                                 grad_feat, grad_attn_col, accumulate):
         from .operators.fused_gat import gat_backward_col_edges_part

@@ -10,7 +10,21 @@ script/train/train_gatconv_our.py:184-200).  Prints ONE JSON line (rank 0).
 Default workload: C5, the 3-layer GAT (4x128, 4x128, 1x47) on the R-MAT graph with
 2,449,029 nodes and ~124 M directed edges — the configuration the 1/2/4/8-GPU metric
 is quoted on; it fits one GPU, so the same workload is timed at every N (strong
-scaling: destination-row blocks over the ranks, all-gather of projected features).
+scaling: destination-row blocks over the ranks, exchange of the referenced rows).
+
+The line's extra records (single GPU, default workload):
+  roofline       the HBM-bound entry point with the largest time inside the timed region:
+                 `achieved` = measured DRAM bytes per launch (profiles/traffic.json, one ncu
+                 capture) / CUDA-event time, `frac` = achieved / measured copy bandwidth;
+                 the figure from algorithmic bytes (every gathered row counted once per
+                 edge, no cache reuse) is kept beside it as `*_algorithmic`;
+  models         the other four configurations, run after the timed workload in the same
+                 process: eager epoch, epoch replayed as a CUDA graph, sum of kernel time,
+                 dominant entry point and what bounds it;
+  cpu_baseline   the reference's CPU formulation on a bounded sample, at two sample sizes,
+                 extrapolated by edge count (flagged as such);
+  gpu_reference  the reference's own CUDA operators (compiled unmodified into oracle/_ref)
+                 timed per operator next to this library's on the same inputs.
 """
 from __future__ import annotations
 
@@ -39,6 +53,13 @@ def mean_cross_entropy(logits, labels):
 
 METRIC = "fwd_bwd_epoch_ms"
 UNIT = "ms/epoch"
+
+# (nodes, edges incl. self-loops) the generators produce for seed 0 at full size; the CPU legs
+# extrapolate to these without building the full graph
+FULL_SIZES = {"C1": (2708, 13264), "C2": (232965, 113696831), "C3": (32768, 655360),
+              "C4": (19717, 108365), "C5": (2449029, 126053365)}
+# gathered operand fits in the 126 MB L2: those epochs are launch / L2 bound, not HBM bound
+L2_RESIDENT = {"C1", "C3", "C4"}
 
 WORKLOADS = {
     "C1": dict(kind="gat", desc="GAT 2-layer, 2,708 nodes / 10,556+2,708 edges, in 1433, 8x8 -> 1x7",
@@ -158,7 +179,7 @@ def algorithmic_bytes(name: str, n: int, e: int, H: int, Fw: int, D: int = 0) ->
 
 class BytesLedger:
     """Wraps _capi.call so that every timed entry-point call is stored with the
-    algorithmic bytes of its arguments."""
+    algorithmic bytes of its arguments, keyed by entry point and shape ("name[HxF]")."""
 
     def __init__(self):
         from ae_mlsys_gnn_b200 import _capi
@@ -166,6 +187,7 @@ class BytesLedger:
         self.capi = _capi
         self.timer = _capi.CallTimer(with_events=True)
         self.bytes: list[float] = []
+        self.keys: list[str] = []
         self._orig = _capi.call
 
     def __enter__(self):
@@ -174,7 +196,9 @@ class BytesLedger:
         orig = self._orig
 
         def call(name, *args):
-            ledger.bytes.append(ledger._bytes_of(name, args))
+            b, shape = ledger._bytes_of(name, args)
+            ledger.bytes.append(b)
+            ledger.keys.append(f"{name}[{shape}]" if shape else name)
             orig(name, *args)
 
         capi.call = call  # operator modules look the function up as capi.call at call time
@@ -186,36 +210,41 @@ class BytesLedger:
 
     @staticmethod
     def _bytes_of(name, a):
-        if name in ("gnn_gat_fwd", "gnn_gat_fwd_part"):
-            return algorithmic_bytes("gnn_gat_fwd", a[2], a[3], a[7], a[8])
+        if name in ("gnn_gat_fwd", "gnn_gat_fwd_part", "gnn_gat_fwd_act"):
+            return algorithmic_bytes("gnn_gat_fwd", a[2], a[3], a[7], a[8]), f"{a[7]}x{a[8]}"
         if name == "gnn_gat_bwd_row":
-            return algorithmic_bytes(name, a[2], a[3], a[10], a[11])
+            return algorithmic_bytes(name, a[2], a[3], a[10], a[11]), f"{a[10]}x{a[11]}"
         if name in ("gnn_gat_bwd_col", "gnn_gat_bwd_col_part"):
-            return algorithmic_bytes("gnn_gat_bwd_col", a[2], a[3], a[8], a[9])
+            return algorithmic_bytes("gnn_gat_bwd_col", a[2], a[3], a[8], a[9]), f"{a[8]}x{a[9]}"
         if name == "gnn_gat_bwd_col_edges":
-            return algorithmic_bytes(name if a[13] else "gnn_gat_bwd_col", a[2], a[3], a[8], a[9])
+            return (algorithmic_bytes(name if a[13] else "gnn_gat_bwd_col", a[2], a[3], a[8], a[9]),
+                    f"{a[8]}x{a[9]}")
         if name in ("gnn_gat_bwd_pack", "gnn_gat_bwd_pack_elu"):
-            return algorithmic_bytes(name, a[0], 0, a[6], a[7])
+            return algorithmic_bytes(name, a[0], 0, a[6], a[7]), f"{a[6]}x{a[7]}"
         if name == "gnn_gat_bwd_row_sum":
-            return algorithmic_bytes(name, a[2], a[3], a[5], 1)
+            return algorithmic_bytes(name, a[2], a[3], a[5], 1), f"{a[5]}"
         if name == "gnn_edgeconv_fwd":
-            return algorithmic_bytes(name, a[4], a[4] * a[0], 1, a[5])
+            return algorithmic_bytes(name, a[4], a[4] * a[0], 1, a[5]), f"k{a[0]}x{a[5]}"
         if name == "gnn_edgeconv_bwd":
-            return algorithmic_bytes(name, a[2], 0, 1, a[4])
+            return algorithmic_bytes(name, a[2], 0, 1, a[4]), f"{a[4]}"
         if name == "gnn_gmm_fwd":
-            return algorithmic_bytes(name, a[2], a[3], a[9], a[11], a[10])
+            return algorithmic_bytes(name, a[2], a[3], a[9], a[11], a[10]), f"{a[9]}x{a[11]}"
         if name == "gnn_mhsddmm":
-            return algorithmic_bytes(name, a[2], a[3], a[6], a[7])
+            return algorithmic_bytes(name, a[2], a[3], a[6], a[7]), f"{a[6]}x{a[7]}"
         if name == "gnn_gat_scores_fwd":
-            return algorithmic_bytes(name, a[3], 0, a[4], a[5])
+            return algorithmic_bytes(name, a[3], 0, a[4], a[5]), f"{a[4]}x{a[5]}"
         if name == "gnn_gat_scores_bwd":
-            return algorithmic_bytes(name, a[5], 0, a[6], a[7])
-        return 0.0
+            return algorithmic_bytes(name, a[5], 0, a[6], a[7]), f"{a[6]}x{a[7]}"
+        if name == "gnn_gemm_tf32x3":
+            return 0.0, f"{a[4]}x{a[5]}x{a[6]}"
+        if name == "gnn_gemm_tf32x3_tn":
+            return 0.0, f"{a[3]}x{a[4]}x{a[5]}"
+        return 0.0, ""
 
     def summary(self):
         per = {}
-        for (name, s, t), b in zip(self.timer.records, self.bytes):
-            d = per.setdefault(name, {"ms": 0.0, "bytes": 0.0, "calls": 0})
+        for (name, s, t), b, key in zip(self.timer.records, self.bytes, self.keys):
+            d = per.setdefault(key, {"ms": 0.0, "bytes": 0.0, "calls": 0})
             d["ms"] += s.elapsed_time(t)
             d["bytes"] += b
             d["calls"] += 1
@@ -306,14 +335,9 @@ def cpu_sample_scale(wl: dict) -> float:
     return {"C1": 1.0, "C2": 1.0 / 32, "C3": 1.0 / 8, "C4": 1.0, "C5": 1.0 / 256}[wl["name"]]
 
 
-def run_cpu_epochs(wl: dict, steps: int, warmup: int, seed: int):
-    """Times `steps` epochs of the CPU model on the bounded sample; returns
-    (ms per epoch extrapolated to the full workload, sample description, cores)."""
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    scale = cpu_sample_scale(wl)
+def _time_cpu_epochs(wl: dict, scale: float, steps: int, warmup: int, seed: int):
+    """(ms per epoch, nodes, edges) of the CPU model on the generator at `scale`."""
     d = build_inputs(wl, "cpu", seed, scale)
-    full_units = wl.get("_full_nnz") or d["nnz"] / scale
     torch.manual_seed(seed)
     model = make_model(wl, cpu=True)
     opt = torch.optim.Adam(model.parameters(), lr=1e-3)
@@ -336,29 +360,363 @@ def run_cpu_epochs(wl: dict, steps: int, warmup: int, seed: int):
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
-    ms = (time.perf_counter() - t0) * 1e3 / max(1, steps)
-    factor = full_units / d["nnz"]
-    sample = (f"{wl['name']} generator at scale {scale:g}: {d['n']} nodes / {d['nnz']} edges, full model "
-              f"fwd+loss+bwd+Adam in PyTorch-CPU fp32 (DGL-style index_select/index_add restatement), "
-              f"{ms:.1f} ms per epoch measured, x{factor:.1f} (edge ratio) to the full workload")
-    return ms * factor, sample, cores
+    return (time.perf_counter() - t0) * 1e3 / max(1, steps), d["n"], d["nnz"]
+
+
+def run_cpu_epochs(wl: dict, steps: int, warmup: int, seed: int):
+    """Times the CPU model on a bounded sample of the workload and extrapolates to the full
+    workload by edge count.  A second, four times larger sample (two epochs) is timed as well
+    so that the linearity the extrapolation assumes can be read off the record.  Returns the
+    `cpu_baseline` record."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    scale = cpu_sample_scale(wl)
+    full_nnz = FULL_SIZES[wl["name"]][1]
+    ms, n, nnz = _time_cpu_epochs(wl, scale, steps, warmup, seed)
+    rec = {"unit": UNIT, "cores": cores, "kind": "port", "extrapolated": scale < 1.0,
+           "sample_ms": ms, "sample_nodes": n, "sample_edges": nnz, "factor": full_nnz / nnz if scale < 1.0 else 1.0}
+    value = ms * rec["factor"]
+    text = (f"{wl['name']} generator at scale {scale:g}: {n} nodes / {nnz} edges, full model "
+            f"fwd+loss+bwd+Adam in PyTorch-CPU fp32 (DGL-style index_select/index_add restatement), "
+            f"{ms:.1f} ms per epoch measured")
+    if scale < 1.0:
+        ms4, n4, nnz4 = _time_cpu_epochs(wl, min(1.0, 4 * scale), 2, 1, seed)
+        rec.update(sample4x_ms=ms4, sample4x_edges=nnz4, sample4x_extrapolated_ms=ms4 * full_nnz / nnz4)
+        text += (f", x{rec['factor']:.1f} (edge ratio to the full {full_nnz} edges); a sample of {nnz4} edges "
+                 f"took {ms4:.1f} ms, which extrapolates to {ms4 * full_nnz / nnz4:.0f} ms")
+    rec["value"] = value
+    rec["sample"] = text
+    return rec
+
+
+def config_of(wl: dict, world: int) -> dict:
+    """The `config` record, identical in the library's arm and in the reference arm."""
+    n, nnz = FULL_SIZES[wl["name"]]
+    return {"workload": f"{wl['name']}: {wl['desc']}", "nodes": n, "edges": nnz,
+            "parallelism": (f"row-block x{world}, {os.environ.get('GNN_B200_EXCHANGE', 'peer')} exchange"
+                            if world > 1 else "single GPU"),
+            "l2": ("flushed between steps (256 MB write)" if wl["name"] in L2_RESIDENT
+                   else "inputs exceed L2 (126 MB)"),
+            "seed": 0}
 
 
 def reference_arm(args, wl):
     rank = env_int("RANK", 0)
     if rank != 0:
         return
-    ms, sample, cores = run_cpu_epochs(wl, args.steps, args.warmup, args.seed)
+    rec = run_cpu_epochs(wl, args.steps, args.warmup, args.seed)
+    ms = rec["value"]
     line = {
         "impl": "reference", "metric": METRIC, "value": ms, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{wl['name']}: {wl['desc']}"},
-        "cpu_baseline": {"value": ms, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": config_of(wl, args.gpus), "extrapolated": rec["extrapolated"],
+        "cpu_baseline": rec,
         "e2e": {"value": ms, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------
+# the reference's own CUDA operators, timed next to this library's on the same inputs
+# ----------------------------------------------------------------------------------------
+
+def _median_ms(fn, iters=5, warmup=2):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for a, b in ev:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    t = sorted(a.elapsed_time(b) for a, b in ev)
+    return t[len(t) // 2]
+
+
+def gpu_reference_leg(dev, seed: int):
+    """Per-operator times of the reference's CUDA kernels (oracle/_ref, built unmodified from
+    the reference sources) and of this library on the same inputs.  Shapes are those where
+    reading the reference kernels shows no out-of-bounds access (F a multiple of 32; below
+    2^24 edges for its float-typed csr2csc permutation): R-MAT 400,000 nodes / ~15.6 M edges
+    with 4x128, 4x64 and 1x64 features; EdgeConv 64 clouds x 1,024 points, k = 20, 64 wide.
+    The 47-wide output layer is left out (fused_gat_SM.cu:279 reads past the row).  For
+    F > 64 and degrees above 32 the reference forward shares a staging buffer between warps
+    without a block barrier: its values are not checked here, only its time is taken."""
+    try:
+        from oracle import build_ref
+    except Exception as e:  # the checker is not shipped
+        return {"unavailable": f"oracle package missing: {e}"}
+    need = ("fused_gat_SM", "fused_edgeconv", "csrtocsc")
+    if not all(build_ref.available(m) for m in need):
+        return {"unavailable": "oracle/_ref modules not built (python -m oracle.build_ref)"}
+    from ae_mlsys_gnn_b200 import graphs as G
+    from ae_mlsys_gnn_b200.operators import fused_gat as GAT
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+    from ae_mlsys_gnn_b200.operators.fused_edgeconv import edgeconv_forward
+
+    gat, ec, tr = (build_ref.load_module(m) for m in need)
+    out = {"graph": "R-MAT 400,000 nodes", "ops": {}}
+    g = G.rmat_graph(400_000, int(400_000 * 50 * 0.45), seed=seed, device=dev)
+    out["graph"] += f" / {g.nnz} edges"
+    rp, ci = g.row_ptr, g.col_ind
+    cp, ri, pm = csr2csc(rp, ci)
+    pos = GAT.invert_permutation(pm)
+    gen = torch.Generator(device=dev).manual_seed(seed)
+
+    def rec(name, ref_fn, own_fn):
+        r, o = _median_ms(ref_fn), _median_ms(own_fn)
+        out["ops"][name] = {"reference_ms": r, "b200_ms": o, "speedup": r / o if o > 0 else None}
+
+    if g.nnz < (1 << 24):
+        vals = torch.arange(g.nnz, dtype=torch.float32, device=dev)
+        rec("csr2csc", lambda: tr.csr2csc(rp, ci, vals), lambda: csr2csc(rp, ci))
+    for H, Fw in ((4, 128), (4, 64), (1, 64)):
+        ar = torch.randn(g.n, H, device=dev, generator=gen)
+        ac = torch.randn(g.n, H, device=dev, generator=gen)
+        x = torch.randn(g.n, H, Fw, device=dev, generator=gen)
+        go = torch.randn(g.n, H, Fw, device=dev, generator=gen)
+        o, m, s = GAT.gat_forward(ar, ac, rp, ci, 0.2, x)
+        rec(f"gat_forward[{H}x{Fw}]", lambda: gat.gat_forward(ar, ac, rp, ci, 0.2, x),
+            lambda: GAT.gat_forward(ar, ac, rp, ci, 0.2, x))
+        rec(f"gat_backward[{H}x{Fw}]", lambda: gat.gat_backward(0.2, rp, ci, cp, ri, m, s, x, ar, ac, go),
+            lambda: GAT.gat_backward_with_output(0.2, rp, ci, cp, ri, pos, m, s, x, ar, ac, o, go))
+        out["ops"][f"gat_backward[{H}x{Fw}]"]["b200_two_pass_ms"] = _median_ms(
+            lambda: GAT.gat_backward(0.2, rp, ci, cp, ri, m, s, x, ar, ac, go))
+    n, k, Fw = 64 * 1024, 20, 64
+    src = torch.randint(0, n, (n * k,), device=dev, dtype=torch.int32, generator=gen)
+    hs = torch.randn(n, Fw, device=dev, generator=gen)
+    hd = torch.randn(n, Fw, device=dev, generator=gen)
+    rec(f"edgeconv_forward[64x1024,k{k},{Fw}]", lambda: ec.edgeconv_forward(k, src, hs, hd),
+        lambda: edgeconv_forward(k, src, hs, hd))
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# one workload on the GPU(s)
+# ----------------------------------------------------------------------------------------
+
+def traffic_from_profile(key: str, workload: str):
+    """DRAM bytes per launch measured once with ncu (profiles/traffic.json), or None."""
+    try:
+        t = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))
+        return t.get(workload, {}).get(key)
+    except Exception:
+        return None
+
+
+def release_device_memory():
+    from ae_mlsys_gnn_b200 import _capi
+    from ae_mlsys_gnn_b200.operators import fused_gat
+
+    _capi._workspaces.clear()
+    fused_gat._CSR_POS.clear()
+    fused_gat._CSC_PERM.clear()
+    torch.cuda.empty_cache()
+
+
+class Workload:
+    """Inputs, model, optimizer and the step function of one configuration."""
+
+    def __init__(self, wl, dev, seed, world=1, rank=0, capturable=False):
+        from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+
+        self.wl, self.dev, self.world, self.rank = wl, dev, world, rank
+        d = self.d = build_inputs(wl, dev, seed)
+        if (d["n"], d["nnz"]) != FULL_SIZES[wl["name"]] and seed == 0:
+            raise SystemExit(f"{wl['name']}: generator produced {d['n']} nodes / {d['nnz']} edges, "
+                             f"FULL_SIZES says {FULL_SIZES[wl['name']]}")
+        self.n, self.nnz = d["n"], d["nnz"]
+        torch.manual_seed(seed)
+        self.part = None
+        self.setup_ms = {}
+        kind = wl["kind"]
+        if kind in ("gat", "gmm"):
+            g = d["graph"]
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            csr2csc(g.row_ptr, g.col_ind)  # first call sizes the workspace
+            a.record()
+            self.col_ptr, self.row_ind, self.permute = csr2csc(g.row_ptr, g.col_ind)
+            b.record()
+            torch.cuda.synchronize()
+            self.setup_ms["csr2csc"] = a.elapsed_time(b)
+        if kind == "gat" and world > 1:
+            self._partition()
+        else:
+            self.model = make_model(wl).to(dev)
+        self.opt = torch.optim.Adam(self.model.parameters(), lr=1e-3, capturable=capturable)
+        torch.cuda.empty_cache()
+
+    def _partition(self):
+        wl, d, dev = self.wl, self.d, self.dev
+        g = d["graph"]
+        scheme = os.environ.get("GNN_B200_EXCHANGE", "peer")
+        if scheme == "gather":
+            from ae_mlsys_gnn_b200.partition import PartitionedGAT, build_partition
+
+            self.part = build_partition(g.row_ptr, g.col_ind, self.col_ptr, self.row_ind, self.rank, self.world)
+            self.model = PartitionedGAT(wl["in_dim"], wl["hidden"], wl["heads"], wl["classes"], 1).to(dev)
+        else:
+            from ae_mlsys_gnn_b200.halo import HaloGAT, build_halo_partition
+
+            self.part = build_halo_partition(g.row_ptr, g.col_ind, self.col_ptr, self.row_ind, self.rank,
+                                             self.world)
+            self.model = HaloGAT(wl["in_dim"], wl["hidden"], wl["heads"], wl["classes"], 1,
+                                 exchange=scheme).to(dev)
+        d["x_l"] = self.part.pad_rows(self.part.local_slice(d["x"]))
+        d["y_l"] = self.part.local_slice(d["labels"]).contiguous()
+        del d["x"]
+        self.col_ptr = self.row_ind = self.permute = None
+        d["graph"] = None
+
+    def step(self):
+        wl, d, model, opt = self.wl, self.d, self.model, self.opt
+        if self.part is not None:
+            out = model(self.part, d["x_l"])
+            loss = model.loss(self.part, out, d["y_l"])
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+            model.all_reduce_grads(self.world)
+        else:
+            if wl["kind"] == "gat":
+                g = d["graph"]
+                out = model(g.row_ptr, g.col_ind, self.col_ptr, self.row_ind, d["x"])
+            elif wl["kind"] == "edgeconv":
+                out = model(d["points"], d["src"])
+            else:
+                g = d["graph"]
+                out = model(g.row_ptr, g.col_ind, self.col_ptr, self.row_ind, self.permute, d["x"], d["pseudo"])
+            loss = mean_cross_entropy(out, d["labels"])
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+        opt.step()
+        return loss
+
+
+def barrier(world):
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def timed_epochs(w: Workload, steps: int, warmup: int, sampler=None):
+    """Warm-up, then `steps` epochs bracketed by barrier + synchronize, one CUDA-event pair per
+    step; small workloads get an L2 flush (256 MB write) between steps, outside the pairs.
+    Returns (ms per step as the max over ranks, per-entry-point summary, launch counts, clocks)."""
+    from ae_mlsys_gnn_b200.operators import dense
+
+    dev, world = w.dev, w.world
+    flush = w.wl["name"] in L2_RESIDENT
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if flush else None
+    for _ in range(warmup):
+        w.step()
+    barrier(world)
+    if sampler is not None:
+        sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    with BytesLedger() as ledger:
+        barrier(world)
+        for a, b in ev:
+            if flush:
+                flush_buf.fill_(1)
+            a.record()
+            w.step()
+            b.record()
+        barrier(world)
+    clocks = sampler.stop() if sampler is not None else None
+    dense.check_status(dev)  # a GEMM whose bounded wait expired must not pass as a result
+    total_ms = torch.tensor([sum(a.elapsed_time(b) for a, b in ev)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    return total_ms.item() / steps, ledger.summary(), dict(ledger.timer.counts), clocks
+
+
+def graphed_epoch_ms(w: Workload, steps: int):
+    """The same epoch captured once as a CUDA graph and replayed (single GPU)."""
+    from ae_mlsys_gnn_b200.graphed import GraphedStep
+
+    gs = GraphedStep(w.step, warmup=3, device=w.dev)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=w.dev) if w.wl["name"] in L2_RESIDENT else None
+    for _ in range(3):
+        gs.replay()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in ev:
+        if flush_buf is not None:
+            flush_buf.fill_(1)
+        a.record()
+        gs.replay()
+        b.record()
+    torch.cuda.synchronize()
+    return sum(a.elapsed_time(b) for a, b in ev) / steps
+
+
+def roofline_of(per: dict, steps: int, workload: str):
+    """Roofline record of the HBM-bound entry point with the largest time."""
+    peak, peak_kind = measured_peak_gbs()
+    hbm = {k: v for k, v in per.items() if v["bytes"] > 0}  # the GEMM entries carry no byte count
+    if not hbm:
+        return None
+    key = max(hbm, key=lambda k: hbm[k]["ms"])
+    p = per[key]
+    launch_ms = p["ms"] / p["calls"]
+    alg = p["bytes"] / p["calls"]
+    alg_gbs = alg / (launch_ms * 1e-3) / 1e9 if launch_ms > 0 else 0.0
+    traffic = traffic_from_profile(key, workload)
+    roof = {"bound": "hbm", "kernel": key, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+            "launch_ms": launch_ms, "traffic": traffic, "bytes_per_launch_algorithmic": alg,
+            "achieved_algorithmic": alg_gbs, "frac_algorithmic": alg_gbs / peak}
+    if traffic:
+        roof["achieved"] = traffic / (launch_ms * 1e-3) / 1e9
+        roof["basis"] = "measured DRAM bytes per launch (ncu, profiles/traffic.json) / CUDA-event time"
+    else:  # no capture of this kernel and shape: only the algorithmic figure exists
+        roof["achieved"] = alg_gbs
+        roof["basis"] = "algorithmic bytes / CUDA-event time (no DRAM capture for this kernel and shape)"
+    roof["frac"] = roof["achieved"] / peak
+    roof["frac_of_8tbs"] = roof["achieved"] / 8000.0
+    entries = {}
+    for k, v in per.items():
+        e = {"ms_per_step": v["ms"] / steps, "calls_per_step": v["calls"] / steps}
+        if v["bytes"] > 0 and v["ms"] > 0:
+            e["gbs_algorithmic"] = v["bytes"] / (v["ms"] * 1e-3) / 1e9
+            t = traffic_from_profile(k, workload)
+            if t:
+                e["gbs_dram"] = t * v["calls"] / (v["ms"] * 1e-3) / 1e9
+        entries[k] = e
+    roof["per_entry_point"] = entries
+    return roof
+
+
+def model_record(name: str, dev, seed: int, steps: int):
+    """Sub-record of one of the other configurations: eager epoch, graph-replayed epoch, kernel sum."""
+    wl = dict(WORKLOADS[name], name=name)
+    w = Workload(wl, dev, seed, capturable=True)
+    ms, per, counts, _ = timed_epochs(w, steps, 3)
+    kernel_ms = sum(v["ms"] for v in per.values()) / steps
+    rec = {"workload": wl["desc"], "nodes": w.n, "edges": w.nnz, "epoch_ms": ms,
+           "library_entry_points_ms": kernel_ms, "gpu_launches_per_step": count_launches(counts, 0) / steps}
+    hbm = {k: v for k, v in per.items() if v["bytes"] > 0}
+    if hbm:
+        key = max(hbm, key=lambda k: hbm[k]["ms"])
+        p = per[key]
+        peak, _ = measured_peak_gbs()
+        gbs = p["bytes"] / (p["ms"] * 1e-3) / 1e9
+        rec["dominant"] = {"entry_point": key, "ms_per_step": p["ms"] / steps,
+                           "gbs_algorithmic": gbs, "frac_algorithmic": gbs / peak}
+    if name in L2_RESIDENT:
+        rec["bound"] = "launch / L2 (gathered operand fits in the 126 MB L2)"
+        try:
+            rec["epoch_ms_cuda_graph"] = graphed_epoch_ms(w, steps)
+        except Exception as e:  # capture refused: report why, keep the eager number
+            rec["epoch_ms_cuda_graph"] = None
+            rec["cuda_graph_error"] = f"{type(e).__name__}: {e}"[:200]
+    else:
+        rec["bound"] = "hbm"
+    del w
+    release_device_memory()
+    return rec
 
 
 # ----------------------------------------------------------------------------------------
@@ -375,6 +733,8 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-models", action="store_true", help="skip the sub-records of the other configurations")
+    ap.add_argument("--no-gpu-reference", action="store_true", help="skip timing the reference's CUDA operators")
     args = ap.parse_args()
     wl = dict(WORKLOADS[args.workload], name=args.workload)
     if args.warmup < 3 and args.impl == "b200":
@@ -398,141 +758,47 @@ def main():
         raise SystemExit("only the GAT workloads are partitioned; EdgeConv / GMMConv run as replicas (N=1)")
 
     from ae_mlsys_gnn_b200 import _capi
-    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+    from ae_mlsys_gnn_b200.operators import dense
 
     _capi.lib()
-    d = build_inputs(wl, dev, args.seed)
-    wl["_full_nnz"] = d["nnz"]
-    n, nnz = d["n"], d["nnz"]
-    torch.manual_seed(args.seed)
-
-    part = None
-    if wl["kind"] == "gat":
-        g = d["graph"]
-        col_ptr, row_ind, _ = csr2csc(g.row_ptr, g.col_ind)
-        if world > 1:
-            # exchange scheme: "halo" (default) moves only the rows a rank's block references,
-            # "gather" all-gathers every rank's rows
-            if os.environ.get("GNN_B200_EXCHANGE", "halo") == "gather":
-                from ae_mlsys_gnn_b200.partition import PartitionedGAT, build_partition
-
-                part = build_partition(g.row_ptr, g.col_ind, col_ptr, row_ind, rank, world)
-                model = PartitionedGAT(wl["in_dim"], wl["hidden"], wl["heads"], wl["classes"], 1).to(dev)
-            else:
-                from ae_mlsys_gnn_b200.halo import HaloGAT, build_halo_partition
-
-                part = build_halo_partition(g.row_ptr, g.col_ind, col_ptr, row_ind, rank, world)
-                model = HaloGAT(wl["in_dim"], wl["hidden"], wl["heads"], wl["classes"], 1).to(dev)
-            x_l = part.pad_rows(part.local_slice(d["x"]))
-            y_l = part.local_slice(d["labels"]).contiguous()
-            d["x_l"], d["y_l"] = x_l, y_l
-            del d["x"], col_ptr, row_ind
-            d["graph"] = None
-        else:
-            model = make_model(wl).to(dev)
-    elif wl["kind"] == "gmm":
-        g = d["graph"]
-        col_ptr, row_ind, permute = csr2csc(g.row_ptr, g.col_ind)
-        model = make_model(wl).to(dev)
-    else:
-        model = make_model(wl).to(dev)
-    opt = torch.optim.Adam(model.parameters(), lr=1e-3)
-    torch.cuda.empty_cache()
-
-    def step():
-        if wl["kind"] == "gat" and part is not None:
-            out = model(part, x_l)
-            loss = model.loss(part, out, y_l)
-            opt.zero_grad(set_to_none=True)
-            loss.backward()
-            model.all_reduce_grads(world)
-        else:
-            if wl["kind"] == "gat":
-                out = model(g.row_ptr, g.col_ind, col_ptr, row_ind, d["x"])
-            elif wl["kind"] == "edgeconv":
-                out = model(d["points"], d["src"])
-            else:
-                out = model(g.row_ptr, g.col_ind, col_ptr, row_ind, permute, d["x"], d["pseudo"])
-            loss = mean_cross_entropy(out, d["labels"])
-            opt.zero_grad(set_to_none=True)
-            loss.backward()
-        opt.step()
-        return loss
-
-    # Inputs larger than the 126 MB L2 need no flush; the small workloads get one
-    # between timed steps (a 256 MB write), outside the per-step event pairs.
-    flush = wl["name"] in ("C1", "C3", "C4")
-    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if flush else None
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    barrier()
-
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    with BytesLedger() as ledger:
-        barrier()
-        for a, b in ev:
-            if flush:
-                flush_buf.fill_(1)
-            a.record()
-            step()
-            b.record()
-        barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    step_ms = [a.elapsed_time(b) for a, b in ev]
-    total_ms = torch.tensor([sum(step_ms)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
-    ms_per_step = total_ms.item() / args.steps
-
-    per = ledger.summary()
-    launches = count_launches(ledger.timer.counts, 0)
+    w = Workload(wl, dev, args.seed, world, rank)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms_per_step, per, counts, clocks = timed_epochs(w, args.steps, args.warmup, sampler)
+    launches = count_launches(counts, 0)
 
     # ---- end to end: host buffers in, loss out, through the public API -------------------
     e2e = None
     if not args.no_e2e:
-        e2e = run_e2e(args, wl, d, model, opt, part, dev, world)
+        e2e = run_e2e(args, w)
+        dense.check_status(dev)
+    roof = roofline_of(per, args.steps, wl["name"])
+    setup_ms = w.setup_ms
+    fallbacks = dense.fallback_calls()
 
-    # ---- roofline of the dominant entry point (rank 0's view) ------------------------------
-    peak, peak_kind = measured_peak_gbs()
-    roof = None
-    hbm_bound = {k: v for k, v in per.items() if v["bytes"] > 0}  # the GEMM entries carry no byte count
-    if hbm_bound:
-        name = max(hbm_bound, key=lambda k: hbm_bound[k]["ms"])
-        p = per[name]
-        achieved = p["bytes"] / (p["ms"] * 1e-3) / 1e9 if p["ms"] > 0 else 0.0
-        roof = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak,
-                "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
-                "frac_of_8tbs": achieved / 8000.0, "traffic": traffic_from_profile(name, wl["name"]),
-                "launch_ms": p["ms"] / p["calls"], "bytes_per_launch": p["bytes"] / p["calls"],
-                "per_entry_point": {k: {"ms_per_step": v["ms"] / args.steps,
-                                        "gbs": v["bytes"] / (v["ms"] * 1e-3) / 1e9 if v["ms"] > 0 else 0.0,
-                                        "calls_per_step": v["calls"] / args.steps} for k, v in per.items()}}
-
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        ms, sample, cores = run_cpu_epochs(wl, 2, 1, args.seed)
-        cpu = {"value": ms, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+    single = rank == 0 and world == 1
+    models = gpu_ref = cpu = None
+    if single and (not args.no_models or not args.no_gpu_reference):
+        del w
+        release_device_memory()
+    if single and not args.no_models and args.workload == "C5":
+        models = {}
+        for name in ("C1", "C2", "C3", "C4"):
+            models[name] = model_record(name, dev, args.seed, min(args.steps, 10))
+    if single and not args.no_gpu_reference:
+        gpu_ref = gpu_reference_leg(dev, args.seed)
+        release_device_memory()
+    if single and not args.no_cpu_baseline:
+        cpu = run_cpu_epochs(wl, 2, 1, args.seed)
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": ms_per_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{wl['name']}: {wl['desc']}", "nodes": n, "edges": nnz,
-                       "parallelism": (f"row-block x{world}, {os.environ.get('GNN_B200_EXCHANGE', 'halo')} exchange"
-                                       if world > 1 else "single GPU"),
-                       "l2": "flushed between steps (256 MB write)" if flush else "inputs exceed L2 (126 MB)",
-                       "seed": args.seed},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roof, "cpu_baseline": cpu,
+            "config": config_of(wl, world),
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "setup_ms": setup_ms,
+            "cublas_fallback_calls": fallbacks, "roofline": roof, "cpu_baseline": cpu,
+            "models": models, "gpu_reference": gpu_ref,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -540,21 +806,14 @@ def main():
         dist.destroy_process_group()
 
 
-def traffic_from_profile(kernel: str, workload: str):
-    """DRAM bytes per launch measured once with ncu (profiles/traffic.json), or None."""
-    try:
-        t = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))
-        return t.get(workload, {}).get(kernel)
-    except Exception:
-        return None
-
-
-def run_e2e(args, wl, d, model, opt, part, dev, world):
+def run_e2e(args, w: Workload):
     """Same epoch, but every step starts from pinned HOST buffers (graph in CSR, inputs,
     labels), copies them to the device, builds the CSC with the csr2csc kernel
     (single GPU), runs forward/backward/update through the public layers API and reads
     the loss back."""
     from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+
+    wl, d, model, opt, part, dev, world = w.wl, w.d, w.model, w.opt, w.part, w.dev, w.world
 
     def pin(t):
         return t.detach().cpu().pin_memory()
@@ -622,19 +881,14 @@ def run_e2e(args, wl, d, model, opt, part, dev, world):
         opt.step()
         return loss.item()  # device -> host read of the result
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     one()
-    barrier()
+    barrier(world)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(args.steps):
         one()
     b.record()
-    barrier()
+    barrier(world)
     ms = torch.tensor([a.elapsed_time(b) / args.steps], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)

@@ -322,6 +322,40 @@ int gnn_edge_softmax_fwd(const int* row_ptr, int64_t n_rows, int64_t nnz, const 
 int gnn_edge_softmax_bwd(const int* row_ptr, int64_t n_rows, int64_t nnz, const float* y,
                          const float* grad_y, int H, float* grad_x, cudaStream_t stream);
 
+/* ---- k-nearest-neighbour graph of point clouds ----------------------------------------
+ * The graph EdgeConv runs on: the reference builds it with DGL's KNNGraph(k) in front of
+ * every layer (script/train/train_edgeconv_our.py:20,52).  points [n_clouds, n_points,
+ * n_coords] float32; src_ind[(b*P + i)*k + j] = b*P + index of the j-th nearest point of
+ * cloud b to its point i (the layout gnn_edgeconv_fwd reads).  Squared Euclidean distance
+ * in float64, coordinates summed in ascending order without fused multiply-add; neighbours
+ * ordered by (distance, index), so a point is its own first neighbour.  Nothing of size
+ * n_points x n_points is stored.  k <= 64, k <= n_points. */
+int gnn_knn_graph(const float* points, int64_t n_clouds, int64_t n_points, int n_coords, int k,
+                  int* src_ind /*[n_clouds*n_points*k]*/, cudaStream_t stream);
+
+/* ---- halo exchange over peer-mapped memory (no counterpart in the reference: single GPU) --
+ * gnn_peer_alloc: device memory other processes of the node can map; writes its IPC handle
+ * (GNN_PEER_HANDLE_BYTES bytes, host memory).  gnn_peer_open maps the allocation behind a
+ * handle received from another process (enabling peer access on first use) and returns the
+ * address it has in THIS process.  These four calls are for set-up: unlike the rest of the
+ * library they allocate / map device memory and may synchronise.
+ *
+ * gnn_halo_push: for i in [send_off[q], send_off[q+1]) stores row send_idx[i] of x
+ * (row_floats floats per row) to dst[q] + (i - send_off[q]) * row_floats, and rows
+ * [0, n_own) of x to own_dst (NULL: skip).  send_off [world+1] and dst [world] are HOST
+ * arrays; dst[q] is a device address in a peer's allocation (from gnn_peer_open), already
+ * advanced to where this rank's rows go.  Ordinary stores, no atomics.  The stores are
+ * visible to the peer once the kernel has completed: order that against the consumer with
+ * a collective or an event on `stream`. */
+#define GNN_MAX_PEERS 8
+#define GNN_PEER_HANDLE_BYTES 64
+int gnn_peer_alloc(size_t bytes, void** ptr, unsigned char* handle);
+int gnn_peer_free(void* ptr);
+int gnn_peer_open(const unsigned char* handle, void** ptr);
+int gnn_peer_close(void* ptr);
+int gnn_halo_push(const float* x, int64_t row_floats, const int* send_idx, const int64_t* send_off,
+                  float* const* dst, int world, float* own_dst, int64_t n_own, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

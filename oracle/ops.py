@@ -221,6 +221,26 @@ def edgeconv_layer_dgl(k, src_ind, x, theta_w, phi_w, dtype=torch.float64):
     return (ht[src] - ht[:, None, :]).max(dim=1).values + hp
 
 
+def knn_graph(points, k):
+    """The graph EdgeConv runs on: DGL's KNNGraph(k) as the reference's DGCNN script calls it
+    in front of every layer (script/train/train_edgeconv_our.py:20,52; DGL itself is absent).
+    Restated rule, which the kNN kernel is compared with bit for bit: per cloud, squared
+    Euclidean distance in float64 accumulated coordinate by coordinate (each square and each
+    sum rounded separately), the k smallest per point ordered by (distance, index) -- a stable
+    sort, so the point itself comes first and exact ties go to the lower index.
+    points (B,P,C) float32 -> int32 (B*P*k,), ids global over the batch."""
+    x = points.numpy().astype(np.float64)
+    B, P, C = x.shape
+    out = np.empty((B, P, k), dtype=np.int64)
+    for b in range(B):
+        d2 = np.zeros((P, P), dtype=np.float64)
+        for c in range(C):
+            diff = x[b, :, None, c] - x[b, None, :, c]
+            d2 = d2 + diff * diff
+        out[b] = np.argsort(d2, axis=1, kind="stable")[:, :k] + b * P
+    return torch.from_numpy(out.reshape(-1).astype(np.int32))
+
+
 # ---------------------------------------------------------------------------------
 # GMMConv
 # ---------------------------------------------------------------------------------

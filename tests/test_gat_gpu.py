@@ -9,7 +9,7 @@ from tests.util import assert_close, crafted_graphs, power_law_graph
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(1, 8), (4, 64), (4, 128), (8, 8), (1, 7), (1, 41), (1, 47), (2, 16), (3, 12), (1, 128),
-          (1, 256), (2, 100)]
+          (1, 256), (2, 100), (1, 5), (1, 13), (1, 30), (1, 61), (1, 63)]
 
 
 def _inputs(g, H, F, seed, n_cols=None):
@@ -54,7 +54,8 @@ def _square(g):
 
 
 @pytest.mark.parametrize("name", list(crafted_graphs().keys()))
-@pytest.mark.parametrize("H,F", [(4, 64), (4, 128), (8, 8), (1, 7), (1, 47), (2, 16), (3, 12)])
+@pytest.mark.parametrize("H,F", [(4, 64), (4, 128), (8, 8), (1, 7), (1, 47), (2, 16), (3, 12), (1, 13), (1, 30),
+                                 (1, 61)])
 def test_gat_backward_crafted(cuda, name, H, F):
     from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
     from ae_mlsys_gnn_b200.operators.fused_gat import gat_backward, gat_forward
@@ -274,7 +275,8 @@ def _one_gather(cuda, g, H, F, seed):
 
 
 @pytest.mark.parametrize("name", list(crafted_graphs().keys()))
-@pytest.mark.parametrize("H,F", [(4, 64), (4, 128), (8, 8), (1, 7), (1, 47), (2, 16), (3, 12)])
+@pytest.mark.parametrize("H,F", [(4, 64), (4, 128), (8, 8), (1, 7), (1, 47), (2, 16), (3, 12), (1, 13), (1, 30),
+                                 (1, 61)])
 def test_gat_one_gather_backward_crafted(cuda, name, H, F):
     g = _square(crafted_graphs()[name])
     got, two, exp = _one_gather(cuda, g, H, F, 12)
@@ -419,3 +421,21 @@ def test_gat_autograd_layer_with_elu(cuda, foreign_csc):
     assert_close(layer.attn_l.grad, al.grad, "attn_l.grad", scale_atol=True)
     assert_close(layer.attn_r.grad, ar.grad, "attn_r.grad", scale_atol=True)
     assert_close(xd.grad, xr.grad, "x.grad", scale_atol=True)
+
+
+def test_gat_forward_blocks_refuse_heads_wider_than_a_tile(cuda):
+    """A head wider than the largest tile is processed in column slabs; launching such a shape
+    block by block (state carried between launches) is refused instead of merging twice."""
+    from ae_mlsys_gnn_b200 import _capi
+    from ae_mlsys_gnn_b200.operators import fused_gat as G
+
+    g = power_law_graph(200, 8, seed=4)
+    H, F = 1, 640
+    attn_row, attn_col, feat, _ = _inputs(g, H, F, 4)
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    d = [t.to(cuda) for t in (attn_row, attn_col, feat)]
+    out, m, s = G.gat_forward(d[0], d[1], rp, ci, 0.2, d[2])           # one launch per slab: fine
+    eo, _, _ = ref.gat_forward(attn_row, attn_col, g.row_ptr, g.col_ind, 0.2, feat)
+    assert_close(out, eo, "out 1x640")
+    with pytest.raises(_capi.GnnError, match="column blocks"):
+        G.gat_forward_part(d[0], d[1], rp, ci, 0.2, d[2], out, m, s, True, True)

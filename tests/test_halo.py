@@ -49,7 +49,80 @@ def test_halo_plans_cover_the_graph(world):
         assert torch.equal(p.row_ind.long()[p.rs_pos.long()], ref.rows_of(p.rs_ptr))
 
 
-def _worker(rank, world, port, results, recompute):
+def _star_graph():
+    """One hub row holds almost all edges: some ranks own no rows at all, most nodes are isolated."""
+    from ae_mlsys_gnn_b200.graphs import Graph
+
+    n = 64
+    deg = torch.zeros(n, dtype=torch.long)
+    deg[5], deg[60] = 40, 2
+    rp = torch.zeros(n + 1, dtype=torch.int32)
+    rp[1:] = torch.cumsum(deg, 0).to(torch.int32)
+    ci = torch.cat([torch.arange(10, 50), torch.tensor([5, 63])]).to(torch.int32)
+    return Graph(n, rp, ci)
+
+
+def _graph(kind):
+    return _star_graph() if kind == "star" else power_law_graph(300, 10, seed=3)
+
+
+class SharedMemoryExchange:
+    """Factory of a CPU stand-in for halo.PeerStoreExchange: the peers' buffers are slices of
+    shared-memory tensors (one pool per rank, created before the ranks are spawned), the push is
+    an index copy into the peers' pools at the offsets the real kernel is given, and completion
+    is a barrier.  Exercises everything host-side of the peer-store exchange: halo sizes of all
+    ranks, destination offsets, the two alternating buffers per exchange point."""
+
+    def __init__(self, pools):
+        self.pools = pools
+
+    def __call__(self, part, group, small_group):
+        from ae_mlsys_gnn_b200.halo import PeerStoreExchange
+
+        pools = self.pools
+
+        class _Buf:
+            def __init__(self, off, nbytes, rank):
+                self.off, self.nbytes, self.rank = off, nbytes, rank
+
+            def view(self, shape, dtype=torch.float32):
+                numel = 1
+                for v in shape:
+                    numel *= int(v)
+                return pools[self.rank][self.off: self.off + numel].view(shape)
+
+            def close(self):
+                pass
+
+        class _Exchange(PeerStoreExchange):
+            def __init__(self, *a):
+                super().__init__(*a)
+                self._next = 0
+
+            def _alloc(self, nbytes, device):
+                floats = (nbytes + 3) // 4
+                off, self._next = self._next, self._next + floats
+                assert self._next <= pools[0].numel(), "test pool too small"
+                return _Buf(off, nbytes, self.rank)
+
+            def _push(self, x, plan, buf, row_bytes, n_local):
+                row = row_bytes // 4
+                xf = x.reshape(x.shape[0], row)
+                pos = 0
+                for q, cnt in enumerate(plan.send_splits):
+                    if cnt:
+                        start = buf.off + (self.n_locals[q] + plan.dst_off[q]) * row
+                        pools[q][start: start + cnt * row] = xf[plan.send_idx[pos: pos + cnt].long()].reshape(-1)
+                        pos += cnt
+                pools[self.rank][buf.off: buf.off + n_local * row] = xf[:n_local].reshape(-1)
+
+            def _complete(self, device):
+                dist.barrier()
+
+        return _Exchange(part, group, small_group)
+
+
+def _worker(rank, world, port, results, recompute, graph="powerlaw", pools=None):
     import os
 
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
@@ -58,7 +131,7 @@ def _worker(rank, world, port, results, recompute):
         from ae_mlsys_gnn_b200.halo import HaloGAT, build_halo_partition, halo_exchange, halo_return_sum
 
         torch.manual_seed(0)
-        g = power_law_graph(300, 10, seed=3)
+        g = _graph(graph)
         cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)
         x = torch.randn(g.n, 12, generator=torch.Generator().manual_seed(1))
         y = torch.randint(0, 5, (g.n,), generator=torch.Generator().manual_seed(2))
@@ -70,12 +143,15 @@ def _worker(rank, world, port, results, recompute):
         e0, e1 = int(g.row_ptr[lo]), int(g.row_ptr[hi])
         assert torch.equal(ext[part.col_ind.long(), 0].long(), g.col_ind.long()[e0:e1])
         back = halo_return_sum(torch.ones(part.n_local + part.bwd.n_halo, 1), part.bwd, part.n_local)
-        model = HaloGAT(12, [8], [2], 5, 1, kernels=OracleKernels)
+        exchange = "nccl" if pools is None else SharedMemoryExchange(pools)
+        model = HaloGAT(12, [8], [2], 5, 1, kernels=OracleKernels, exchange=exchange)
         for layer in model.gat_layers:
             layer.recompute_projection = recompute
-        out = model(part, part.local_slice(x))
-        loss = model.loss(part, out, part.local_slice(y))
-        loss.backward()
+        for _ in range(3 if pools is not None else 1):  # several steps: both buffers of every exchange point
+            model.zero_grad()
+            out = model(part, part.local_slice(x))
+            loss = model.loss(part, out, part.local_slice(y))
+            loss.backward()
         model.all_reduce_grads(world)
         total = loss.detach().clone()
         dist.all_reduce(total)
@@ -94,17 +170,21 @@ def _worker(rank, world, port, results, recompute):
 
 
 @pytest.mark.timeout(300)
-@pytest.mark.parametrize("world,recompute", [(2, False), (3, True), (8, "auto")])
-def test_halo_gat_matches_single(world, recompute):
+@pytest.mark.parametrize("world,recompute,graph,peer", [
+    (2, False, "powerlaw", False), (3, True, "powerlaw", False), (8, "auto", "powerlaw", False),
+    (4, False, "star", False),      # ranks with empty blocks still join every collective
+    (2, False, "powerlaw", True), (3, True, "powerlaw", True), (4, "auto", "star", True)])
+def test_halo_gat_matches_single(world, recompute, graph, peer):
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
     mgr = mp.Manager()
     results = mgr.dict()
-    mp.spawn(_worker, args=(world, port, results, recompute), nprocs=world, join=True)
+    pools = [torch.zeros(1 << 20).share_memory_() for _ in range(world)] if peer else None
+    mp.spawn(_worker, args=(world, port, results, recompute, graph, pools), nprocs=world, join=True)
 
-    g = power_law_graph(300, 10, seed=3)
+    g = _graph(graph)
     cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)
     # every node got 1 from its owner plus 1 from every other rank that has it in its backward halo
     assert results["back"].min() >= 1 and results["back"].max() <= world

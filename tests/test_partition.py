@@ -68,6 +68,13 @@ class OracleKernels:
         return _pad(pack.float(), pad_to)
 
     @staticmethod
+    def backward_pack_elu(out, grad_act, attn_row, edge_max, edge_sum):
+        n = edge_max.shape[0]
+        o = out.double()[:n]
+        grad_pre = (grad_act.double()[:n] * torch.where(o > 0, torch.ones_like(o), torch.exp(o))).float()
+        return grad_pre, OracleKernels.backward_pack(out, grad_pre, attn_row, edge_max, edge_sum)
+
+    @staticmethod
     def backward_col_edges_part(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full,
                                 grad_feat, grad_attn_col, accumulate):
         cols, rows = ref.rows_of(col_ptr), row_ind.long()   # segments are the owned sources
