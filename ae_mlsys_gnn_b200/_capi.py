@@ -31,6 +31,8 @@ PROTOTYPES = {
     "gnn_gat_fwd_workspace_bytes": [_I64, _INT, _INT, _SZP],
     "gnn_gat_fwd": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _INT, _INT, _F32,
                     _PTR, _PTR, _PTR, _PTR, _SZ, _PTR],
+    "gnn_gat_fwd_act": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _INT, _INT, _F32, _F32,
+                        _PTR, _PTR, _PTR, _PTR, _PTR, _SZ, _PTR],
     "gnn_gat_fwd_part": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _INT, _INT, _F32,
                          _PTR, _PTR, _PTR, _INT, _INT, _PTR, _SZ, _PTR],
     "gnn_gat_bwd_col_part": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _PTR, _INT, _INT, _F32,
@@ -139,7 +141,7 @@ def check(rc: int, what: str) -> None:
 # memsets excluded); bench.py uses it to count its own launches.
 KERNELS_PER_CALL = {
     "gnn_csr2csc": None,  # depends on the number of radix passes, see launches_csr2csc
-    "gnn_gat_fwd": 2, "gnn_gat_fwd_part": 2, "gnn_gat_bwd_col_part": 2,
+    "gnn_gat_fwd": 2, "gnn_gat_fwd_act": 2, "gnn_gat_fwd_part": 2, "gnn_gat_bwd_col_part": 2,
     "gnn_gat_fwd_static_scratch": 2, "gnn_gat_bwd": 4, "gnn_gat_bwd_row": 2, "gnn_gat_bwd_col": 2,
     "gnn_gat_scores_fwd": 1, "gnn_gat_scores_bwd": 2,
     # weight split + GEMM; GEMM + split reduction (plus one transposing pre-pass per operand

@@ -6,26 +6,6 @@ using namespace gnn;
 
 namespace {
 
-struct HeadPlan {
-  bool fused;   // all heads in one launch
-  bool vec;     // 128-bit row accesses
-  int HP;       // padded head count of the launch
-  int slab;     // columns per launch in the per-head fallback
-};
-
-// Decides how (H, F) maps onto the instantiated tiles.
-bool plan_heads(int H, int F, bool aligned, bool need_full_head, HeadPlan* pl) {
-  const bool vec = aligned && (F % 4 == 0);
-  const int cap = max_tile_width(vec);
-  if (H <= 8 && (int64_t)H * F <= cap) {
-    pl->fused = true; pl->vec = vec; pl->HP = next_pow2(H); pl->slab = H * F;
-    return true;
-  }
-  if (need_full_head && F > cap) return false;
-  pl->fused = false; pl->vec = vec; pl->HP = 1; pl->slab = F < cap ? F : cap;
-  return true;
-}
-
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // One head, rows of at most 64 floats that cannot be read with 128-bit accesses: the

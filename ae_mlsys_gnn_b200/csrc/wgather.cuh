@@ -56,6 +56,7 @@ struct WGatherParams {
 template <int HP>
 struct GatSoftmaxPolicy {
   static constexpr bool kSoftmax = true;
+  static constexpr bool kElu = false;
   const float* attn_seg;  // [nseg][ld_attn]
   const float* attn_idx;  // [*][ld_attn]
   int ld_attn;
@@ -64,11 +65,23 @@ struct GatSoftmaxPolicy {
   float* seg_sum;
 };
 
+// The same, and next to out[s] the activated row act[s] = ELU(out[s]) is stored: the
+// activation a model applies to the layer's output (script/train/train_gatconv_our.py:50-52)
+// costs no pass of its own.  The backward needs both: out for the softmax identity and for
+// ELU', act as the next layer's input.
+template <int HP>
+struct GatSoftmaxEluPolicy : GatSoftmaxPolicy<HP> {
+  static constexpr bool kElu = true;
+  float* act;    // [nseg] rows, leading dimension as `out`
+  float alpha;
+};
+
 // Stored edge values att[e*ld + h] (nullptr: weight one).  When perm is given
 // the value of edge e is att[perm[e]*ld + h].
 template <int HP>
 struct EdgeValuePolicy {
   static constexpr bool kSoftmax = false;
+  static constexpr bool kElu = false;
   const float* att;
   const int* perm;
   int ld_att;
@@ -80,6 +93,7 @@ struct EdgeValuePolicy {
 template <int HP>
 struct GaussPolicy {
   static constexpr bool kSoftmax = false;
+  static constexpr bool kElu = false;
   const float* pseudo;  // [E][D]
   const float* mu;      // [K][D]
   const float* inv_sigma;
@@ -187,6 +201,14 @@ __device__ __forceinline__ void finish_segment(const WGatherParams& p, const Pol
     }
   }
   t.store(orow, lane, acc);
+  if constexpr (Policy<HP>::kElu) {
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+#pragma unroll
+      for (int i = 0; i < VW; ++i)  // exp2-based exponential: absolute error below 1e-6, a few instructions per element
+        acc[q][i] = acc[q][i] > 0.f ? acc[q][i] : pol.alpha * (__expf(acc[q][i]) - 1.f);
+    t.store(pol.act + (size_t)s * p.ld_out, lane, acc);
+  }
 }
 
 // ----- main kernel ----------------------------------------------------------
@@ -408,6 +430,7 @@ wgather_fixup_kernel(WGatherParams p, Policy<HP> pol, int boundary_blocks) {
       const int se = s - lane + src;
       if (!p.accumulate) {
         t.store(p.out + (size_t)se * p.ld_out, lane, z);
+        if constexpr (Policy<HP>::kElu) t.store(pol.act + (size_t)se * p.ld_out, lane, z);
         if constexpr (SOFTMAX) {
           if (lane < p.H) {
             pol.seg_max[(size_t)se * pol.ld_attn + lane] = kNegBig;
@@ -486,6 +509,26 @@ inline bool dispatch_tile(int HP, int width, bool vec, Fn&& fn) {
 }
 
 inline int max_tile_width(bool vec) { return vec ? 512 : 256; }
+
+// How (H, F) maps onto the instantiated tiles.
+struct HeadPlan {
+  bool fused;   // all heads in one launch
+  bool vec;     // 128-bit row accesses
+  int HP;       // padded head count of the launch
+  int slab;     // columns per launch in the per-head fallback
+};
+
+inline bool plan_heads(int H, int F, bool aligned, bool need_full_head, HeadPlan* pl) {
+  const bool vec = aligned && (F % 4 == 0);
+  const int cap = max_tile_width(vec);
+  if (H <= 8 && (int64_t)H * F <= cap) {
+    pl->fused = true; pl->vec = vec; pl->HP = next_pow2(H); pl->slab = H * F;
+    return true;
+  }
+  if (need_full_head && F > cap) return false;
+  pl->fused = false; pl->vec = vec; pl->HP = 1; pl->slab = F < cap ? F : cap;
+  return true;
+}
 
 // The merge of split segments and the defaults of empty segments (second launch of every
 // weighted gather).

@@ -209,26 +209,47 @@ def halo_return_sum(x_ext: torch.Tensor, plan: ExchangePlan, n_local: int, group
 
 
 class NcclExchange:
-    """Moves halo rows with ``all_to_all_single`` (any backend of torch.distributed)."""
+    """Moves halo rows with ``all_to_all_single`` (any backend of torch.distributed).
+
+    Protocol of both exchange classes: ``open`` hands out the extended tensors [own | halo] of
+    one exchange point, the caller fills rows [0, n_local) (ideally the producing kernel writes
+    there directly), ``push`` moves those rows into the other ranks' halo regions and returns
+    once everything enqueued afterwards may read the halo rows.  ``exchange`` = open + copy +
+    push for tensors that already exist."""
 
     def __init__(self, part: "HaloPartition", group=None, small_group=None):
         self.group, self.small_group = group, small_group
 
+    def open(self, key, tails, plan: ExchangePlan, n_local: int, device):
+        rows = n_local + (plan.n_halo if plan.active else 0)
+        return [torch.empty((rows,) + tuple(t), dtype=torch.float32, device=device) for t in tails]
+
+    def push(self, key, exts, plan: ExchangePlan, n_local: int):
+        if not plan.active:
+            return
+        pending = []
+        for i, ext in enumerate(exts):  # the first, wide tensor on the main communicator, the rest on the second
+            send = ext[:n_local].index_select(0, plan.send_idx)
+            work = dist.all_to_all_single(ext[n_local:], send, output_split_sizes=plan.recv_splits,
+                                          input_split_sizes=plan.send_splits,
+                                          group=self.group if i == 0 else self.small_group,
+                                          async_op=(i == 0 and len(exts) > 1))
+            if work is not None and i == 0 and len(exts) > 1:
+                pending.append((work, send))
+        for work, _ in pending:
+            work.wait()
+
     def exchange(self, key, tensors, plan: ExchangePlan, n_local: int):
-        """Extended copies [own | halo] of all ``tensors`` (same plan).  The first, wide one
-        travels on the main communicator while the others use the second."""
-        if len(tensors) == 1:
-            return [halo_exchange(tensors[0], plan, n_local, self.group)[0]]
-        first, pending = halo_exchange(tensors[0], plan, n_local, self.group, async_op=True)
-        rest = [halo_exchange(t, plan, n_local, self.small_group)[0] for t in tensors[1:]]
-        if pending is not None:
-            pending[0].wait()
-        return [first] + rest
+        exts = self.open(key, [t.shape[1:] for t in tensors], plan, n_local, tensors[0].device)
+        for e, t in zip(exts, tensors):
+            e[:n_local] = t[:n_local]
+        self.push(key, exts, plan, n_local)
+        return exts
 
 
-class PeerStoreExchange:
+class PeerStoreExchange(NcclExchange):
     """Moves halo rows with one store kernel per tensor into peer-mapped buffers (see the module
-    docstring).  ``exchange`` is collective and must be called by every rank with the same
+    docstring).  ``open`` / ``push`` are collective and must be called by every rank with the same
     sequence of keys; the buffers of a key are allocated at its first use."""
 
     def __init__(self, part: "HaloPartition", group=None, small_group=None):
@@ -237,6 +258,7 @@ class PeerStoreExchange:
         self.rank, self.world = part.rank, part.world
         self.n_locals = [part.bounds[q + 1] - part.bounds[q] for q in range(part.world)]
         self._slots = {}   # key -> [buffers of use 0, buffers of use 1, next use]
+        self._open = {}    # key -> buffers handed out by the last open()
         self._flag = None
 
     # -- overridable pieces (a CPU stand-in for tests replaces them) -------------------------
@@ -245,7 +267,8 @@ class PeerStoreExchange:
 
         return PeerBuffer(nbytes, device, self.group)
 
-    def _push(self, x, plan, buf, row_bytes, n_local):
+    def _push(self, ext, plan, buf, row_bytes, n_local):
+        """Stores the rows of ``ext`` (this rank's buffer) listed in the plan into the peers' buffers."""
         from .peer import halo_push
 
         offs = [0]
@@ -253,7 +276,7 @@ class PeerStoreExchange:
             offs.append(offs[-1] + int(c))
         dst = [0 if q == self.rank or plan.send_splits[q] == 0
                else buf.ptrs[q] + (self.n_locals[q] + plan.dst_off[q]) * row_bytes for q in range(self.world)]
-        halo_push(x, plan.send_idx32, offs, dst, buf.ptrs[self.rank], n_local)
+        halo_push(ext, plan.send_idx32, offs, dst, 0, 0)
 
     def _complete(self, device):
         """Every rank's push kernels are complete before anything enqueued after this call runs."""
@@ -262,28 +285,31 @@ class PeerStoreExchange:
         dist.all_reduce(self._flag, group=self.small_group)
 
     # ----------------------------------------------------------------------------------------
-    def exchange(self, key, tensors, plan: ExchangePlan, n_local: int):
-        tensors = [t.contiguous() for t in tensors]
+    def open(self, key, tails, plan: ExchangePlan, n_local: int, device):
         if not plan.active:
-            return [t[:n_local] for t in tensors]
-        dev = tensors[0].device
+            return [torch.empty((n_local,) + tuple(t), dtype=torch.float32, device=device) for t in tails]
         rows_max = max(n + h for n, h in zip(self.n_locals, plan.halo_sizes))
-        rows = n_local + plan.n_halo
-        row_bytes = [4 * math.prod(t.shape[1:]) for t in tensors]
+        row_bytes = [4 * math.prod(t) for t in tails]
         slot = self._slots.get(key)
         if slot is None:
-            slot = [[self._alloc(rows_max * rb, dev) for rb in row_bytes] for _ in range(2)] + [0]
+            slot = [[self._alloc(rows_max * rb, device) for rb in row_bytes] for _ in range(2)] + [0]
             self._slots[key] = slot
         bufs = slot[slot[2]]
         slot[2] ^= 1
-        out = []
-        for t, buf, rb in zip(tensors, bufs, row_bytes):
+        for buf, rb in zip(bufs, row_bytes):
             if rows_max * rb > buf.nbytes:
                 raise ValueError(f"exchange {key!r}: rows changed width since its buffers were allocated")
-            self._push(t, plan, buf, rb, n_local)
-            out.append(buf.view((rows,) + tuple(t.shape[1:]), torch.float32))
-        self._complete(dev)
-        return out
+        self._open[key] = (bufs, row_bytes)
+        rows = n_local + plan.n_halo
+        return [buf.view((rows,) + tuple(t), torch.float32) for buf, t in zip(bufs, tails)]
+
+    def push(self, key, exts, plan: ExchangePlan, n_local: int):
+        if not plan.active:
+            return
+        bufs, row_bytes = self._open.pop(key)
+        for ext, buf, rb in zip(exts, bufs, row_bytes):
+            self._push(ext, plan, buf, rb, n_local)
+        self._complete(exts[0].device)
 
     def close(self):
         for slot in self._slots.values():
@@ -305,30 +331,39 @@ def make_exchange(kind, part, group=None, small_group=None):
 
 class HaloGATFunction(torch.autograd.Function):
     """Scores + fused GAT aggregation (+ optional ELU) on a halo partition, one autograd node.
-    ``h`` and the output have n_local rows.  ``exch`` moves the halo rows; ``key`` names this
-    layer's exchange points."""
+    ``h`` (n_local rows) is the front of ``h_ext`` ([own | halo] rows).  ``ac_ext`` is the buffer of
+    the extended source scores opened together with ``h_ext``; None means the halo rows of ``h_ext``
+    are already there (the caller projected the halo's inputs) and only the scores travel.  ``exch`` moves the rows; ``key`` names this layer's exchange points."""
 
     @staticmethod
-    def forward(ctx, h, attn_l, attn_r, part: HaloPartition, slope, kernels, exch, key, activation=None,
-                h_halo=None):
+    def forward(ctx, h, attn_l, attn_r, part: HaloPartition, slope, kernels, exch, key, activation, h_ext,
+                ac_ext):
+        halo_ready = ac_ext is None
         n = part.n_local
-        h, attn_l, attn_r = h.contiguous(), attn_l.contiguous(), attn_r.contiguous()
+        attn_l, attn_r = attn_l.contiguous(), attn_r.contiguous()
         H, Fo = h.shape[1], h.shape[2]
         attn_row, attn_col = kernels.scores_forward(h, attn_l, attn_r)
-        if h_halo is None:
-            h_ext, ac_ext = exch.exchange((key, "fwd"), [h, attn_col], part.fwd, n)
-        else:  # the caller projected the halo inputs itself: nothing wide to move
-            h_ext = torch.cat([h, h_halo])
+        if halo_ready:
             (ac_ext,) = exch.exchange((key, "fwd_attn"), [attn_col], part.fwd, n)
-        out = h.new_empty((n, H, Fo))
-        edge_max = h.new_empty((n, H))
-        edge_sum = h.new_empty((n, H))
-        kernels.forward_part(attn_row, ac_ext, part.row_ptr, part.col_ind, slope, h_ext, out, edge_max,
-                             edge_sum, False, True)
+        else:  # h_ext and ac_ext came from one exch.open((key, "fwd"), ...): one push, one completion
+            ac_ext[:n] = attn_col
+            exch.push((key, "fwd"), [h_ext, ac_ext], part.fwd, n)
+        act = None
+        if activation == "elu" and hasattr(kernels, "forward_act"):  # ELU stored by the forward kernel
+            out, act, edge_max, edge_sum = kernels.forward_act(attn_row, ac_ext, part.row_ptr, part.col_ind,
+                                                               slope, h_ext)
+        else:
+            out = h.new_empty((n, H, Fo))
+            edge_max = h.new_empty((n, H))
+            edge_sum = h.new_empty((n, H))
+            kernels.forward_part(attn_row, ac_ext, part.row_ptr, part.col_ind, slope, h_ext, out, edge_max,
+                                 edge_sum, False, True)
+            if activation == "elu":
+                act = F.elu(out)
         ctx.save_for_backward(attn_row, attn_col, h, edge_max, edge_sum, attn_l, attn_r, out)
         ctx.part, ctx.slope, ctx.kernels = part, slope, kernels
         ctx.exch, ctx.key, ctx.activation = exch, key, activation
-        return F.elu(out) if activation == "elu" else out
+        return out if act is None else act
 
     @staticmethod
     def backward(ctx, grad_out):
@@ -337,11 +372,24 @@ class HaloGATFunction(torch.autograd.Function):
         n = part.n_local
         H, Fo = h.shape[1], h.shape[2]
         grad_out = grad_out.contiguous()
+        # the rows the column pass gathers (gradient w.r.t. the pre-activation output, per-row
+        # record) are produced straight into the front of the exchange buffers
+        gout_ext, rp_ext = exch.open((ctx.key, "bwd"), [(H, Fo), (4, H)], part.bwd, n, h.device)
+        direct = getattr(kernels, "writes_into", False)
         if ctx.activation == "elu":  # the ELU backward rides on the node-wise per-row pack
-            grad_out, rowpack = kernels.backward_pack_elu(out, grad_out, attn_row, edge_max, edge_sum)
+            if direct:
+                kernels.backward_pack_elu(out, grad_out, attn_row, edge_max, edge_sum, grad_pre=gout_ext,
+                                          rowpack=rp_ext)
+            else:
+                g, rp = kernels.backward_pack_elu(out, grad_out, attn_row, edge_max, edge_sum)
+                gout_ext[:n], rp_ext[:n] = g, rp
         else:
-            rowpack = kernels.backward_pack(out, grad_out, attn_row, edge_max, edge_sum)
-        gout_ext, rp_ext = exch.exchange((ctx.key, "bwd"), [grad_out, rowpack], part.bwd, n)
+            gout_ext[:n] = grad_out
+            if direct:
+                kernels.backward_pack(out, grad_out, attn_row, edge_max, edge_sum, rowpack=rp_ext)
+            else:
+                rp_ext[:n] = kernels.backward_pack(out, grad_out, attn_row, edge_max, edge_sum)
+        exch.push((ctx.key, "bwd"), [gout_ext, rp_ext], part.bwd, n)
         gh = h.new_empty((n, H, Fo))
         gac = h.new_empty((n, H))
         edge_grad = kernels.backward_col_edges_part(slope, part.col_ptr, part.row_ind, h, attn_col, rp_ext,
@@ -349,7 +397,7 @@ class HaloGATFunction(torch.autograd.Function):
         gar_ext = kernels.backward_row_sum(part.rs_ptr, part.rs_pos, edge_grad)
         gar = halo_return_sum(gar_ext, part.bwd, n, exch.small_group)
         gl, gr = kernels.scores_backward(h, attn_l, attn_r, gar, gac, gh)
-        return gh, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None, None, None
+        return gh, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None, None, None, None
 
 
 class HaloGATConv(_GATBase):
@@ -375,18 +423,22 @@ class HaloGATConv(_GATBase):
         return bool(self.recompute_projection)
 
     def forward(self, part: HaloPartition, feat, exch):
-        h_halo = None
+        n, H, Fo = part.n_local, self.num_heads, self.out_feats
         if self._recompute(part):
-            # the narrow inputs travel first; the own rows are projected while they do
+            # the narrow inputs travel first; both projections write into one [own | halo] tensor
             with torch.no_grad():
-                (x_ext,) = exch.exchange((self.key, "fwd_x"), [feat.detach()], part.fwd, part.n_local)
-        h = dense.project(feat, self.W).view(-1, self.num_heads, self.out_feats)
-        if self._recompute(part):
-            with torch.no_grad():
-                h_halo = dense.project(x_ext[part.n_local:].contiguous(), self.W.detach()).view(
-                    -1, self.num_heads, self.out_feats)
+                (x_ext,) = exch.exchange((self.key, "fwd_x"), [feat.detach()], part.fwd, n)
+            h_ext = feat.new_empty((x_ext.shape[0], H, Fo))
+            h = dense.project(feat, self.W, out=dense.OutRows(h_ext, 0)).view(-1, H, Fo)
+            if x_ext.shape[0] > n:
+                with torch.no_grad():
+                    dense.project(x_ext[n:], self.W.detach(), out=dense.OutRows(h_ext, n))
+            ac_ext = None  # only the scores of the halo are still to be exchanged
+        else:
+            h_ext, ac_ext = exch.open((self.key, "fwd"), [(H, Fo), (H,)], part.fwd, n, feat.device)
+            h = dense.project(feat, self.W, out=dense.OutRows(h_ext, 0)).view(-1, H, Fo)
         return HaloGATFunction.apply(h, self.attn_l, self.attn_r, part, self.negative_slope,
-                                     self.kernels, exch, self.key, self.activation, h_halo)
+                                     self.kernels, exch, self.key, self.activation, h_ext, ac_ext)
 
 
 class HaloGAT(nn.Module):

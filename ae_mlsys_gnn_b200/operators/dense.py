@@ -63,7 +63,25 @@ def supported(m: int, n: int, k: int, a: torch.Tensor) -> bool:
             and bool(capi.lib().gnn_gemm_tf32x3_supported(m, n, k4)))
 
 
-def gemm(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool) -> torch.Tensor:
+class OutRows:
+    """Where a product is to be written: rows [start, start + M) of ``base`` (rows, N), e.g. the
+    front of a buffer whose remaining rows other ranks fill.  Not a tensor argument on purpose:
+    autograd then sees the returned view as an ordinary fresh output of the product."""
+
+    def __init__(self, base: torch.Tensor, start: int = 0):
+        self.base, self.start = base, int(start)
+
+    def rows(self, m: int, n: int) -> torch.Tensor:
+        width = 1
+        for d in self.base.shape[1:]:
+            width *= int(d)
+        flat = self.base.view(self.base.shape[0], width)
+        if flat.shape[1] != n or self.start + m > flat.shape[0] or not flat.is_contiguous():
+            raise ValueError("output rows do not fit the given buffer")
+        return flat[self.start: self.start + m]
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool, out: "OutRows | None" = None) -> torch.Tensor:
     """a (M,K) times b, where b is (K,N) or, with ``b_is_n_by_k``, (N,K)."""
     dev = a.device
     capi.require(a, F32, "a", 2)
@@ -72,7 +90,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool) -> torch.Tensor:
     N = b.shape[0] if b_is_n_by_k else b.shape[1]
     if (b.shape[1] if b_is_n_by_k else b.shape[0]) != K:
         raise ValueError(f"inner dimensions differ: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
-    out = torch.empty((M, N), dtype=F32, device=dev)
+    out = torch.empty((M, N), dtype=F32, device=dev) if out is None else out.rows(M, N)
     nbytes = capi.workspace_bytes("gnn_gemm_tf32x3_workspace_bytes", M, N, K)
     ws = capi.workspace(dev, nbytes)
     with torch.cuda.device(dev):
@@ -81,7 +99,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool) -> torch.Tensor:
     return out
 
 
-def gemm_any_k(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool) -> torch.Tensor:
+def gemm_any_k(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool, out: "OutRows | None" = None) -> torch.Tensor:
     """``gemm`` for any inner dimension: TMA reads rows whose length is a multiple of 4 floats,
     so other lengths (an input width of 602, a gradient with 47 columns) are padded with zero
     columns first -- one copy of ``a``, far cheaper than leaving the product to an fp32 SIMT GEMM."""
@@ -92,7 +110,7 @@ def gemm_any_k(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool) -> torch.Ten
     a = a.contiguous()
     if a.data_ptr() % 16:  # a view that starts at an odd offset of its storage
         a = a.clone()
-    return gemm(a, b.contiguous(), b_is_n_by_k)
+    return gemm(a, b.contiguous(), b_is_n_by_k, out)
 
 
 def gemm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
@@ -119,12 +137,12 @@ TN_MIN_ROWS = 4096
 
 class _MatmulFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, w_is_out_by_in):
+    def forward(ctx, x, w, w_is_out_by_in, out=None):
         x = x.contiguous()
         w = w.contiguous()
         ctx.save_for_backward(x, w)
         ctx.w_is_out_by_in = w_is_out_by_in
-        return gemm_any_k(x, w, w_is_out_by_in)
+        return gemm_any_k(x, w, w_is_out_by_in, out)
 
     @staticmethod
     def backward(ctx, g):
@@ -145,20 +163,26 @@ class _MatmulFunction(torch.autograd.Function):
             else:
                 _note_fallback()
                 gw = (g.t() @ x) if ctx.w_is_out_by_in else (x.t() @ g)
-        return gx, gw, None
+        return gx, gw, None, None
 
 
-def matmul_tf32x3(x, w):
+def matmul_tf32x3(x, w, out=None):
     """x (M,K) @ w (K,N)."""
-    return _MatmulFunction.apply(x, w, False)
+    return _MatmulFunction.apply(x, w, False, out)
 
 
-def project(x, w):
-    """x @ w, on the tensor cores for CUDA fp32 matrices."""
+def project(x, w, out: "OutRows | None" = None):
+    """x @ w, on the tensor cores for CUDA fp32 matrices.  ``out``: rows of an existing buffer to
+    write the product into (the returned tensor is then that view)."""
     if x.dim() == 2 and supported(x.shape[0], w.shape[1], w.shape[0], x):
-        return matmul_tf32x3(x, w)
+        return matmul_tf32x3(x, w, out)
     _note_fallback()
-    return torch.matmul(x, w)
+    res = torch.matmul(x, w)
+    if out is None:
+        return res
+    dst = out.rows(res.shape[0], res.shape[1])
+    dst.copy_(res.detach())
+    return res
 
 
 def linear(x, weight):

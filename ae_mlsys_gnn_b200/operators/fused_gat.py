@@ -102,6 +102,34 @@ def gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, p
     return out, edge_max, edge_sum
 
 
+def gat_forward_act(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat, alpha=1.0, out=None,
+                    act=None):
+    """(out, elu(out), edge_max, edge_sum): ``gat_forward`` with the ELU a model applies to the layer
+    output stored by the same kernel.  ``out`` / ``act`` may be given (n_rows, H, F) buffers."""
+    dev = in_feat.device
+    capi.require(in_feat, F32, "in_feat", 3)
+    n_rows = row_ptr.numel() - 1
+    H, F = in_feat.shape[1], in_feat.shape[2]
+    capi.require(attn_row, F32, "attn_row", 2, dev)
+    capi.require(attn_col, F32, "attn_col", 2, dev)
+    _check_graph(row_ptr, col_ind, dev)
+    if attn_row.shape[0] < n_rows or attn_row.shape[1] != H:
+        raise ValueError(f"attn_row must be (>= {n_rows}, {H}), got {tuple(attn_row.shape)}")
+    nnz = col_ind.numel()
+    out = torch.empty((n_rows, H, F), dtype=F32, device=dev) if out is None else capi.require(out, F32, "out", 3, dev)
+    act = torch.empty((n_rows, H, F), dtype=F32, device=dev) if act is None else capi.require(act, F32, "act", 3, dev)
+    edge_max = torch.empty((n_rows, H), dtype=F32, device=dev)
+    edge_sum = torch.empty((n_rows, H), dtype=F32, device=dev)
+    nbytes = capi.workspace_bytes("gnn_gat_fwd_workspace_bytes", nnz, H, F)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_fwd_act", capi.ptr(row_ptr), capi.ptr(col_ind), n_rows, nnz,
+                  capi.ptr(attn_row), capi.ptr(attn_col), capi.ptr(in_feat), H, F,
+                  float(negative_slope), float(alpha), capi.ptr(out), capi.ptr(act), capi.ptr(edge_max),
+                  capi.ptr(edge_sum), capi.ptr(ws), ws.numel(), capi.stream_ptr(dev))
+    return out, act, edge_max, edge_sum
+
+
 def gat_backward(negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum,
                  in_feat, attn_row, attn_col, grad_out):
     """(grad_feat, grad_attn_row, grad_attn_col) — fused_gat_SM.gat_backward
@@ -188,10 +216,10 @@ def gat_backward_col(negative_slope, col_ptr, row_ind, in_feat, attn_col, rowpac
     return grad_feat, grad_attn_col
 
 
-def gat_backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=None):
+def gat_backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=None, rowpack=None):
     """rowpack (n, 4, H) = {attn_row, edge_max, 1/edge_sum, S} with S = <grad_out, out> per
     head: the per-row record of the column pass, from the forward output instead of a pass
-    over the edges."""
+    over the edges.  ``rowpack``: an existing (>= n, 4, H) buffer to write into."""
     dev = out.device
     capi.require(out, F32, "out", 3)
     capi.require(grad_out, F32, "grad_out", 3, dev)
@@ -200,16 +228,20 @@ def gat_backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=None):
         capi.require(t, F32, name, 2, dev)
     if out.shape[0] < n or grad_out.shape[0] < n or attn_row.shape[0] < n:
         raise ValueError("out / grad_out / attn_row need at least one row per edge_max row")
-    rowpack = _rows(n, pad_to, (4, H), dev)
+    if rowpack is None:
+        rowpack = _rows(n, pad_to, (4, H), dev)
+    else:
+        capi.require(rowpack, F32, "rowpack", 3, dev)
     with torch.cuda.device(dev):
         capi.call("gnn_gat_bwd_pack", n, capi.ptr(out), capi.ptr(grad_out), capi.ptr(attn_row),
                   capi.ptr(edge_max), capi.ptr(edge_sum), H, F, capi.ptr(rowpack), capi.stream_ptr(dev))
     return rowpack
 
 
-def gat_backward_pack_elu(out, grad_act, attn_row, edge_max, edge_sum, alpha=1.0):
+def gat_backward_pack_elu(out, grad_act, attn_row, edge_max, edge_sum, alpha=1.0, grad_pre=None, rowpack=None):
     """(grad_pre, rowpack) for a layer output that went through ELU: ``grad_act`` is the gradient
-    with respect to elu(out); grad_pre = grad_act * elu'(out) is what the column pass takes."""
+    with respect to elu(out); grad_pre = grad_act * elu'(out) is what the column pass takes.
+    ``grad_pre`` / ``rowpack``: existing (>= n, H, F) / (>= n, 4, H) buffers to write into."""
     dev = out.device
     capi.require(out, F32, "out", 3)
     capi.require(grad_act, F32, "grad_act", 3, dev)
@@ -218,8 +250,10 @@ def gat_backward_pack_elu(out, grad_act, attn_row, edge_max, edge_sum, alpha=1.0
         capi.require(t, F32, name, 2, dev)
     if out.shape[0] < n or grad_act.shape[0] < n or attn_row.shape[0] < n:
         raise ValueError("out / grad_act / attn_row need at least one row per edge_max row")
-    grad_pre = torch.empty((n, H, F), dtype=F32, device=dev)
-    rowpack = torch.empty((n, 4, H), dtype=F32, device=dev)
+    grad_pre = (torch.empty((n, H, F), dtype=F32, device=dev) if grad_pre is None
+                else capi.require(grad_pre, F32, "grad_pre", 3, dev))
+    rowpack = (torch.empty((n, 4, H), dtype=F32, device=dev) if rowpack is None
+               else capi.require(rowpack, F32, "rowpack", 3, dev))
     with torch.cuda.device(dev):
         capi.call("gnn_gat_bwd_pack_elu", n, capi.ptr(out), capi.ptr(grad_act), capi.ptr(attn_row),
                   capi.ptr(edge_max), capi.ptr(edge_sum), H, F, float(alpha), capi.ptr(grad_pre),
@@ -445,14 +479,18 @@ class FusedGATLayerFunction(torch.autograd.Function):
         h = h.contiguous()
         attn_l, attn_r = attn_l.contiguous(), attn_r.contiguous()
         attn_row, attn_col = gat_scores_forward(h, attn_l, attn_r)
-        out, edge_max, edge_sum = gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, h)
+        # with an activation the node returns elu(out), stored by the forward kernel itself, and
+        # keeps out: its backward folds the activation's derivative into the per-row pack
+        act = None
+        if activation == "elu":
+            out, act, edge_max, edge_sum = gat_forward_act(attn_row, attn_col, row_ptr, col_ind, negative_slope, h)
+        else:
+            out, edge_max, edge_sum = gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, h)
         ctx.save_for_backward(row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, h, attn_row,
                               attn_col, attn_l, attn_r, out)
         ctx.negative_slope = negative_slope
         ctx.activation = activation
-        # with an activation the node returns elu(out) and keeps out: its backward folds the
-        # activation's derivative into the per-row pack instead of a separate pass
-        return torch.nn.functional.elu(out) if activation == "elu" else out
+        return out if act is None else act
 
     @staticmethod
     def backward(ctx, grad_out):

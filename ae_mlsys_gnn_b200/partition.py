@@ -267,16 +267,26 @@ class _CudaKernels:
                          edge_sum, accumulate, finalize)
 
     @staticmethod
-    def backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=None):
-        from .operators.fused_gat import gat_backward_pack
+    def forward_act(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full):
+        """(out, elu(out), edge_max, edge_sum) of one launch over the whole block."""
+        from .operators.fused_gat import gat_forward_act
 
-        return gat_backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=pad_to)
+        return gat_forward_act(attn_row, attn_col_full, row_ptr, col_ind, slope, h_full)
+
+    writes_into = True  # backward_pack / backward_pack_elu accept the buffers to write into
 
     @staticmethod
-    def backward_pack_elu(out, grad_act, attn_row, edge_max, edge_sum):
+    def backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=None, rowpack=None):
+        from .operators.fused_gat import gat_backward_pack
+
+        return gat_backward_pack(out, grad_out, attn_row, edge_max, edge_sum, pad_to=pad_to, rowpack=rowpack)
+
+    @staticmethod
+    def backward_pack_elu(out, grad_act, attn_row, edge_max, edge_sum, grad_pre=None, rowpack=None):
         from .operators.fused_gat import gat_backward_pack_elu
 
-        return gat_backward_pack_elu(out, grad_act, attn_row, edge_max, edge_sum)
+        return gat_backward_pack_elu(out, grad_act, attn_row, edge_max, edge_sum, grad_pre=grad_pre,
+                                     rowpack=rowpack)
 
     @staticmethod
     def backward_col_edges_part(slope, col_ptr, row_ind, h_local, attn_col_local, rowpack_full, gout_full,

@@ -188,6 +188,7 @@ class BytesLedger:
         self.timer = _capi.CallTimer(with_events=True)
         self.bytes: list[float] = []
         self.keys: list[str] = []
+        self.link_bytes: dict[str, float] = {}  # bytes stored into other GPUs' memory, per push key
         self._orig = _capi.call
 
     def __enter__(self):
@@ -197,8 +198,11 @@ class BytesLedger:
 
         def call(name, *args):
             b, shape = ledger._bytes_of(name, args)
+            key = f"{name}[{shape}]" if shape else name
             ledger.bytes.append(b)
-            ledger.keys.append(f"{name}[{shape}]" if shape else name)
+            ledger.keys.append(key)
+            if name == "gnn_halo_push":  # (x, row_floats, send_idx, send_off[world+1], dst, world, ...)
+                ledger.link_bytes[key] = ledger.link_bytes.get(key, 0.0) + 4.0 * args[1] * args[3][args[5]]
             orig(name, *args)
 
         capi.call = call  # operator modules look the function up as capi.call at call time
@@ -239,6 +243,8 @@ class BytesLedger:
             return 0.0, f"{a[4]}x{a[5]}x{a[6]}"
         if name == "gnn_gemm_tf32x3_tn":
             return 0.0, f"{a[3]}x{a[4]}x{a[5]}"
+        if name == "gnn_halo_push":
+            return 0.0, f"{a[1]}"
         return 0.0, ""
 
     def summary(self):
@@ -630,7 +636,11 @@ def timed_epochs(w: Workload, steps: int, warmup: int, sampler=None):
     total_ms = torch.tensor([sum(a.elapsed_time(b) for a, b in ev)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
-    return total_ms.item() / steps, ledger.summary(), dict(ledger.timer.counts), clocks
+    per = ledger.summary()
+    for key, nbytes in ledger.link_bytes.items():  # NVLink side of the exchange kernels
+        if key in per and per[key]["ms"] > 0:
+            per[key]["link_bytes"] = nbytes
+    return total_ms.item() / steps, per, dict(ledger.timer.counts), clocks
 
 
 def graphed_epoch_ms(w: Workload, steps: int):
@@ -679,6 +689,9 @@ def roofline_of(per: dict, steps: int, workload: str):
     entries = {}
     for k, v in per.items():
         e = {"ms_per_step": v["ms"] / steps, "calls_per_step": v["calls"] / steps}
+        if v.get("link_bytes"):
+            e["nvlink_gb_per_step"] = v["link_bytes"] / steps / 1e9
+            e["nvlink_gbs"] = v["link_bytes"] / (v["ms"] * 1e-3) / 1e9
         if v["bytes"] > 0 and v["ms"] > 0:
             e["gbs_algorithmic"] = v["bytes"] / (v["ms"] * 1e-3) / 1e9
             t = traffic_from_profile(k, workload)
@@ -773,6 +786,8 @@ def main():
         dense.check_status(dev)
     roof = roofline_of(per, args.steps, wl["name"])
     setup_ms = w.setup_ms
+    if hasattr(w.model, "close"):
+        w.model.close()  # peer-mapped exchange buffers
     fallbacks = dense.fallback_calls()
 
     single = rank == 0 and world == 1

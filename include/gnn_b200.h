@@ -322,6 +322,17 @@ int gnn_edge_softmax_fwd(const int* row_ptr, int64_t n_rows, int64_t nnz, const 
 int gnn_edge_softmax_bwd(const int* row_ptr, int64_t n_rows, int64_t nnz, const float* y,
                          const float* grad_y, int H, float* grad_x, cudaStream_t stream);
 
+/* gnn_gat_fwd with the model's activation on the layer output folded in: act_out = ELU(out)
+ * (alpha as in torch.nn.functional.elu) is stored next to out by the warp that normalises the
+ * row.  The reference's models apply the activation as a separate framework op after the layer
+ * (script/train/train_gatconv_our.py:50-52).  Same arguments and workspace as gnn_gat_fwd;
+ * H <= 8 and H*F within one tile (512 floats, 256 if rows are not 16-byte aligned). */
+int gnn_gat_fwd_act(const int* row_ptr, const int* col_ind, int64_t n_rows, int64_t nnz,
+                    const float* attn_row, const float* attn_col, const float* in_feat, int H, int F,
+                    float negative_slope, float alpha, float* out /*[n_rows,H,F]*/,
+                    float* act_out /*[n_rows,H,F]*/, float* edge_max, float* edge_sum, void* workspace,
+                    size_t workspace_bytes, cudaStream_t stream);
+
 /* ---- k-nearest-neighbour graph of point clouds ----------------------------------------
  * The graph EdgeConv runs on: the reference builds it with DGL's KNNGraph(k) in front of
  * every layer (script/train/train_edgeconv_our.py:20,52).  points [n_clouds, n_points,

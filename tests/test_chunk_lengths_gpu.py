@@ -113,6 +113,13 @@ def test_gat_forward_and_backward(cuda, chunk, H, F):
     # same launch twice: bit-identical (no atomics, merge in chunk order)
     out2, m2, s2 = G.gat_forward(dar, dac, rp, ci, 0.2, dx)
     assert torch.equal(out, out2) and torch.equal(m, m2) and torch.equal(s, s2)
+    # the variant that also stores ELU(out): same values, activation of split rows applied after the merge
+    out3, act, m3, s3 = G.gat_forward_act(dar, dac, rp, ci, 0.2, dx)
+    if H == 1 and F % 4:  # one narrow head: gnn_gat_fwd runs the sub-warp kernel, another summation order
+        assert_close(out3, out, "out of the ELU variant")
+    else:
+        assert torch.equal(out, out3) and torch.equal(m, m3) and torch.equal(s, s3)
+    assert_close(act, torch.nn.functional.elu(eo), "elu(out)")
 
 
 @pytest.mark.parametrize("chunk", CHUNKS, indirect=True)

@@ -439,3 +439,26 @@ def test_gat_forward_blocks_refuse_heads_wider_than_a_tile(cuda):
     assert_close(out, eo, "out 1x640")
     with pytest.raises(_capi.GnnError, match="column blocks"):
         G.gat_forward_part(d[0], d[1], rp, ci, 0.2, d[2], out, m, s, True, True)
+
+
+@pytest.mark.parametrize("name", ["empty_rows", "hub", "long_rows", "random_200", "no_edges"])
+@pytest.mark.parametrize("H,F", [(4, 128), (4, 64), (8, 8), (1, 47), (3, 12), (2, 100)])
+def test_gat_forward_with_fused_elu(cuda, name, H, F):
+    """gnn_gat_fwd_act: same out / edge_max / edge_sum as gnn_gat_fwd (bit for bit), and ELU(out)
+    next to it; rows without edges give 0 in both."""
+    from ae_mlsys_gnn_b200.operators import fused_gat as G
+
+    g = crafted_graphs()[name]
+    nc = _n_cols(g)
+    attn_row, attn_col, feat, _ = _inputs(g, H, F, 21, nc)
+    d = [t.to(cuda) for t in (attn_row, attn_col, feat)]
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    out, m, s = G.gat_forward(d[0], d[1], rp, ci, 0.2, d[2])
+    out2, act, m2, s2 = G.gat_forward_act(d[0], d[1], rp, ci, 0.2, d[2])
+    if H == 1 and F % 4:  # one narrow head: gnn_gat_fwd runs the sub-warp kernel, another summation order
+        assert_close(out2, out, "out of the ELU variant")
+    else:
+        assert torch.equal(out, out2) and torch.equal(m, m2) and torch.equal(s, s2)
+    assert_close(act, torch.nn.functional.elu(out2.double()), "elu(out)", rtol=1e-6, atol=2e-6)
+    eo, _, _ = ref.gat_forward(attn_row, attn_col, g.row_ptr, g.col_ind, 0.2, feat)
+    assert_close(act, torch.nn.functional.elu(eo), "elu(out) vs oracle")

@@ -1,6 +1,7 @@
 """Partitioned GAT on real GPUs (skipped with fewer than two): NCCL ranks running the
 CUDA kernels must reproduce the single-GPU model's logits, loss and gradients, with both
-exchange schemes (all-gather of every rank's rows; halo: only the rows a block references)."""
+exchange schemes (all-gather of every rank's rows; halo: only the rows a block references, moved by
+an all-to-all; peer: the same rows stored straight into the receivers' buffers over NVLink)."""
 import os
 import socket
 
@@ -36,19 +37,21 @@ def _worker(rank, world, port, results, exchange="gather"):
         g, x, y = _inputs()
         g = g.to(dev)
         cp, ri, _ = csr2csc(g.row_ptr, g.col_ind)
-        if exchange == "halo":
+        if exchange in ("halo", "peer"):
             from ae_mlsys_gnn_b200.halo import HaloGAT, build_halo_partition
 
             part = build_halo_partition(g.row_ptr, g.col_ind, cp, ri, rank, world)
-            model = HaloGAT(20, [16, 16], [4, 4], 6, 1).to(dev)
+            model = HaloGAT(20, [16, 16], [4, 4], 6, 1, exchange="peer" if exchange == "peer" else "nccl").to(dev)
             max_n = max(part.bounds[r + 1] - part.bounds[r] for r in range(world))
         else:
             part = build_partition(g.row_ptr, g.col_ind, cp, ri, rank, world, pieces=1 if world == 2 else 3)
             model = PartitionedGAT(20, [16, 16], [4, 4], 6, 1).to(dev)
             max_n = part.max_n
-        out = model(part, part.pad_rows(part.local_slice(x.to(dev))))
-        loss = model.loss(part, out, part.local_slice(y.to(dev)))
-        loss.backward()
+        for _ in range(3 if exchange == "peer" else 1):  # both buffers of every exchange point get used
+            model.zero_grad()
+            out = model(part, part.pad_rows(part.local_slice(x.to(dev))))
+            loss = model.loss(part, out, part.local_slice(y.to(dev)))
+            loss.backward()
         model.all_reduce_grads(world)
         total = loss.detach().clone()
         dist.all_reduce(total)
@@ -64,12 +67,14 @@ def _worker(rank, world, port, results, exchange="gather"):
             results["loss"] = total.cpu()
             results["grads"] = {k: p.grad.cpu() for k, p in model.named_parameters()}
             results["state"] = {k: v.cpu() for k, v in model.state_dict().items()}
+        if hasattr(model, "close"):
+            model.close()
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("exchange", ["gather", "halo"])
+@pytest.mark.parametrize("exchange", ["gather", "halo", "peer"])
 @pytest.mark.parametrize("world", [2, 4])
 def test_partitioned_gat_matches_single_gpu(cuda, world, exchange):
     if torch.cuda.device_count() < world:
