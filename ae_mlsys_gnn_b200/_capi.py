@@ -84,6 +84,13 @@ PROTOTYPES = {
     "gnn_u_add_v_bwd": [_PTR, _PTR, _I64, _I64, _I64, _PTR, _INT, _PTR, _PTR, _PTR],
     "gnn_edge_softmax_fwd": [_PTR, _I64, _I64, _PTR, _INT, _PTR, _PTR],
     "gnn_edge_softmax_bwd": [_PTR, _I64, _I64, _PTR, _PTR, _INT, _PTR, _PTR],
+    "gnn_coo_to_csr_workspace_bytes": [_I64, _I64, _SZP],
+    "gnn_coo_to_csr": [_PTR, _PTR, _I64, _I64, _INT, _PTR, _PTR, _PTR, _PTR, _SZ, _PTR],
+    "gnn_edge_balanced_bounds": [_PTR, _I64, _INT, _PTR, _PTR],
+    "gnn_halo_needs_workspace_bytes": [_I64, _INT, _SZP],
+    "gnn_halo_needs": [_PTR, _PTR, _I64, _I64, _PTR, _INT, _PTR, _PTR, _SZ, _PTR],
+    "gnn_compact_flagged": [_PTR, _I64, _I64, _PTR, _PTR],
+    "gnn_halo_remap": [_PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR],
     "gnn_knn_graph": [_PTR, _I64, _I64, _INT, _INT, _PTR, _PTR],
     "gnn_peer_alloc": [_SZ, C.POINTER(C.c_void_p), _PTR],
     "gnn_peer_free": [_PTR],

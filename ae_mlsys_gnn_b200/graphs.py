@@ -40,8 +40,15 @@ def _gen(seed: int, device) -> torch.Generator:
 
 def csr_from_edges(n: int, dst: torch.Tensor, src: torch.Tensor, self_loops: bool = True) -> Graph:
     """Deduplicates (dst, src) pairs, optionally forces one self-loop per node, and
-    builds the CSR sorted by (dst, src)."""
+    builds the CSR sorted by (dst, src).  On a GPU this is the library's own construction
+    (operators.graph_build.coo_to_csr: radix sorts, flags, scan, compaction); on the host the
+    same result with framework ops."""
     dev = dst.device
+    if dst.is_cuda and n < 2**31 - 2 and dst.numel() + n < 2**31 - 4096:
+        from .operators.graph_build import coo_to_csr
+
+        rp, ci = coo_to_csr(dst.to(torch.int32).contiguous(), src.to(torch.int32).contiguous(), n, self_loops)
+        return Graph(n, rp, ci)
     dst = dst.long()
     src = src.long()
     if self_loops:

@@ -115,9 +115,41 @@ def _outside(ids: torch.Tensor, lo: int, hi: int) -> torch.Tensor:
     return u[(u < lo) | (u >= hi)]
 
 
+def _plan_device(ptr: torch.Tensor, idx: torch.Tensor, bounds: list, rank: int, world: int):
+    """``_plan`` for a graph on a GPU, with the library's own kernels: one pass over the edges marks
+    what every block references outside itself, a scan turns the marks into positions (which give
+    every count and offset of the plans), a compaction lists the ids, a last kernel remaps this
+    block's ids.  One small device-to-host copy."""
+    from .operators import graph_build as gb
+
+    dev = idx.device
+    n = ptr.numel() - 1
+    lo, hi = bounds[rank], bounds[rank + 1]
+    positions, needs = gb.halo_needs(ptr, idx, bounds)
+    bd = torch.tensor(bounds, dtype=torch.long, device=dev)
+    at = (torch.arange(world, device=dev)[:, None] * n + bd[None, :]).reshape(-1)
+    fetch = torch.cat([positions[at].long(), ptr[bd[[rank, rank + 1]]].long()]).tolist()
+    table = [fetch[q * (world + 1): (q + 1) * (world + 1)] for q in range(world)]  # table[q][r]: needs of q below bounds[r]
+    e0, e1 = fetch[-2], fetch[-1]
+    halo_sizes = [table[q][world] - table[q][0] for q in range(world)]
+    recv_splits = [table[rank][r + 1] - table[rank][r] for r in range(world)]
+    send_splits = [0 if q == rank else table[q][rank + 1] - table[q][rank] for q in range(world)]
+    dst_off = [0 if q == rank else table[q][rank] - table[q][0] for q in range(world)]
+    parts = [needs[table[q][rank]: table[q][rank + 1]] for q in range(world) if q != rank]
+    send32 = (torch.cat(parts) - lo).to(torch.int32).contiguous() if parts else \
+        torch.zeros(0, dtype=torch.int32, device=dev)
+    local_ptr = (ptr[lo: hi + 1] - e0).to(torch.int32).contiguous()
+    ext = gb.halo_remap(idx[e0:e1].contiguous(), lo, hi, positions, rank, n)
+    plan = ExchangePlan(send32.long(), send_splits, recv_splits, active=any(h > 0 for h in halo_sizes),
+                        halo_sizes=halo_sizes, dst_off=dst_off, send_idx32=send32)
+    return plan, local_ptr, ext
+
+
 def _plan(ptr: torch.Tensor, idx: torch.Tensor, bounds: list, rank: int, world: int):
     """Exchange plan and remapped ids for the segment array (ptr, idx) of a square graph whose
     segments AND ids are global node ids: rank r works on segments [bounds[r], bounds[r+1])."""
+    if idx.is_cuda and ptr.dtype == torch.int32 and idx.dtype == torch.int32:
+        return _plan_device(ptr.contiguous(), idx.contiguous(), bounds, rank, world)
     dev = idx.device
     p = ptr.long()
     b = torch.tensor(bounds, dtype=torch.long, device=dev)
@@ -163,7 +195,13 @@ def build_halo_partition(row_ptr, col_ind, col_ptr, row_ind, rank: int, world: i
     """Cuts the global CSR (row_ptr, col_ind) and CSC (col_ptr, row_ind) of a square graph into
     rank ``rank``'s block and builds both exchange plans.  Every rank calls it with the same
     global graph (the plans of the peers are derived from it, no communication)."""
-    bounds = edge_balanced_bounds(row_ptr, world) if bounds is None else bounds
+    if bounds is None:
+        if row_ptr.is_cuda and row_ptr.dtype == torch.int32:
+            from .operators.graph_build import edge_balanced_bounds as device_bounds
+
+            bounds = device_bounds(row_ptr.contiguous(), world)
+        else:
+            bounds = edge_balanced_bounds(row_ptr, world)
     fwd, rp, ci = _plan(row_ptr, col_ind, bounds, rank, world)
     bwd, cp, ri = _plan(col_ptr, row_ind, bounds, rank, world)
     n_local = bounds[rank + 1] - bounds[rank]

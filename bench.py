@@ -548,12 +548,37 @@ class Workload:
             b.record()
             torch.cuda.synchronize()
             self.setup_ms["csr2csc"] = a.elapsed_time(b)
+            if rank == 0:
+                self.setup_ms["coo_to_csr"] = self._time_graph_build(g, seed)
         if kind == "gat" and world > 1:
             self._partition()
         else:
             self.model = make_model(wl).to(dev)
         self.opt = torch.optim.Adam(self.model.parameters(), lr=1e-3, capturable=capturable)
         torch.cuda.empty_cache()
+
+    @staticmethod
+    def _time_graph_build(g, seed):
+        """Device time of building this CSR from its shuffled edge list (sort by (dst, src), dedup,
+        self-loops): the step the reference's scripts do on the host.  The result is compared
+        with the graph in use, bit for bit."""
+        from ae_mlsys_gnn_b200.operators.graph_build import coo_to_csr
+
+        dev = g.row_ptr.device
+        rp = g.row_ptr.long()
+        dst = torch.repeat_interleave(torch.arange(g.n, device=dev, dtype=torch.int32), rp[1:] - rp[:-1])
+        perm = torch.randperm(g.nnz, device=dev, generator=torch.Generator(device=dev).manual_seed(seed))
+        dst, src = dst[perm].contiguous(), g.col_ind[perm].contiguous()
+        del perm, rp
+        coo_to_csr(dst[:1024], src[:1024], g.n, True)  # loads the kernels
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        rp2, ci2 = coo_to_csr(dst, src, g.n, True)
+        b.record()
+        torch.cuda.synchronize()
+        if not (torch.equal(rp2, g.row_ptr) and torch.equal(ci2, g.col_ind)):
+            raise SystemExit("graph construction on the device does not reproduce the workload's CSR")
+        return a.elapsed_time(b)
 
     def _partition(self):
         wl, d, dev = self.wl, self.d, self.dev
@@ -567,8 +592,12 @@ class Workload:
         else:
             from ae_mlsys_gnn_b200.halo import HaloGAT, build_halo_partition
 
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
             self.part = build_halo_partition(g.row_ptr, g.col_ind, self.col_ptr, self.row_ind, self.rank,
                                              self.world)
+            torch.cuda.synchronize()
+            self.setup_ms["halo_partition"] = (time.perf_counter() - t0) * 1e3
             self.model = HaloGAT(wl["in_dim"], wl["hidden"], wl["heads"], wl["classes"], 1,
                                  exchange=scheme).to(dev)
         d["x_l"] = self.part.pad_rows(self.part.local_slice(d["x"]))

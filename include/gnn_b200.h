@@ -333,6 +333,38 @@ int gnn_gat_fwd_act(const int* row_ptr, const int* col_ind, int64_t n_rows, int6
                     float* act_out /*[n_rows,H,F]*/, float* edge_max, float* edge_sum, void* workspace,
                     size_t workspace_bytes, cudaStream_t stream);
 
+/* ---- graph construction ------------------------------------------------------------------
+ * gnn_coo_to_csr replaces the host-side preprocessing of the reference's scripts
+ * (script/train/train_gatconv_our.py:82-95: dgl.remove_self_loop / add_self_loop, then
+ * scipy.sparse.csr_matrix((ones, (row, col))) -> indptr, indices; train_gmmconv_our.py:80-93).
+ * dst/src [n_pairs] are the endpoints of directed edges src -> dst.  Output: the in-edge CSR
+ * sorted by (dst, src) with duplicate pairs removed; with self_loops != 0 pairs with
+ * dst == src are dropped and one (i, i) per node is added.  Pairs with an endpoint outside
+ * [0, n_nodes) are dropped.  col_ind must hold n_pairs + (self_loops ? n_nodes : 0) entries;
+ * the number actually written goes to *nnz_out (device memory, int64).  Integer work: the
+ * result equals SciPy's bit for bit. */
+int gnn_coo_to_csr_workspace_bytes(int64_t n_pairs, int64_t n_nodes, size_t* bytes);
+int gnn_coo_to_csr(const int* dst, const int* src, int64_t n_pairs, int64_t n_nodes, int self_loops,
+                   int* row_ptr /*[n_nodes+1]*/, int* col_ind, long long* nnz_out, void* workspace,
+                   size_t workspace_bytes, cudaStream_t stream);
+
+/* Row-block partition bookkeeping (no counterpart in the reference: single GPU).
+ * gnn_edge_balanced_bounds: bounds[g] (device, parts+1 entries) = first row whose first edge is
+ * at or after g * nnz / parts.
+ * gnn_halo_needs: positions [world*n_nodes + 1] = exclusive scan of the flags "an edge of a row of
+ * block q has id v outside block q", laid out [q][v] (bounds: device array of world+1 rows).
+ * gnn_compact_flagged: out[positions[i]] = i % period for every i in [0, n) whose flag is set,
+ * i.e. the sorted id lists of all blocks one after the other.
+ * gnn_halo_remap: ext[e] = idx[e] - lo for ids inside [lo, hi), else (hi - lo) + rank of the id
+ * among the flagged ids of this block (positions_of_rank = positions + rank * n_nodes). */
+int gnn_edge_balanced_bounds(const int* row_ptr, int64_t n_rows, int parts, int* bounds, cudaStream_t stream);
+int gnn_halo_needs_workspace_bytes(int64_t n_nodes, int world, size_t* bytes);
+int gnn_halo_needs(const int* ptr, const int* idx, int64_t n_nodes, int64_t nnz, const int* bounds, int world,
+                   unsigned* positions, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+int gnn_compact_flagged(const unsigned* positions, int64_t n, int64_t period, int* out, cudaStream_t stream);
+int gnn_halo_remap(const int* idx, int64_t nnz, int lo, int hi, const unsigned* positions_of_rank, int* ext,
+                   cudaStream_t stream);
+
 /* ---- k-nearest-neighbour graph of point clouds ----------------------------------------
  * The graph EdgeConv runs on: the reference builds it with DGL's KNNGraph(k) in front of
  * every layer (script/train/train_edgeconv_our.py:20,52).  points [n_clouds, n_points,
