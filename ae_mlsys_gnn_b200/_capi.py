@@ -33,6 +33,9 @@ PROTOTYPES = {
                     _PTR, _PTR, _PTR, _PTR, _SZ, _PTR],
     "gnn_gat_fwd_act": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _INT, _INT, _F32, _F32,
                         _PTR, _PTR, _PTR, _PTR, _PTR, _SZ, _PTR],
+    "gnn_to_bf16": [_PTR, _I64, _PTR, _PTR],
+    "gnn_gat_fwd_bf16": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _INT, _INT, _F32,
+                         _PTR, _PTR, _PTR, _PTR, _SZ, _PTR],
     "gnn_gat_fwd_part": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _INT, _INT, _F32,
                          _PTR, _PTR, _PTR, _INT, _INT, _PTR, _SZ, _PTR],
     "gnn_gat_bwd_col_part": [_PTR, _PTR, _I64, _I64, _PTR, _PTR, _PTR, _PTR, _INT, _INT, _F32,
@@ -73,6 +76,9 @@ PROTOTYPES = {
     "gnn_gemm_tf32x3_supported": [_I64, _I64, _I64],
     "gnn_gemm_tf32x3_workspace_bytes": [_I64, _I64, _I64, _SZP],
     "gnn_gemm_tf32x3": [_PTR, _PTR, _INT, _PTR, _I64, _I64, _I64, _PTR, _SZ, _PTR, _PTR],
+    "gnn_gemm_tf32x3_scores_supported": [_INT, _INT],
+    "gnn_gemm_tf32x3_scores": [_PTR, _PTR, _INT, _PTR, _I64, _I64, _I64, _PTR, _PTR, _INT, _INT, _PTR, _PTR,
+                               _PTR, _SZ, _PTR, _PTR],
     "gnn_gemm_tf32x3_tn_workspace_bytes": [_I64, _I64, _I64, _SZP],
     "gnn_gemm_tf32x3_tn": [_PTR, _PTR, _PTR, _I64, _I64, _I64, _PTR, _SZ, _PTR, _PTR],
     "gnn_mhspmm_workspace_bytes": [_I64, _INT, _INT, _SZP],
@@ -148,12 +154,12 @@ def check(rc: int, what: str) -> None:
 # memsets excluded); bench.py uses it to count its own launches.
 KERNELS_PER_CALL = {
     "gnn_csr2csc": None,  # depends on the number of radix passes, see launches_csr2csc
-    "gnn_gat_fwd": 2, "gnn_gat_fwd_act": 2, "gnn_gat_fwd_part": 2, "gnn_gat_bwd_col_part": 2,
+    "gnn_gat_fwd": 2, "gnn_gat_fwd_bf16": 2, "gnn_to_bf16": 1, "gnn_gat_fwd_act": 2, "gnn_gat_fwd_part": 2, "gnn_gat_bwd_col_part": 2,
     "gnn_gat_fwd_static_scratch": 2, "gnn_gat_bwd": 4, "gnn_gat_bwd_row": 2, "gnn_gat_bwd_col": 2,
     "gnn_gat_scores_fwd": 1, "gnn_gat_scores_bwd": 2,
     # weight split + GEMM; GEMM + split reduction (plus one transposing pre-pass per operand
     # whose row length is not a multiple of 4 floats, not counted here)
-    "gnn_gemm_tf32x3": 2, "gnn_gemm_tf32x3_tn": 2,
+    "gnn_gemm_tf32x3": 2, "gnn_gemm_tf32x3_scores": 2, "gnn_gemm_tf32x3_tn": 2,
     "gnn_gat_bwd_col_edges": 2, "gnn_gat_bwd_pack": 1, "gnn_gat_bwd_pack_elu": 1, "gnn_gat_bwd_row_sum": 2, "gnn_invert_permutation": 1,
     "gnn_gat_edge_alpha": 1, "gnn_edgeconv_fwd": 1, "gnn_edgeconv_bwd": 1, "gnn_gmm_fwd": 2,
     "gnn_gaussian_fwd": 1, "gnn_gaussian_bwd": 2, "gnn_mhspmm": 2, "gnn_mhsddmm": 1,

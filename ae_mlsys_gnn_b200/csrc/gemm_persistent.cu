@@ -67,6 +67,16 @@ struct Params {
   int* status;
   int a_mode, b_mode;       // OperandMode
   int chain_kb;             // K blocks accumulated in tensor memory before the sum moves to registers
+  // Optional epilogue of the GAT projection: the output row is H heads of head_w floats, and
+  //   score_l[row, h] = <C[row, h, :], attn_l[h, :]>,  score_r[row, h] = <C[row, h, :], attn_r[h, :]>
+  // (layers/gatconv_layer.py:52-53) are formed by the thread that holds the row, while it stores it.
+  // Requires every head to lie inside one column tile and to start on a 32-column chunk:
+  // head_w in {32, 64, 128}, or one head with N <= 128.  nullptr: off.
+  const float* attn_l;
+  const float* attn_r;
+  float* score_l;
+  float* score_r;
+  int heads, head_w;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -342,6 +352,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
       const int row = t.m0 + lg * 32 + lane;
       float* const Cout = p.C + (size_t)t.z * p.split_stride;
       float sum[BN];  // running fp32 sum of this thread's output row when the tile has several chains
+      float dl = 0.f, dr = 0.f;  // running dot products of the current head with attn_l / attn_r
       for (int ch = 0; ch < t.chains; ++ch, ++tcount) {
         const int buf = tcount & 1;
         if (!mbar_wait(acc_full_bar(buf), (tcount >> 1) & 1, &s_failed)) { s_failed = 1; ok = false; break; }
@@ -373,6 +384,36 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
               const float v = __uint_as_float(r[j]);
               sum[c * 32 + j] = ch == 0 ? v : sum[c * 32 + j] + v;
               r[j] = __float_as_uint(sum[c * 32 + j]);
+            }
+          }
+          if (last && p.score_l != nullptr) {
+            const int ncols = min(32, p.N - col0);
+            if (ncols == 32) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                const float4 al = __ldg(reinterpret_cast<const float4*>(p.attn_l + col0 + j));
+                const float4 ar = __ldg(reinterpret_cast<const float4*>(p.attn_r + col0 + j));
+                dl = fmaf(__uint_as_float(r[j]), al.x, dl); dr = fmaf(__uint_as_float(r[j]), ar.x, dr);
+                dl = fmaf(__uint_as_float(r[j + 1]), al.y, dl); dr = fmaf(__uint_as_float(r[j + 1]), ar.y, dr);
+                dl = fmaf(__uint_as_float(r[j + 2]), al.z, dl); dr = fmaf(__uint_as_float(r[j + 2]), ar.z, dr);
+                dl = fmaf(__uint_as_float(r[j + 3]), al.w, dl); dr = fmaf(__uint_as_float(r[j + 3]), ar.w, dr);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < ncols) {
+                  dl = fmaf(__uint_as_float(r[j]), __ldg(p.attn_l + col0 + j), dl);
+                  dr = fmaf(__uint_as_float(r[j]), __ldg(p.attn_r + col0 + j), dr);
+                }
+            }
+            const int end = col0 + ncols;  // a head ends with this chunk?
+            if (end % p.head_w == 0 || end == p.N) {
+              if (row < p.M) {
+                const int head = (end - 1) / p.head_w;
+                p.score_l[(size_t)row * p.heads + head] = dl;
+                p.score_r[(size_t)row * p.heads + head] = dr;
+              }
+              dl = dr = 0.f;
             }
           }
           if (last && row < p.M) {
@@ -492,7 +533,8 @@ bool encode_operand(const GemmOperand& o, int64_t K, CUtensorMap* m0, CUtensorMa
 }  // namespace
 
 int launch_gemm_persistent(const GemmOperand& a, const GemmOperand& b, int64_t K, float* C, int64_t ldc,
-                           int splits, int64_t split_stride, int* status, cudaStream_t stream) {
+                           int splits, int64_t split_stride, int* status, cudaStream_t stream,
+                           const GemmScores* scores) {
   CUtensorMap ma0, ma1, mb0, mb1;
   if (!encode_operand(a, K, &ma0, &ma1) || !encode_operand(b, K, &mb0, &mb1)) {
     set_last_error("gnn_gemm_tf32x3: cuTensorMapEncodeTiled failed");
@@ -535,6 +577,15 @@ int launch_gemm_persistent(const GemmOperand& a, const GemmOperand& b, int64_t K
   p.a_mode = a.mode;
   p.b_mode = b.mode;
   p.chain_kb = kChainKb;
+  p.attn_l = p.attn_r = nullptr;
+  p.score_l = p.score_r = nullptr;
+  p.heads = 1;
+  p.head_w = (int)b.rows;
+  if (scores) {
+    p.attn_l = scores->attn_l; p.attn_r = scores->attn_r;
+    p.score_l = scores->score_l; p.score_r = scores->score_r;
+    p.heads = scores->heads; p.head_w = scores->head_w;
+  }
   const int grid = (int)(tiles < sms ? tiles : sms);
   gemm_persistent_kernel<<<grid, kThreads, kSmemBytes, stream>>>(ma0, ma1, mb0, mb1, p);
   return GNN_OK;

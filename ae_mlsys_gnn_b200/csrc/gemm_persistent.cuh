@@ -26,10 +26,26 @@ struct GemmOperand {
   int64_t rows;     // extent along the output dimension (M for A, N for B)
 };
 
+// Attention scores formed in the epilogue (splits == 1): C rows are `heads` heads of `head_w` floats.
+struct GemmScores {
+  const float* attn_l;  // [heads][head_w]
+  const float* attn_r;
+  float* score_l;       // [M][heads]
+  float* score_r;
+  int heads, head_w;
+};
+
+// Shapes for which the epilogue can form the scores: every head inside one 128-column tile and
+// starting on a 32-column chunk.
+inline bool gemm_scores_ok(int heads, int head_w) {
+  return (heads == 1 && head_w <= 128) || head_w == 32 || head_w == 64 || head_w == 128;
+}
+
 // C[z][M][N] (z < splits) = sum over the z-th range of K blocks of A * B^T.
 // Returns 0, or a negative GNN_ERR_* after set_last_error.
 int launch_gemm_persistent(const GemmOperand& a, const GemmOperand& b, int64_t K, float* C, int64_t ldc,
-                           int splits, int64_t split_stride, int* status, cudaStream_t stream);
+                           int splits, int64_t split_stride, int* status, cudaStream_t stream,
+                           const GemmScores* scores = nullptr);
 
 // Whether an operand with `cols` contiguous floats per row and base pointer p can be read by TMA.
 inline bool tma_rows_ok(const void* p, int64_t cols) {

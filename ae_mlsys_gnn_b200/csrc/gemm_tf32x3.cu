@@ -144,6 +144,28 @@ extern "C" int gnn_gemm_tf32x3_workspace_bytes(int64_t M, int64_t N, int64_t K, 
 extern "C" int gnn_gemm_tf32x3(const float* A, const float* B, int b_is_n_by_k, float* C, int64_t M,
                                int64_t N, int64_t K, void* workspace, size_t workspace_bytes,
                                int* status, cudaStream_t stream) {
+  return gnn_gemm_tf32x3_scores(A, B, b_is_n_by_k, C, M, N, K, nullptr, nullptr, 0, 0, nullptr, nullptr,
+                                workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int gnn_gemm_tf32x3_scores_supported(int heads, int head_w) {
+  return heads >= 1 && head_w >= 1 && gemm_scores_ok(heads, head_w);
+}
+
+extern "C" int gnn_gemm_tf32x3_scores(const float* A, const float* B, int b_is_n_by_k, float* C, int64_t M,
+                                      int64_t N, int64_t K, const float* attn_l, const float* attn_r, int heads,
+                                      int head_w, float* score_l, float* score_r, void* workspace,
+                                      size_t workspace_bytes, int* status, cudaStream_t stream) {
+  const bool with_scores = attn_l || attn_r || score_l || score_r;
+  if (with_scores) {
+    if (!attn_l || !attn_r || !score_l || !score_r) return bad("gnn_gemm_tf32x3_scores: null pointer");
+    if (heads < 1 || head_w < 1 || (int64_t)heads * head_w != N) return bad("gnn_gemm_tf32x3_scores: heads * head_w must equal N");
+    if (!gemm_scores_ok(heads, head_w) || !aligned16(attn_l) || !aligned16(attn_r)) {
+      set_last_error("gnn_gemm_tf32x3_scores: head width must be 32, 64 or 128 (or one head of at most 128) "
+                     "and the attention vectors 16-byte aligned");
+      return GNN_ERR_UNSUPPORTED;
+    }
+  }
   if (M < 0 || N < 0 || K < 0) return bad("gnn_gemm_tf32x3: negative size");
   if (M == 0 || N == 0) return GNN_OK;
   if (!A || !B || !C || !status) return bad("gnn_gemm_tf32x3: null pointer");
@@ -170,7 +192,8 @@ extern "C" int gnn_gemm_tf32x3(const float* A, const float* B, int b_is_n_by_k, 
   }
   const GemmOperand oa{kKMajorRaw, A, nullptr, M};
   const GemmOperand ob{kKMajorSplit, b_hi, b_lo, N};
-  const int rc = launch_gemm_persistent(oa, ob, K, C, N, 1, 0, status, stream);
+  const GemmScores sc{attn_l, attn_r, score_l, score_r, heads, head_w};
+  const int rc = launch_gemm_persistent(oa, ob, K, C, N, 1, 0, status, stream, with_scores ? &sc : nullptr);
   if (rc != GNN_OK) return rc;
   return check_launch("gnn_gemm_tf32x3");
 }

@@ -27,6 +27,74 @@ struct Unroll {
   static constexpr int U = R >= 16 ? 2 : (R >= 8 ? 4 : 8);
 };
 
+// Tile whose gathered rows are bfloat16 (an opt-in storage format of the gathered operand: half
+// the bytes per edge, fp32 arithmetic): lane l owns elements (l + 32 q) * 8 + i, i < 8, read as
+// one 128-bit word of 8 bfloat16 and widened; rows this kernel writes (outputs, scratch slots)
+// stay fp32.  `row` pointers of gathered rows are typed float* but point at bfloat16 data: their
+// leading dimension is given in units of 4 bytes.
+template <int Q>
+struct RowTileBf16 {
+  static constexpr int VW = 8;
+  bool valid[Q];
+  int head[Q];
+  __device__ __forceinline__ void init(int lane, int width, int F, int H) {
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+      const int e0 = (lane + 32 * q) * VW;
+      valid[q] = e0 < width;
+      const int h = e0 / F;
+      head[q] = h < H ? h : H - 1;
+    }
+  }
+  __device__ __forceinline__ void zero(float (&v)[Q][VW]) const {
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+#pragma unroll
+      for (int i = 0; i < VW; ++i) v[q][i] = 0.f;
+  }
+  __device__ __forceinline__ void load(const float* __restrict__ row, int lane, float (&v)[Q][VW]) const {
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+      if (valid[q]) {
+        const uint4 t = __ldg(reinterpret_cast<const uint4*>(row) + lane + 32 * q);
+        const unsigned w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // a bfloat16 is the upper half of the fp32 with the same value
+          v[q][2 * i] = __uint_as_float(w[i] << 16);
+          v[q][2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < VW; ++i) v[q][i] = 0.f;
+      }
+    }
+  }
+  __device__ __forceinline__ void load_rw(const float* row, int lane, float (&v)[Q][VW]) const {
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+      if (valid[q]) {
+        const float4 a = *(reinterpret_cast<const float4*>(row) + (lane + 32 * q) * 2);
+        const float4 b = *(reinterpret_cast<const float4*>(row) + (lane + 32 * q) * 2 + 1);
+        v[q][0] = a.x; v[q][1] = a.y; v[q][2] = a.z; v[q][3] = a.w;
+        v[q][4] = b.x; v[q][5] = b.y; v[q][6] = b.z; v[q][7] = b.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < VW; ++i) v[q][i] = 0.f;
+      }
+    }
+  }
+  __device__ __forceinline__ void store(float* __restrict__ row, int lane, const float (&v)[Q][VW]) const {
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+      if (valid[q]) {
+        float4* d = reinterpret_cast<float4*>(row) + (lane + 32 * q) * 2;
+        d[0] = make_float4(v[q][0], v[q][1], v[q][2], v[q][3]);
+        d[1] = make_float4(v[q][4], v[q][5], v[q][6], v[q][7]);
+      }
+    }
+  }
+};
+
 struct WGatherParams {
   ChunkGeom g;
   const float* feat;   // gathered rows, indexed by idx[e]
@@ -140,12 +208,12 @@ __device__ __forceinline__ void edge_weights(const GaussPolicy<HP>& pol, int H,
 // Final step for one segment whose edges (of this launch) have all been reduced into
 // acc (softmax: un-normalised, relative to maximum m, with exp-sum ssum): merge with the
 // state left by earlier launches, normalise if asked to, store.
-template <template <int> class Policy, int HP, int Q, bool VEC>
+template <template <int> class Policy, int HP, int Q, class Tile>
 __device__ __forceinline__ void finish_segment(const WGatherParams& p, const Policy<HP>& pol,
-                                               const RowTile<Q, VEC>& t, int lane, int s,
-                                               float (&acc)[Q][VEC ? 4 : 1], float (&m)[HP],
+                                               const Tile& t, int lane, int s,
+                                               float (&acc)[Q][Tile::VW], float (&m)[HP],
                                                float (&ssum)[HP]) {
-  constexpr int VW = VEC ? 4 : 1;
+  constexpr int VW = Tile::VW;
   float* orow = p.out + (size_t)s * p.ld_out;
   if constexpr (Policy<HP>::kSoftmax) {
     if (p.accumulate) {
@@ -213,11 +281,11 @@ __device__ __forceinline__ void finish_segment(const WGatherParams& p, const Pol
 
 // ----- main kernel ----------------------------------------------------------
 
-template <template <int> class Policy, int HP, int Q, bool VEC>
+template <template <int> class Policy, int HP, int Q, bool VEC, class Tile = RowTile<Q, VEC>>
 __global__ void __launch_bounds__(kThreadsPerCta)
 wgather_kernel(WGatherParams p, Policy<HP> pol) {
-  constexpr int VW = VEC ? 4 : 1;
-  constexpr int U = Unroll<Q, VEC>::U;
+  constexpr int VW = Tile::VW;
+  constexpr int U = Q * VW >= 16 ? 2 : (Q * VW >= 8 ? 4 : 8);
   constexpr bool SOFTMAX = Policy<HP>::kSoftmax;
   __shared__ int cs_all[kWarpsPerCta][32];
   __shared__ float ws_all[kWarpsPerCta][32 * HP];
@@ -228,7 +296,7 @@ wgather_kernel(WGatherParams p, Policy<HP> pol) {
   if (chunk_id >= p.g.num_chunks) return;
   int* cs = cs_all[wib];
   float* ws = ws_all[wib];
-  RowTile<Q, VEC> t;
+  Tile t;
   t.init(lane, p.width, p.F, p.H);
 
   for_each_piece(p.g, chunk_id, [&](int s, int a, int b, bool first, bool last) {
@@ -332,7 +400,7 @@ wgather_kernel(WGatherParams p, Policy<HP> pol) {
     }
 
     if (first && last) {
-      finish_segment<Policy, HP, Q, VEC>(p, pol, t, lane, s, acc, segm, segs);
+      finish_segment<Policy, HP, Q, Tile>(p, pol, t, lane, s, acc, segm, segs);
     } else {
       float* slot = p.scratch + slot_index(chunk_id, first) * p.slot_stride;
       t.store(slot, lane, acc);
@@ -357,14 +425,14 @@ wgather_kernel(WGatherParams p, Policy<HP> pol) {
 // Blocks [boundary_blocks, ...) : one thread per segment, empty segments get
 //   zeros (and, for the softmax policy, max = -1e38 and sum = 0 like the
 //   reference's empty rows).
-template <template <int> class Policy, int HP, int Q, bool VEC>
+template <template <int> class Policy, int HP, int Q, bool VEC, class Tile = RowTile<Q, VEC>>
 __global__ void __launch_bounds__(kThreadsPerCta)
 wgather_fixup_kernel(WGatherParams p, Policy<HP> pol, int boundary_blocks) {
-  constexpr int VW = VEC ? 4 : 1;
+  constexpr int VW = Tile::VW;
   constexpr bool SOFTMAX = Policy<HP>::kSoftmax;
   const int lane = threadIdx.x & 31;
   const int wib = threadIdx.x >> 5;
-  RowTile<Q, VEC> t;
+  Tile t;
   t.init(lane, p.width, p.F, p.H);
 
   if ((int)blockIdx.x < boundary_blocks) {
@@ -392,7 +460,7 @@ wgather_fixup_kernel(WGatherParams p, Policy<HP> pol, int boundary_blocks) {
     for (int c = c0; c <= c1; ++c) {
       const float* slot = p.scratch + slot_index(c, c == c0) * p.slot_stride;
       float v[Q][VW];
-      t.load(slot, lane, v);
+      t.load_rw(slot, lane, v);  // slots hold fp32 whatever the gathered rows are
       if constexpr (SOFTMAX) {
         float sc[HP];
 #pragma unroll
@@ -413,7 +481,7 @@ wgather_fixup_kernel(WGatherParams p, Policy<HP> pol, int boundary_blocks) {
           for (int i = 0; i < VW; ++i) acc[q][i] += v[q][i];
       }
     }
-    finish_segment<Policy, HP, Q, VEC>(p, pol, t, lane, s, acc, m, ssum);
+    finish_segment<Policy, HP, Q, Tile>(p, pol, t, lane, s, acc, m, ssum);
   } else {
     const int s = ((int)blockIdx.x - boundary_blocks) * kThreadsPerCta + threadIdx.x;
     bool empty = false;
@@ -532,24 +600,24 @@ inline bool plan_heads(int H, int F, bool aligned, bool need_full_head, HeadPlan
 
 // The merge of split segments and the defaults of empty segments (second launch of every
 // weighted gather).
-template <template <int> class Policy, int HP, int Q, bool VEC>
+template <template <int> class Policy, int HP, int Q, bool VEC, class Tile = RowTile<Q, VEC>>
 inline void launch_wgather_fixup(const WGatherParams& p, const Policy<HP>& pol, cudaStream_t stream) {
   const int nbound = p.g.num_chunks > 1 ? p.g.num_chunks - 1 : 0;
   const int bblocks = (nbound + kWarpsPerCta - 1) / kWarpsPerCta;
   const int sblocks = (p.g.nseg + kThreadsPerCta - 1) / kThreadsPerCta;
   if (bblocks + sblocks > 0)
-    wgather_fixup_kernel<Policy, HP, Q, VEC>
+    wgather_fixup_kernel<Policy, HP, Q, VEC, Tile>
         <<<bblocks + sblocks, kThreadsPerCta, 0, stream>>>(p, pol, bblocks);
 }
 
-template <template <int> class Policy, int HP, int Q, bool VEC>
+template <template <int> class Policy, int HP, int Q, bool VEC, class Tile = RowTile<Q, VEC>>
 inline void launch_wgather(const WGatherParams& p, const Policy<HP>& pol,
                            cudaStream_t stream) {
   if (p.g.num_chunks > 0) {
     const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
-    wgather_kernel<Policy, HP, Q, VEC><<<blocks, kThreadsPerCta, 0, stream>>>(p, pol);
+    wgather_kernel<Policy, HP, Q, VEC, Tile><<<blocks, kThreadsPerCta, 0, stream>>>(p, pol);
   }
-  launch_wgather_fixup<Policy, HP, Q, VEC>(p, pol, stream);
+  launch_wgather_fixup<Policy, HP, Q, VEC, Tile>(p, pol, stream);
 }
 
 }  // namespace gnn

@@ -5,8 +5,9 @@ import torch
 from torch import nn
 
 from ..operators import dense
-from ..operators.fused_gat import (fused_gat_fusescatter, fused_gat_layer_op, fused_gat_op,
-                                   fused_gat_stash_op, fused_scores_supported)
+from ..operators.fused_gat import (FusedGATProjectedLayerFunction, fused_gat_fusescatter, fused_gat_layer_op,
+                                   fused_gat_op, fused_gat_stash_op, fused_scores_supported,
+                                   projected_layer_supported)
 
 
 class _GATBase(nn.Module):
@@ -57,6 +58,10 @@ class GATConv(_GATBase):
         self.activation = activation
 
     def forward(self, row_ptr, col_ind, col_ptr, row_ind, feat, save_memory=True):
+        if self.fuse_scores and projected_layer_supported(feat, self.W, self.num_heads, self.out_feats):
+            # projection, scores (in the GEMM's epilogue) and the fused op as one node
+            return FusedGATProjectedLayerFunction.apply(feat, self.W, self.attn_l, self.attn_r, row_ptr, col_ind,
+                                                        col_ptr, row_ind, self.negative_slope, self.activation)
         if self.fuse_scores and fused_scores_supported(self.num_heads, self.out_feats):
             h = dense.project(feat, self.W).view(-1, self.num_heads, self.out_feats)
             return fused_gat_layer_op(h, self.attn_l, self.attn_r, row_ptr, col_ind, col_ptr,

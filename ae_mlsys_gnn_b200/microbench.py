@@ -12,7 +12,7 @@ import json
 
 import torch
 
-OPS = ("gat_fwd", "gat_bwd_row", "gat_bwd_col", "gat_bwd_col_edges", "gat_bwd_row_sum", "gat_bwd_pack", "csr2csc", "edgeconv_fwd", "gmm_fwd", "mhspmm", "mhsddmm",
+OPS = ("gat_fwd", "gat_fwd_act", "gat_fwd_bf16", "gat_bwd_pack_elu", "gat_bwd_row", "gat_bwd_col", "gat_bwd_col_edges", "gat_bwd_row_sum", "gat_bwd_pack", "csr2csc", "edgeconv_fwd", "gmm_fwd", "mhspmm", "mhsddmm",
        "gemm", "gemm_tn")
 
 
@@ -101,6 +101,17 @@ def main():
     if a.op == "gat_fwd":
         fn = lambda: GAT.gat_forward(ar, ac, g.row_ptr, g.col_ind, 0.2, feat)
         nbytes = 4.0 * nnz * (1 + H + HF) + 4.0 * n * (1 + 3 * H + HF)
+    elif a.op == "gat_fwd_act":
+        fn = lambda: GAT.gat_forward_act(ar, ac, g.row_ptr, g.col_ind, 0.2, feat)
+        nbytes = 4.0 * nnz * (1 + H + HF) + 4.0 * n * (1 + 3 * H + 2 * HF)
+    elif a.op == "gat_fwd_bf16":
+        f16 = GAT.to_bf16(feat)
+        fn = lambda: GAT.gat_forward_bf16(ar, ac, g.row_ptr, g.col_ind, 0.2, f16)
+        nbytes = 4.0 * nnz * (1 + H) + 2.0 * nnz * HF + 4.0 * n * (1 + 3 * H + HF)
+    elif a.op == "gat_bwd_pack_elu":
+        out0 = GAT.gat_forward(ar, ac, g.row_ptr, g.col_ind, 0.2, feat)[0]
+        fn = lambda: GAT.gat_backward_pack_elu(out0, gout, ar, m, s)
+        nbytes = 4.0 * n * (3 * HF + 7 * H)
     elif a.op == "gat_bwd_row":
         fn = lambda: GAT.gat_backward_row(0.2, g.row_ptr, g.col_ind, m, s, feat, ar, ac, gout)
         nbytes = 4.0 * nnz * (1 + H + HF) + 4.0 * n * (1 + HF + 3 * H)

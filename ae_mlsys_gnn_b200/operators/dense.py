@@ -81,8 +81,15 @@ class OutRows:
         return flat[self.start: self.start + m]
 
 
-def gemm(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool, out: "OutRows | None" = None) -> torch.Tensor:
-    """a (M,K) times b, where b is (K,N) or, with ``b_is_n_by_k``, (N,K)."""
+def scores_supported(heads: int, head_w: int) -> bool:
+    """Whether the GEMM's epilogue can form the per-head attention scores for this output shape."""
+    return bool(capi.lib().gnn_gemm_tf32x3_scores_supported(int(heads), int(head_w)))
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool, out: "OutRows | None" = None, scores=None):
+    """a (M,K) times b, where b is (K,N) or, with ``b_is_n_by_k``, (N,K).
+    ``scores`` = (attn_l, attn_r) of shape (H, F) with H*F == N: also returns the (M, H) dot products
+    of every output row's heads with them, formed in the kernel's epilogue -> (out, score_l, score_r)."""
     dev = a.device
     capi.require(a, F32, "a", 2)
     capi.require(b, F32, "b", 2, dev)
@@ -93,13 +100,25 @@ def gemm(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool, out: "OutRows | No
     out = torch.empty((M, N), dtype=F32, device=dev) if out is None else out.rows(M, N)
     nbytes = capi.workspace_bytes("gnn_gemm_tf32x3_workspace_bytes", M, N, K)
     ws = capi.workspace(dev, nbytes)
+    if scores is None:
+        with torch.cuda.device(dev):
+            capi.call("gnn_gemm_tf32x3", capi.ptr(a), capi.ptr(b), int(b_is_n_by_k), capi.ptr(out), M, N, K,
+                      capi.ptr(ws), ws.numel(), capi.ptr(_status_word(dev)), capi.stream_ptr(dev))
+        return out
+    al, ar = (capi.require(t, F32, "attn", 2, dev) for t in scores)
+    H, Fw = al.shape
+    if H * Fw != N or ar.shape != al.shape:
+        raise ValueError("attention vectors must be (H, F) with H * F equal to the output width")
+    sl = torch.empty((M, H), dtype=F32, device=dev)
+    sr = torch.empty((M, H), dtype=F32, device=dev)
     with torch.cuda.device(dev):
-        capi.call("gnn_gemm_tf32x3", capi.ptr(a), capi.ptr(b), int(b_is_n_by_k), capi.ptr(out), M, N, K,
-                  capi.ptr(ws), ws.numel(), capi.ptr(_status_word(dev)), capi.stream_ptr(dev))
-    return out
+        capi.call("gnn_gemm_tf32x3_scores", capi.ptr(a), capi.ptr(b), int(b_is_n_by_k), capi.ptr(out), M, N, K,
+                  capi.ptr(al), capi.ptr(ar), H, Fw, capi.ptr(sl), capi.ptr(sr), capi.ptr(ws), ws.numel(),
+                  capi.ptr(_status_word(dev)), capi.stream_ptr(dev))
+    return out, sl, sr
 
 
-def gemm_any_k(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool, out: "OutRows | None" = None) -> torch.Tensor:
+def gemm_any_k(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool, out: "OutRows | None" = None, scores=None):
     """``gemm`` for any inner dimension: TMA reads rows whose length is a multiple of 4 floats,
     so other lengths (an input width of 602, a gradient with 47 columns) are padded with zero
     columns first -- one copy of ``a``, far cheaper than leaving the product to an fp32 SIMT GEMM."""
@@ -110,7 +129,7 @@ def gemm_any_k(a: torch.Tensor, b: torch.Tensor, b_is_n_by_k: bool, out: "OutRow
     a = a.contiguous()
     if a.data_ptr() % 16:  # a view that starts at an odd offset of its storage
         a = a.clone()
-    return gemm(a, b.contiguous(), b_is_n_by_k, out)
+    return gemm(a, b.contiguous(), b_is_n_by_k, out, scores)
 
 
 def gemm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:

@@ -130,6 +130,39 @@ def gat_forward_act(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_fea
     return out, act, edge_max, edge_sum
 
 
+def to_bf16(x: torch.Tensor) -> torch.Tensor:
+    """fp32 CUDA tensor -> bfloat16 copy (round to nearest even); the element count must be a multiple of 8."""
+    capi.require(x, F32, "x")
+    out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        capi.call("gnn_to_bf16", capi.ptr(x), x.numel(), capi.ptr(out), capi.stream_ptr(x.device))
+    return out
+
+
+def gat_forward_bf16(attn_row, attn_col, row_ptr, col_ind, negative_slope, in_feat_bf16):
+    """``gat_forward`` with the gathered rows stored as bfloat16 (opt-in: half the gather traffic,
+    fp32 arithmetic and outputs; equals ``gat_forward`` on the rounded features)."""
+    dev = in_feat_bf16.device
+    capi.require(in_feat_bf16, torch.bfloat16, "in_feat_bf16", 3)
+    n_rows = row_ptr.numel() - 1
+    H, F = in_feat_bf16.shape[1], in_feat_bf16.shape[2]
+    capi.require(attn_row, F32, "attn_row", 2, dev)
+    capi.require(attn_col, F32, "attn_col", 2, dev)
+    _check_graph(row_ptr, col_ind, dev)
+    nnz = col_ind.numel()
+    out = torch.empty((n_rows, H, F), dtype=F32, device=dev)
+    edge_max = torch.empty((n_rows, H), dtype=F32, device=dev)
+    edge_sum = torch.empty((n_rows, H), dtype=F32, device=dev)
+    nbytes = capi.workspace_bytes("gnn_gat_fwd_workspace_bytes", nnz, H, F)
+    ws = capi.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        capi.call("gnn_gat_fwd_bf16", capi.ptr(row_ptr), capi.ptr(col_ind), n_rows, nnz,
+                  capi.ptr(attn_row), capi.ptr(attn_col), capi.ptr(in_feat_bf16), H, F,
+                  float(negative_slope), capi.ptr(out), capi.ptr(edge_max), capi.ptr(edge_sum),
+                  capi.ptr(ws), ws.numel(), capi.stream_ptr(dev))
+    return out, edge_max, edge_sum
+
+
 def gat_backward(negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum,
                  in_feat, attn_row, attn_col, grad_out):
     """(grad_feat, grad_attn_row, grad_attn_col) — fused_gat_SM.gat_backward
@@ -145,11 +178,41 @@ def gat_backward(negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, e
         capi.require(t, F32, name, 2, dev)
     if row_ptr.numel() - 1 != n or col_ptr.numel() - 1 != n:
         raise ValueError("gat_backward expects a square graph with one row per in_feat row")
+    if not fused_backward_supported(H, F):
+        return _gat_backward_per_head(negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum,
+                                      in_feat, attn_row, attn_col, grad_out)
     # the two passes of gnn_gat_bwd, called one after the other so that each can be timed
     grad_attn_row, rowpack = gat_backward_row(negative_slope, row_ptr, col_ind, edge_max, edge_sum,
                                               in_feat, attn_row, attn_col, grad_out)
     grad_feat, grad_attn_col = gat_backward_col(negative_slope, col_ptr, row_ind, in_feat, attn_col,
                                                 rowpack, grad_out)
+    return grad_feat, grad_attn_row, grad_attn_col
+
+
+def fused_backward_supported(H, F):
+    """Shapes the backward kernels take in one launch: at most 8 heads whose rows fit one tile
+    (512 floats with 16-byte aligned rows, 256 otherwise)."""
+    return H <= 8 and H * F <= (512 if F % 4 == 0 else 256)
+
+
+def _gat_backward_per_head(negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, in_feat,
+                           attn_row, attn_col, grad_out):
+    """The backward for more than 8 heads or rows wider than a tile: the heads are independent, so
+    each is run as a one-head problem on contiguous copies (the forward does the same inside
+    gnn_gat_fwd with strided launches).  A single head wider than a tile is refused."""
+    n, H, F = in_feat.shape
+    if not fused_backward_supported(1, F):
+        raise ValueError(f"fused GAT backward: per-head width {F} exceeds the largest tile "
+                         "(512 floats, 256 when F is not a multiple of 4)")
+    grad_feat = torch.empty_like(in_feat)
+    grad_attn_row = torch.empty_like(attn_row)
+    grad_attn_col = torch.empty_like(attn_col)
+    for h in range(H):
+        one = [t[:, h:h + 1].contiguous() for t in (edge_max, edge_sum, in_feat, attn_row, attn_col, grad_out)]
+        gf, gar, gac = gat_backward(negative_slope, row_ptr, col_ind, col_ptr, row_ind, *one)
+        grad_feat[:, h:h + 1] = gf
+        grad_attn_row[:, h:h + 1] = gar
+        grad_attn_col[:, h:h + 1] = gac
     return grad_feat, grad_attn_row, grad_attn_col
 
 
@@ -393,7 +456,7 @@ def _backward(negative_slope, row_ptr, col_ind, col_ptr, row_ind, edge_max, edge
               attn_row, attn_col, out, grad_out, activation=None):
     """Backward of the autograd nodes: one gather pass when the graph allows, else two.
     ``activation`` = "elu": ``grad_out`` is the gradient with respect to elu(out)."""
-    if one_gather_backward and in_feat.shape[1] <= 8:
+    if one_gather_backward and fused_backward_supported(in_feat.shape[1], in_feat.shape[2]):
         pos = csr_positions(row_ptr, col_ind, col_ptr, row_ind)
         if pos is not None:
             if activation == "elu":  # the elu backward rides on the per-row pack
@@ -462,7 +525,7 @@ def gat_scores_backward(h, attn_l, attn_r, grad_attn_row, grad_attn_col, grad_fe
 
 def fused_scores_supported(H, F):
     """Shapes the one-pass score kernels cover (same limit as the fused backward)."""
-    return H <= 8 and H * F <= (512 if F % 4 == 0 else 256)
+    return fused_backward_supported(H, F)
 
 
 class FusedGATLayerFunction(torch.autograd.Function):
@@ -501,6 +564,68 @@ class FusedGATLayerFunction(torch.autograd.Function):
                                         grad_out.contiguous(), ctx.activation)
         gl, gr = gat_scores_backward(h, attn_l, attn_r, gar, gac, grad_feat)
         return grad_feat, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None, None
+
+
+class FusedGATProjectedLayerFunction(torch.autograd.Function):
+    """The whole GATConv layer as one autograd node: feat (N, in), W (in, H*F), attn_l / attn_r
+    (1, H, F) -> out (N, H, F).  The projection runs on the tensor-core GEMM whose epilogue also
+    forms attn_row / attn_col (no pass over h for the scores); the rest is FusedGATLayerFunction.
+    Backward: the fused GAT backward and the score gradients give grad_h; grad_feat = grad_h W^T and
+    grad_W = feat^T grad_h are the same GEMM kernel."""
+
+    @staticmethod
+    def forward(ctx, feat, W, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind, negative_slope,
+                activation=None):
+        from . import dense
+
+        if activation not in (None, "elu"):
+            raise ValueError("activation must be None or 'elu'")
+        H, F = attn_l.shape[1], attn_l.shape[2]
+        feat, W = feat.contiguous(), W.contiguous()
+        attn_l, attn_r = attn_l.contiguous(), attn_r.contiguous()
+        h2, attn_row, attn_col = dense.gemm_any_k(feat, W, False, scores=(attn_l.view(H, F), attn_r.view(H, F)))
+        h = h2.view(-1, H, F)
+        act = None
+        if activation == "elu":
+            out, act, edge_max, edge_sum = gat_forward_act(attn_row, attn_col, row_ptr, col_ind, negative_slope, h)
+        else:
+            out, edge_max, edge_sum = gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, h)
+        ctx.save_for_backward(row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, h, attn_row,
+                              attn_col, attn_l, attn_r, out, feat, W)
+        ctx.negative_slope = negative_slope
+        ctx.activation = activation
+        return out if act is None else act
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from . import dense
+
+        (row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, h, attn_row, attn_col, attn_l,
+         attn_r, out, feat, W) = ctx.saved_tensors
+        grad_h, gar, gac = _backward(ctx.negative_slope, row_ptr, col_ind, col_ptr, row_ind,
+                                     edge_max, edge_sum, h, attn_row, attn_col, out,
+                                     grad_out.contiguous(), ctx.activation)
+        gl, gr = gat_scores_backward(h, attn_l, attn_r, gar, gac, grad_h)
+        g2 = grad_h.view(grad_h.shape[0], -1)
+        grad_feat = grad_w = None
+        if ctx.needs_input_grad[0]:
+            grad_feat = dense.gemm_any_k(g2, W, True)      # g (N, HF) @ W^T: W is (in, HF) = "N x K" of this product
+        if ctx.needs_input_grad[1]:
+            if feat.shape[0] >= dense.TN_MIN_ROWS and feat.data_ptr() % 16 == 0 and g2.data_ptr() % 16 == 0:
+                grad_w = dense.gemm_tn(feat, g2)
+            else:
+                dense._note_fallback()
+                grad_w = feat.t() @ g2
+        return (grad_feat, grad_w, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None, None)
+
+
+def projected_layer_supported(feat, W, H, F):
+    """Whether FusedGATProjectedLayerFunction applies: the tensor-core GEMM takes the product and
+    its epilogue can form the scores for H heads of width F."""
+    from . import dense
+
+    return (feat.dim() == 2 and fused_scores_supported(H, F) and dense.scores_supported(H, F)
+            and dense.supported(feat.shape[0], W.shape[1], W.shape[0], feat))
 
 
 def fused_gat_layer_op(h, attn_l, attn_r, row_ptr, col_ind, col_ptr, row_ind, negative_slope,

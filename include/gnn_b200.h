@@ -280,6 +280,17 @@ int gnn_gemm_tf32x3(const float* A, const float* B, int b_is_n_by_k, float* C, i
                     int64_t K, void* workspace, size_t workspace_bytes, int* status,
                     cudaStream_t stream);
 
+/* gnn_gemm_tf32x3 for the projection of a GAT layer: C rows are `heads` heads of `head_w` floats
+ * (heads * head_w == N), and the per-node attention scores of layers/gatconv_layer.py:52-53,
+ *   score_l[m, h] = <C[m, h, :], attn_l[h, :]>,   score_r[m, h] = <C[m, h, :], attn_r[h, :]>,
+ * are formed in the GEMM's epilogue by the thread that stores the row: no pass over C afterwards.
+ * head_w must be 32, 64 or 128, or heads == 1 with N <= 128 (gnn_gemm_tf32x3_scores_supported). */
+int gnn_gemm_tf32x3_scores_supported(int heads, int head_w);
+int gnn_gemm_tf32x3_scores(const float* A, const float* B, int b_is_n_by_k, float* C, int64_t M, int64_t N,
+                           int64_t K, const float* attn_l /*[heads,head_w]*/, const float* attn_r, int heads,
+                           int head_w, float* score_l /*[M,heads]*/, float* score_r, void* workspace,
+                           size_t workspace_bytes, int* status, cudaStream_t stream);
+
 /* C[K1,N1] = A^T * B with A [M,K1], B [M,N1] (the weight gradient X^T * dH of a projection;
  * autograd's MmBackward in the reference, a cuBLAS SGEMM).  Same 3xTF32 tcgen05 kernel, the
  * reduction axis M cut into ranges whose partial tiles are summed in a fixed order. */
@@ -332,6 +343,18 @@ int gnn_gat_fwd_act(const int* row_ptr, const int* col_ind, int64_t n_rows, int6
                     float negative_slope, float alpha, float* out /*[n_rows,H,F]*/,
                     float* act_out /*[n_rows,H,F]*/, float* edge_max, float* edge_sum, void* workspace,
                     size_t workspace_bytes, cudaStream_t stream);
+
+/* ---- opt-in: gathered operand stored as bfloat16 (no counterpart in the reference) -----------
+ * gnn_gat_fwd_bf16 is gnn_gat_fwd with in_feat given as bfloat16 [*,H,F] (half the gather traffic);
+ * scores, softmax, accumulation and outputs are fp32.  Outside the fp32 parity contract of the
+ * other entry points: the result equals gnn_gat_fwd on the bfloat16-rounded features.
+ * H <= 8, H*F <= 512 and a multiple of 8, 16-byte aligned.  Workspace as gnn_gat_fwd.
+ * gnn_to_bf16 converts n fp32 values (n % 8 == 0) with round-to-nearest-even. */
+int gnn_to_bf16(const float* in, int64_t n, void* out_bf16, cudaStream_t stream);
+int gnn_gat_fwd_bf16(const int* row_ptr, const int* col_ind, int64_t n_rows, int64_t nnz,
+                     const float* attn_row, const float* attn_col, const void* in_feat_bf16, int H, int F,
+                     float negative_slope, float* out, float* edge_max, float* edge_sum, void* workspace,
+                     size_t workspace_bytes, cudaStream_t stream);
 
 /* ---- graph construction ------------------------------------------------------------------
  * gnn_coo_to_csr replaces the host-side preprocessing of the reference's scripts

@@ -462,3 +462,57 @@ def test_gat_forward_with_fused_elu(cuda, name, H, F):
     assert_close(act, torch.nn.functional.elu(out2.double()), "elu(out)", rtol=1e-6, atol=2e-6)
     eo, _, _ = ref.gat_forward(attn_row, attn_col, g.row_ptr, g.col_ind, 0.2, feat)
     assert_close(act, torch.nn.functional.elu(eo), "elu(out) vs oracle")
+
+
+@pytest.mark.parametrize("H,F", [(8, 128), (12, 8), (16, 40), (2, 300)])
+def test_gat_layer_with_many_or_wide_heads(cuda, H, F):
+    """More than 8 heads, or rows wider than one tile: forward and backward run head by head and
+    the GATConv layer trains (the reference's fused_gat takes any H and F)."""
+    from ae_mlsys_gnn_b200.layers import GATConv
+    from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
+
+    torch.manual_seed(2)
+    g = power_law_graph(300, 12, seed=11)
+    layer = GATConv(10, F, H).to(cuda)
+    x = torch.randn(g.n, 10)
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    cp, ri, _ = csr2csc(rp, ci)
+    xd = x.to(cuda).requires_grad_(True)
+    out = layer(rp, ci, cp, ri, xd)
+    gout = torch.randn(out.shape, generator=torch.Generator().manual_seed(3))
+    out.backward(gout.to(cuda))
+    W = layer.W.detach().cpu().double().requires_grad_(True)
+    al = layer.attn_l.detach().cpu().double().requires_grad_(True)
+    ar = layer.attn_r.detach().cpu().double().requires_grad_(True)
+    xr = x.double().requires_grad_(True)
+    eo = ref.gat_layer_dgl(g.row_ptr, g.col_ind, xr, W, al, ar, 0.2)
+    eo.backward(gout.double())
+    assert_close(out, eo, "layer out", scale_atol=True)
+    assert_close(layer.W.grad, W.grad, "W.grad", scale_atol=True)
+    assert_close(layer.attn_l.grad, al.grad, "attn_l.grad", scale_atol=True)
+    assert_close(layer.attn_r.grad, ar.grad, "attn_r.grad", scale_atol=True)
+    assert_close(xd.grad, xr.grad, "x.grad", scale_atol=True)
+
+
+@pytest.mark.parametrize("name", ["empty_rows", "hub", "long_rows", "random_200"])
+@pytest.mark.parametrize("H,F", [(4, 128), (4, 64), (8, 8), (1, 256), (2, 16), (1, 8)])
+def test_gat_forward_bf16_gather(cuda, name, H, F):
+    """Opt-in bfloat16 storage of the gathered rows: equals the fp32 kernel, and the oracle, on the
+    rounded features within the usual fp32 tolerance (rounding the input is the only difference)."""
+    from ae_mlsys_gnn_b200.operators import fused_gat as G
+
+    g = crafted_graphs()[name]
+    nc = _n_cols(g)
+    attn_row, attn_col, feat, _ = _inputs(g, H, F, 31, nc)
+    feat16 = feat.to(torch.bfloat16)
+    d = [t.to(cuda) for t in (attn_row, attn_col, feat)]
+    rp, ci = g.row_ptr.to(cuda), g.col_ind.to(cuda)
+    conv = G.to_bf16(d[2])
+    assert torch.equal(conv.cpu().view(torch.int16), feat16.view(torch.int16)), "round to nearest even"
+    out, m, s = G.gat_forward_bf16(d[0], d[1], rp, ci, 0.2, conv)
+    eo, em, es = ref.gat_forward(attn_row, attn_col, g.row_ptr, g.col_ind, 0.2, feat16.float())
+    assert_close(out, eo, "out (bf16 gather)")
+    assert_close(s, es, "edge_sum")
+    out32, m32, s32 = G.gat_forward(d[0], d[1], rp, ci, 0.2, conv.float())
+    assert_close(out, out32, "bf16 gather vs fp32 kernel on the rounded features")
+    assert torch.equal(m, m32)
