@@ -14,7 +14,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 BUILD = os.path.join(HERE, "build")
-LIB = os.path.join(HERE, "libgnn_b200.so")
+# GNN_B200_LIB: load another build of the library (the A/B timing of two kernel variants)
+LIB = os.environ.get("GNN_B200_LIB") or os.path.join(HERE, "libgnn_b200.so")
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",

@@ -1,4 +1,5 @@
 // C-ABI entry points of the fused GAT forward / backward.
+#include <stdlib.h>
 #include "../../include/gnn_b200.h"
 #include "gat_narrow.cuh"
 
@@ -10,7 +11,14 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // One head, rows of at most 64 floats that cannot be read with 128-bit accesses: the
 // sub-warp tiles of gat_narrow.cuh (several rows per warp instruction).
-bool narrow_shape(const HeadPlan& pl, int H, int64_t width) { return pl.fused && !pl.vec && H == 1 && width <= 64; }
+// (GNN_B200_NARROW=0 in the environment keeps the general tile: for A/B timing of the two.)
+bool narrow_shape(const HeadPlan& pl, int H, int64_t width) {
+  static const bool enabled = [] {
+    const char* e = getenv("GNN_B200_NARROW");
+    return !(e && e[0] == '0');
+  }();
+  return enabled && pl.fused && !pl.vec && H == 1 && width <= 64;
+}
 
 // Calls fn(integral_constant<LPR>, integral_constant<Q>) for the sub-warp tile covering `width`.
 template <class Fn>

@@ -239,7 +239,7 @@ class BytesLedger:
             return algorithmic_bytes(name, a[3], 0, a[4], a[5]), f"{a[4]}x{a[5]}"
         if name == "gnn_gat_scores_bwd":
             return algorithmic_bytes(name, a[5], 0, a[6], a[7]), f"{a[6]}x{a[7]}"
-        if name == "gnn_gemm_tf32x3":
+        if name in ("gnn_gemm_tf32x3", "gnn_gemm_tf32x3_scores"):
             return 0.0, f"{a[4]}x{a[5]}x{a[6]}"
         if name == "gnn_gemm_tf32x3_tn":
             return 0.0, f"{a[3]}x{a[4]}x{a[5]}"
