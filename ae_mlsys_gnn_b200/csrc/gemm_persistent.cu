@@ -31,6 +31,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include "../../include/gnn_b200.h"
 #include "common.cuh"
 #include "gemm_persistent.cuh"
@@ -38,16 +39,26 @@
 namespace gnn {
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 32;
-constexpr int kStages = 3;
-constexpr int kTileBytes = BM * BK * 4;      // 16 KB: one operand tile (raw/hi or lo)
-constexpr int kStageBytes = 4 * kTileBytes;  // A0, A1, B0, B1
+constexpr int BM = 128, BK = 32;
+constexpr int kTileBytes = BM * BK * 4;      // 16 KB: one 128-row operand tile (raw/hi or lo)
 constexpr int kConvThreads = 128;
 constexpr int kThreads = 32 * 10;
 constexpr int kAccBufs = 2;
-constexpr int kTmemCols = kAccBufs * BN;     // 256
-constexpr int kNumBars = 3 * kStages + 2 * kAccBufs;
-constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 8 * kNumBars + 16;
+constexpr int kMaxStages = 3;
+constexpr int kNumBars = 3 * kMaxStages + 2 * kAccBufs;
+
+// Geometry of one instantiation.  BN = 128: three stages, 256 tensor-memory columns, any operand
+// mode.  BN = 256 (B given as split hi/lo, K-major: the projection weights): the B tile is
+// 256 rows, two stages of 96 KB, all 512 tensor-memory columns; per multiply-add it reads 2/3 of
+// the shared-memory bytes of the 128-wide tile, which is what bounds this kernel.
+template <int BN>
+struct Geom {
+  static constexpr int kStages = BN == 128 ? 3 : 2;
+  static constexpr int kBTileBytes = BN * BK * 4;
+  static constexpr int kStageBytes = 2 * kTileBytes + 2 * kBTileBytes;  // A0, A1, B0, B1
+  static constexpr int kTmemCols = kAccBufs * BN;
+  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 8 * kNumBars + 16;
+};
 // The tensor core adds into its fp32 accumulator with truncation: a chain of n MMAs comes
 // out low by about n * 2^-26 of its value (measured: -4e-4 after 25,000 MMAs).  After this
 // many K blocks (12 MMAs each) the accumulator is therefore drained and the running sum
@@ -165,20 +176,23 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 }
 
 __device__ __forceinline__ bool is_raw(int mode) { return mode == kKMajorRaw || mode == kMnMajorRaw; }
-__device__ __forceinline__ uint32_t operand_tx_bytes(int mode) { return is_raw(mode) ? kTileBytes : 2 * kTileBytes; }
+__device__ __forceinline__ uint32_t operand_tx_bytes(int mode, int tile_bytes) {
+  return is_raw(mode) ? tile_bytes : 2 * tile_bytes;
+}
 
 // Issues the copies of one operand for one stage.  r0: first output row of the tile;
-// kblk: index of the block of 32 along the reduction axis.
+// kblk: index of the block of 32 along the reduction axis; tile_bytes: bytes of one tile of
+// this operand (the second copy of a split operand follows the first).
 __device__ __forceinline__ void load_operand(int mode, uint32_t x0, const CUtensorMap* m0, const CUtensorMap* m1,
-                                             int r0, int kblk, uint32_t bar) {
+                                             int r0, int kblk, uint32_t bar, int tile_bytes = kTileBytes) {
   if (mode == kKMajorRaw) {
     tma_load_2d(x0, m0, kblk * BK, r0, bar);
   } else if (mode == kKMajorSplit) {
     tma_load_2d(x0, m0, kblk * BK, r0, bar);
-    tma_load_2d(x0 + kTileBytes, m1, kblk * BK, r0, bar);
+    tma_load_2d(x0 + tile_bytes, m1, kblk * BK, r0, bar);
   } else if (mode == kKMajorSplitBlocked) {
     tma_load_3d(x0, m0, 0, r0, kblk, bar);
-    tma_load_3d(x0 + kTileBytes, m1, 0, r0, kblk, bar);
+    tma_load_3d(x0 + tile_bytes, m1, 0, r0, kblk, bar);
   } else {
 #pragma unroll
     for (int g = 0; g < BM / 32; ++g) tma_load_2d(x0 + g * 4096, m0, r0 + 32 * g, kblk * BK, bar);
@@ -206,6 +220,7 @@ struct TileCoord {
   int m0, n0, kb_begin, num_kb, z;
   int chains;  // accumulator chains of at most chain_kb K blocks (1 for an empty range)
 };
+template <int BN>
 __device__ __forceinline__ TileCoord decode_tile(const Params& p, int tile) {
   TileCoord t;
   const int nt = tile % p.tiles_n;
@@ -220,10 +235,15 @@ __device__ __forceinline__ TileCoord decode_tile(const Params& p, int tile) {
   return t;
 }
 
+template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
                        const __grid_constant__ CUtensorMap map_b0, const __grid_constant__ CUtensorMap map_b1,
                        Params p) {
+  constexpr int kStages = Geom<BN>::kStages;
+  constexpr int kStageBytes = Geom<BN>::kStageBytes;
+  constexpr int kBTileBytes = Geom<BN>::kBTileBytes;
+  constexpr int kTmemCols = Geom<BN>::kTmemCols;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
@@ -232,8 +252,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
   auto full_bar = [&](int s) { return bars + 8u * s; };                       // TMA -> converters
   auto conv_bar = [&](int s) { return bars + 8u * (kStages + s); };           // converters -> MMA
   auto empty_bar = [&](int s) { return bars + 8u * (2 * kStages + s); };      // MMA -> TMA
-  auto acc_full_bar = [&](int b) { return bars + 8u * (3 * kStages + b); };   // MMA -> epilogue
-  auto acc_empty_bar = [&](int b) { return bars + 8u * (3 * kStages + kAccBufs + b); };  // epilogue -> MMA
+  auto acc_full_bar = [&](int b) { return bars + 8u * (3 * kMaxStages + b); };   // MMA -> epilogue
+  auto acc_empty_bar = [&](int b) { return bars + 8u * (3 * kMaxStages + kAccBufs + b); };  // epilogue -> MMA
   const uint32_t tmem_slot = bars + 8u * kNumBars;
   uint32_t* const tmem_slot_ptr = reinterpret_cast<uint32_t*>(base_ptr + kStages * kStageBytes + 8 * kNumBars);
 
@@ -265,10 +285,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      const uint32_t tx = operand_tx_bytes(p.a_mode) + operand_tx_bytes(p.b_mode);
+      const uint32_t tx = operand_tx_bytes(p.a_mode, kTileBytes) + operand_tx_bytes(p.b_mode, kBTileBytes);
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < p.num_tiles && !s_failed; tile += gridDim.x) {
-        const TileCoord t = decode_tile(p, tile);
+        const TileCoord t = decode_tile<BN>(p, tile);
         for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t round = it / kStages;
@@ -276,7 +296,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
           const uint32_t st = base + s * kStageBytes;
           mbar_expect_tx(full_bar(s), tx);
           load_operand(p.a_mode, st, &map_a0, &map_a1, t.m0, t.kb_begin + kb, full_bar(s));
-          load_operand(p.b_mode, st + 2 * kTileBytes, &map_b0, &map_b1, t.n0, t.kb_begin + kb, full_bar(s));
+          load_operand(p.b_mode, st + 2 * kTileBytes, &map_b0, &map_b1, t.n0, t.kb_begin + kb, full_bar(s),
+                       kBTileBytes);
         }
       }
     }
@@ -289,7 +310,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
       uint32_t it = 0, tcount = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok && !s_failed; tile += gridDim.x) {
-        const TileCoord t = decode_tile(p, tile);
+        const TileCoord t = decode_tile<BN>(p, tile);
         int n_mma = min(BN, p.N - t.n0);
         n_mma = (n_mma + 15) & ~15;
         const uint32_t idesc = make_idesc(n_mma, a_mn, b_mn);
@@ -309,7 +330,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
             const uint64_t a_hi = operand_desc(st, a_mn);
             const uint64_t a_lo = operand_desc(st + kTileBytes, a_mn);
             const uint64_t b_hi = operand_desc(st + 2 * kTileBytes, b_mn);
-            const uint64_t b_lo = operand_desc(st + 3 * kTileBytes, b_mn);
+            const uint64_t b_lo = operand_desc(st + 2 * kTileBytes + kBTileBytes, b_mn);
 #pragma unroll
             for (int k = 0; k < BK / 8; ++k) {
               const uint64_t da = a_step * k, db = b_step * k;
@@ -330,13 +351,15 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
     uint32_t it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.num_tiles && ok && !s_failed; tile += gridDim.x) {
-      const TileCoord t = decode_tile(p, tile);
+      const TileCoord t = decode_tile<BN>(p, tile);
       for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
         const int s = it % kStages;
         if (!mbar_wait(full_bar(s), (it / kStages) & 1, &s_failed)) { s_failed = 1; ok = false; break; }
         uint8_t* st = base_ptr + s * kStageBytes;
         if (conv_a) convert_tile(st, st + kTileBytes, tid);
-        if (conv_b) convert_tile(st + 2 * kTileBytes, st + 3 * kTileBytes, tid);
+        if constexpr (BN == 128) {  // the 256-wide tile takes B already split
+          if (conv_b) convert_tile(st + 2 * kTileBytes, st + 3 * kTileBytes, tid);
+        }
         // the tensor core reads shared memory through the async proxy
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_arrive(conv_bar(s));
@@ -348,10 +371,12 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
     uint32_t tcount = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.num_tiles && ok && !s_failed; tile += gridDim.x) {
-      const TileCoord t = decode_tile(p, tile);
+      const TileCoord t = decode_tile<BN>(p, tile);
       const int row = t.m0 + lg * 32 + lane;
       float* const Cout = p.C + (size_t)t.z * p.split_stride;
-      float sum[BN];  // running fp32 sum of this thread's output row when the tile has several chains
+      // running fp32 sum of this thread's output row when the tile has several chains (the
+      // 256-wide tile is only launched for reductions that fit one chain)
+      float sum[BN == 128 ? BN : 1];
       float dl = 0.f, dr = 0.f;  // running dot products of the current head with attn_l / attn_r
       for (int ch = 0; ch < t.chains; ++ch, ++tcount) {
         const int buf = tcount & 1;
@@ -378,12 +403,14 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
 #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = 0u;  // an empty range contributes nothing
           }
-          if (t.chains > 1) {
+          if constexpr (BN == 128) {
+            if (t.chains > 1) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float v = __uint_as_float(r[j]);
-              sum[c * 32 + j] = ch == 0 ? v : sum[c * 32 + j] + v;
-              r[j] = __float_as_uint(sum[c * 32 + j]);
+              for (int j = 0; j < 32; ++j) {
+                const float v = __uint_as_float(r[j]);
+                sum[c * 32 + j] = ch == 0 ? v : sum[c * 32 + j] + v;
+                r[j] = __float_as_uint(sum[c * 32 + j]);
+              }
             }
           }
           if (last && p.score_l != nullptr) {
@@ -513,14 +540,15 @@ bool encode_blocked(CUtensorMap* m, const float* ptr, int64_t rows, int64_t kblo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-bool encode_operand(const GemmOperand& o, int64_t K, CUtensorMap* m0, CUtensorMap* m1) {
+// box_rows: output rows of this operand per tile (128, or 256 for the wide B tile)
+bool encode_operand(const GemmOperand& o, int64_t K, CUtensorMap* m0, CUtensorMap* m1, int box_rows = BM) {
   const int64_t kblocks = (K + BK - 1) / BK;
   switch (o.mode) {
     case kKMajorRaw:
       *m1 = CUtensorMap{};
-      return encode_2d(m0, o.p0, o.rows, K, BK, BM);
+      return encode_2d(m0, o.p0, o.rows, K, BK, box_rows);
     case kKMajorSplit:
-      return encode_2d(m0, o.p0, o.rows, K, BK, BM) && encode_2d(m1, o.p1, o.rows, K, BK, BM);
+      return encode_2d(m0, o.p0, o.rows, K, BK, box_rows) && encode_2d(m1, o.p1, o.rows, K, BK, box_rows);
     case kKMajorSplitBlocked:
       return encode_blocked(m0, o.p0, o.rows, kblocks) && encode_blocked(m1, o.p1, o.rows, kblocks);
     case kMnMajorRaw:
@@ -530,23 +558,16 @@ bool encode_operand(const GemmOperand& o, int64_t K, CUtensorMap* m0, CUtensorMa
   return false;
 }
 
-}  // namespace
-
-int launch_gemm_persistent(const GemmOperand& a, const GemmOperand& b, int64_t K, float* C, int64_t ldc,
-                           int splits, int64_t split_stride, int* status, cudaStream_t stream,
-                           const GemmScores* scores) {
-  CUtensorMap ma0, ma1, mb0, mb1;
-  if (!encode_operand(a, K, &ma0, &ma1) || !encode_operand(b, K, &mb0, &mb1)) {
-    set_last_error("gnn_gemm_tf32x3: cuTensorMapEncodeTiled failed");
-    return GNN_ERR_CUDA;
-  }
-  static bool attr_set = false;  // per process; the attribute is per device, so set it on every device seen
+template <int BN>
+int launch_instance(const CUtensorMap& ma0, const CUtensorMap& ma1, const CUtensorMap& mb0, const CUtensorMap& mb1,
+                    Params p, int64_t b_rows, int splits, cudaStream_t stream) {
+  static bool attr_set = false;  // per process and instantiation; the attribute is per device
   static int attr_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set || attr_dev != dev) {
-    if (cudaFuncSetAttribute(gemm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)kSmemBytes) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_persistent_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)Geom<BN>::kSmemBytes) != cudaSuccess) {
       set_last_error("gnn_gemm_tf32x3: cannot reserve dynamic shared memory");
       return GNN_ERR_CUDA;
     }
@@ -556,20 +577,31 @@ int launch_gemm_persistent(const GemmOperand& a, const GemmOperand& b, int64_t K
   int sms = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms <= 0) sms = 148;
-
-  Params p;
-  p.M = (int)a.rows;
-  p.N = (int)b.rows;
-  p.total_kb = (int)((K + BK - 1) / BK);
-  p.kb_per_split = (p.total_kb + splits - 1) / splits;
-  p.tiles_m = (int)((a.rows + BM - 1) / BM);
-  p.tiles_n = (int)((b.rows + BN - 1) / BN);
+  p.tiles_n = (int)((b_rows + BN - 1) / BN);
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n * splits;
   if (tiles > INT32_MAX) {
     set_last_error("gnn_gemm_tf32x3: too many output tiles");
     return GNN_ERR_INVALID_ARG;
   }
   p.num_tiles = (int)tiles;
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  gemm_persistent_kernel<BN><<<grid, kThreads, Geom<BN>::kSmemBytes, stream>>>(ma0, ma1, mb0, mb1, p);
+  return GNN_OK;
+}
+
+}  // namespace
+
+int launch_gemm_persistent(const GemmOperand& a, const GemmOperand& b, int64_t K, float* C, int64_t ldc,
+                           int splits, int64_t split_stride, int* status, cudaStream_t stream,
+                           const GemmScores* scores) {
+  Params p;
+  p.M = (int)a.rows;
+  p.N = (int)b.rows;
+  p.total_kb = (int)((K + BK - 1) / BK);
+  p.kb_per_split = (p.total_kb + splits - 1) / splits;
+  p.tiles_m = (int)((a.rows + BM - 1) / BM);
+  p.tiles_n = 0;
+  p.num_tiles = 0;
   p.C = C;
   p.ldc = ldc;
   p.split_stride = split_stride;
@@ -586,9 +618,21 @@ int launch_gemm_persistent(const GemmOperand& a, const GemmOperand& b, int64_t K
     p.score_l = scores->score_l; p.score_r = scores->score_r;
     p.heads = scores->heads; p.head_w = scores->head_w;
   }
-  const int grid = (int)(tiles < sms ? tiles : sms);
-  gemm_persistent_kernel<<<grid, kThreads, kSmemBytes, stream>>>(ma0, ma1, mb0, mb1, p);
-  return GNN_OK;
+  // the 256-wide column tile: weights given split and K-major, a reduction that fits one
+  // accumulator chain, at least 256 output columns (GNN_B200_GEMM_BN=128 keeps the narrow tile)
+  static const bool wide_ok = [] {
+    const char* e = getenv("GNN_B200_GEMM_BN");
+    return !(e && e[0] == '1' && e[1] == '2' && e[2] == '8');
+  }();
+  const bool wide = wide_ok && b.mode == kKMajorSplit && a.mode == kKMajorRaw && splits == 1 && b.rows >= 256 &&
+                    p.total_kb <= kChainKb;
+  CUtensorMap ma0, ma1, mb0, mb1;
+  if (!encode_operand(a, K, &ma0, &ma1) || !encode_operand(b, K, &mb0, &mb1, wide ? 256 : BM)) {
+    set_last_error("gnn_gemm_tf32x3: cuTensorMapEncodeTiled failed");
+    return GNN_ERR_CUDA;
+  }
+  return wide ? launch_instance<256>(ma0, ma1, mb0, mb1, p, b.rows, splits, stream)
+              : launch_instance<128>(ma0, ma1, mb0, mb1, p, b.rows, splits, stream);
 }
 
 }  // namespace gnn

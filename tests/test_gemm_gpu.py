@@ -10,7 +10,9 @@ pytestmark = pytest.mark.gpu
 SHAPES = [(128, 128, 32), (1000, 512, 100), (300, 47, 512), (4097, 512, 512), (130, 70, 36), (5, 3, 4),
           (257, 256, 64), (2048, 64, 128), (999, 41, 256),
           (40000, 512, 64),   # more output tiles than SMs: every CTA walks several tiles
-          (150 * 128 + 5, 200, 96)]
+          (150 * 128 + 5, 200, 96),
+          (3000, 300, 128),   # 256-wide column tile with a partial second tile
+          (2500, 768, 64), (20000, 256, 512), (700, 512, 544)]  # three wide tiles; K at / beyond one accumulator chain
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -127,3 +129,25 @@ def test_gemm_misaligned_view(cuda):
     out = dense.gemm_any_k(a, w, False)
     dense.check_status()
     assert_close(out, a.double() @ w.double(), "gemm on a misaligned view", scale_atol=True)
+
+
+@pytest.mark.parametrize("M,K,H,F", [(5000, 100, 4, 128), (3001, 512, 4, 64), (777, 64, 8, 32), (4000, 96, 1, 47),
+                                      (1500, 36, 2, 128), (900, 128, 1, 128), (2000, 32, 16, 32)])
+def test_gemm_scores_epilogue(cuda, M, K, H, F):
+    """Projection with the per-head attention scores formed in the epilogue: same product as the plain
+    GEMM (bit for bit), scores against the float64 dot products of that product's rows."""
+    from ae_mlsys_gnn_b200.operators import dense
+
+    gen = torch.Generator().manual_seed(M + K + H)
+    x = torch.randn(M, K, generator=gen).to(cuda)
+    w = torch.randn(K, H * F, generator=gen).to(cuda)
+    al = torch.randn(H, F, generator=gen).to(cuda)
+    ar = torch.randn(H, F, generator=gen).to(cuda)
+    assert dense.scores_supported(H, F)
+    out, sl, sr = dense.gemm_any_k(x, w, False, scores=(al, ar))
+    plain = dense.gemm_any_k(x, w, False)
+    dense.check_status()
+    assert torch.equal(out, plain)
+    h = out.double().view(M, H, F)
+    assert_close(sl, (h * al.double()).sum(-1), "score_l", scale_atol=True)
+    assert_close(sr, (h * ar.double()).sum(-1), "score_r", scale_atol=True)
