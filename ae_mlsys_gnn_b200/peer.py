@@ -108,3 +108,44 @@ def halo_push(x: torch.Tensor, send_idx: torch.Tensor, send_off: list, dst_ptrs:
     with torch.cuda.device(dev):
         capi.call("gnn_halo_push", capi.ptr(x), row, capi.ptr(send_idx) if send_idx.numel() else None, off, dst,
                   world, own_dst_ptr if own_dst_ptr else None, int(n_own), capi.stream_ptr(dev))
+
+
+def probe(device, group=None) -> bool:
+    """Whether peer-mapped buffers work between the ranks of ``group`` on this node: every rank
+    stores one row into every other rank's buffer and checks what it received.  Collective; all
+    ranks return the same answer (False if any rank failed at any step)."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    ok = torch.ones(1, dtype=torch.float32, device=device)
+    buf = None
+    try:
+        buf = PeerBuffer(16 * world, device, group)
+    except Exception:
+        ok.zero_()
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+    if ok.item() < 1:  # some rank could not allocate or map: no rank pushes
+        if buf is not None:
+            buf.close()
+        return False
+    try:
+        mine = torch.full((1, 4), float(rank + 1), dtype=torch.float32, device=device)
+        own = buf.view((world, 4))
+        own.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+        idx = torch.zeros(world - 1, dtype=torch.int32, device=device)
+        offs, dst = [0], []
+        for q in range(world):
+            offs.append(offs[-1] + (0 if q == rank else 1))
+            dst.append(0 if q == rank else buf.ptrs[q] + 16 * rank)
+        halo_push(mine, idx, offs, dst, 0, 0)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+        got = own[:, 0].tolist()
+        for q in range(world):
+            if q != rank and got[q] != float(q + 1):
+                ok.zero_()
+    except Exception:
+        ok.zero_()
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+    buf.close()
+    return bool(ok.item() >= 1)

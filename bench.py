@@ -395,12 +395,12 @@ def run_cpu_epochs(wl: dict, steps: int, warmup: int, seed: int):
     return rec
 
 
-def config_of(wl: dict, world: int) -> dict:
+def config_of(wl: dict, world: int, exchange: str | None = None) -> dict:
     """The `config` record, identical in the library's arm and in the reference arm."""
     n, nnz = FULL_SIZES[wl["name"]]
+    exchange = exchange or os.environ.get("GNN_B200_EXCHANGE", "peer")
     return {"workload": f"{wl['name']}: {wl['desc']}", "nodes": n, "edges": nnz,
-            "parallelism": (f"row-block x{world}, {os.environ.get('GNN_B200_EXCHANGE', 'peer')} exchange"
-                            if world > 1 else "single GPU"),
+            "parallelism": (f"row-block x{world}, {exchange} exchange" if world > 1 else "single GPU"),
             "l2": ("flushed between steps (256 MB write)" if wl["name"] in L2_RESIDENT
                    else "inputs exceed L2 (126 MB)"),
             "seed": 0}
@@ -530,6 +530,7 @@ class Workload:
         from ae_mlsys_gnn_b200.operators.csr2csc import csr2csc
 
         self.wl, self.dev, self.world, self.rank = wl, dev, world, rank
+        self.exchange = None
         d = self.d = build_inputs(wl, dev, seed)
         if (d["n"], d["nnz"]) != FULL_SIZES[wl["name"]] and seed == 0:
             raise SystemExit(f"{wl['name']}: generator produced {d['n']} nodes / {d['nnz']} edges, "
@@ -587,11 +588,18 @@ class Workload:
         if scheme == "gather":
             from ae_mlsys_gnn_b200.partition import PartitionedGAT, build_partition
 
+            self.exchange = scheme
             self.part = build_partition(g.row_ptr, g.col_ind, self.col_ptr, self.row_ind, self.rank, self.world)
             self.model = PartitionedGAT(wl["in_dim"], wl["hidden"], wl["heads"], wl["classes"], 1).to(dev)
         else:
             from ae_mlsys_gnn_b200.halo import HaloGAT, build_halo_partition
 
+            if scheme == "peer":  # stores into the peers' memory need working IPC mappings on this node
+                from ae_mlsys_gnn_b200 import peer
+
+                if not peer.probe(dev):
+                    scheme = "nccl"
+            self.exchange = scheme
             torch.cuda.synchronize()
             t0 = time.perf_counter()
             self.part = build_halo_partition(g.row_ptr, g.col_ind, self.col_ptr, self.row_ind, self.rank,
@@ -815,6 +823,7 @@ def main():
         dense.check_status(dev)
     roof = roofline_of(per, args.steps, wl["name"])
     setup_ms = w.setup_ms
+    exchange = w.exchange
     if hasattr(w.model, "close"):
         w.model.close()  # peer-mapped exchange buffers
     fallbacks = dense.fallback_calls()
@@ -839,7 +848,7 @@ def main():
             "metric": METRIC, "value": ms_per_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": config_of(wl, world),
+            "config": config_of(wl, world, exchange),
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "setup_ms": setup_ms,
             "cublas_fallback_calls": fallbacks, "roofline": roof, "cpu_baseline": cpu,
             "models": models, "gpu_reference": gpu_ref,
