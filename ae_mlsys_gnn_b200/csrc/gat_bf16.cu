@@ -36,6 +36,139 @@ __global__ void to_bf16_kernel(const float* __restrict__ in, int64_t n8, uint4* 
   o.w = rn(b.z) | (rn(b.w) << 16);
   out[i] = o;
 }
+
+// The forward kernel for bfloat16 rows.  Same structure as wgather_kernel (one warp per edge
+// chunk, online softmax per piece, rows of the next edges requested while the current ones are
+// consumed), but the rows in flight are held as the 128-bit words that arrived and widened only
+// when they are consumed: a row occupies half the registers of an fp32 row, so twice as many
+// rows are in flight per warp.  (With the rows widened on arrival the kernel ran no faster than
+// the fp32 one: what bounds the gather is the number of rows in flight times the memory latency,
+// not the bytes.)
+template <int HP, int Q>
+__global__ void __launch_bounds__(kThreadsPerCta)
+gat_fwd_bf16_kernel(WGatherParams p, GatSoftmaxPolicy<HP> pol) {
+  using Tile = RowTileBf16<Q>;
+  constexpr int VW = 8;
+  constexpr int U = Q >= 2 ? 4 : 8;
+  __shared__ int cs_all[kWarpsPerCta][32];
+  __shared__ float ws_all[kWarpsPerCta][32 * HP];
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int chunk_id = blockIdx.x * kWarpsPerCta + wib;
+  if (chunk_id >= p.g.num_chunks) return;
+  int* cs = cs_all[wib];
+  float* ws = ws_all[wib];
+  Tile t;
+  t.init(lane, p.width, p.F, p.H);
+  const uint4* rows = reinterpret_cast<const uint4*>(p.feat);
+  const size_t ld16 = (size_t)p.ld_feat / 4;  // 16-byte words per row
+
+  for_each_piece(p.g, chunk_id, [&](int s, int a, int b, bool first, bool last) {
+    float segw[HP], segm[HP], segs[HP];
+#pragma unroll
+    for (int h = 0; h < HP; ++h) {
+      segw[h] = h < p.H ? __ldg(pol.attn_seg + (size_t)s * pol.ld_attn + h) : 0.f;
+      segm[h] = kNegBig;
+      segs[h] = 0.f;
+    }
+    for (int base = a; base < b; base += 32) {
+      const int e = base + lane;
+      if (e < b) {
+        const float* ac = pol.attn_idx + (size_t)__ldg(p.g.idx + e) * pol.ld_attn;
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+          if (h < p.H) {
+            const float x = leaky_relu(segw[h] + __ldg(ac + h), pol.slope);
+            if (x > segm[h]) {
+              segs[h] = segs[h] * expf(segm[h] - x) + 1.f;
+              segm[h] = x;
+            } else {
+              segs[h] += expf(x - segm[h]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < HP; ++h) {
+      const float m = warp_max(segm[h]);
+      segs[h] = warp_sum(segs[h] * expf(segm[h] - m));
+      segm[h] = m;
+    }
+
+    float acc[Q][VW];
+    t.zero(acc);
+    for (int base = a; base < b; base += 32) {
+      const int e = base + lane;
+      const bool ok = e < b;
+      const int c = __ldg(p.g.idx + (ok ? e : a));
+      const float* ac = pol.attn_idx + (size_t)c * pol.ld_attn;
+      float w[HP];
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        w[h] = 0.f;
+        if (h < p.H) w[h] = expf(leaky_relu(segw[h] + __ldg(ac + h), pol.slope) - segm[h]);
+      }
+      __syncwarp();
+      cs[lane] = c;
+#pragma unroll
+      for (int h = 0; h < HP; ++h) ws[lane * HP + h] = ok ? w[h] : 0.f;
+      __syncwarp();
+      const int nb = min(32, b - base);
+      const int nbr = (nb + U - 1) / U * U;
+      auto load_rows = [&](uint4 (&r)[U][Q], int jj) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint4* row = rows + (size_t)cs[jj + u] * ld16;
+#pragma unroll
+          for (int q = 0; q < Q; ++q) r[u][q] = t.valid[q] ? __ldg(row + lane + 32 * q) : make_uint4(0, 0, 0, 0);
+        }
+      };
+      auto accumulate = [&](const uint4 (&r)[U][Q], int jj) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int q = 0; q < Q; ++q) {
+            const float wq = ws[(jj + u) * HP + t.head[q]];
+            const unsigned x[4] = {r[u][q].x, r[u][q].y, r[u][q].z, r[u][q].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              acc[q][2 * i] = fmaf(wq, __uint_as_float(x[i] << 16), acc[q][2 * i]);
+              acc[q][2 * i + 1] = fmaf(wq, __uint_as_float(x[i] & 0xffff0000u), acc[q][2 * i + 1]);
+            }
+          }
+        }
+      };
+      uint4 ra[U][Q], rb[U][Q];
+      load_rows(ra, 0);
+#pragma unroll 1
+      for (int jj = 0; jj < nbr; jj += 2 * U) {
+        const bool more = jj + U < nbr;
+        if (more) load_rows(rb, jj + U);
+        accumulate(ra, jj);
+        if (more) {
+          if (jj + 2 * U < nbr) load_rows(ra, jj + 2 * U);
+          accumulate(rb, jj + U);
+        }
+      }
+    }
+
+    if (first && last) {
+      finish_segment<GatSoftmaxPolicy, HP, Q, Tile>(p, pol, t, lane, s, acc, segm, segs);
+    } else {
+      float* slot = p.scratch + slot_index(chunk_id, first) * p.slot_stride;
+      t.store(slot, lane, acc);
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        if (lane == h) {
+          slot[p.aux_off + h] = segm[h];
+          slot[p.aux_off + HP + h] = segs[h];
+        }
+      }
+    }
+  });
+}
+
 }  // namespace
 
 extern "C" int gnn_to_bf16(const float* in, int64_t n, void* out, cudaStream_t stream) {
@@ -85,7 +218,11 @@ extern "C" int gnn_gat_fwd_bf16(const int* row_ptr, const int* col_ind, int64_t 
     GatSoftmaxPolicy<HP> pol;
     pol.attn_seg = attn_row; pol.attn_idx = attn_col; pol.ld_attn = H; pol.slope = negative_slope;
     pol.seg_max = edge_max; pol.seg_sum = edge_sum;
-    launch_wgather<GatSoftmaxPolicy, HP, Q, true, RowTileBf16<Q>>(p, pol, stream);
+    if (p.g.num_chunks > 0) {
+      const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
+      gat_fwd_bf16_kernel<HP, Q><<<blocks, kThreadsPerCta, 0, stream>>>(p, pol);
+    }
+    launch_wgather_fixup<GatSoftmaxPolicy, HP, Q, true, RowTileBf16<Q>>(p, pol, stream);
   };
   using std::integral_constant;
   auto by_q = [&](auto hp) {
