@@ -75,8 +75,9 @@ class PeerBuffer:
             return torch.empty(tuple(shape), dtype=dtype, device=self.device)
         return torch.as_tensor(_Span(self._own + byte_offset, shape, dtype, self), device=self.device)
 
-    def close(self):
-        """Unmaps the peers' allocations, waits for every rank to have done so, frees the own one."""
+    def close(self, collective: bool = True):
+        """Unmaps the peers' allocations, waits for every rank to have done so (``collective``:
+        every rank calls close at the same point), frees the own one."""
         if self._own is None:
             return
         torch.cuda.synchronize(self.device)
@@ -84,7 +85,7 @@ class PeerBuffer:
             for p in self._opened:
                 capi.lib().gnn_peer_close(p)
             self._opened = []
-            if dist.is_initialized():
+            if collective and dist.is_initialized():
                 dist.barrier(group=self.group)
             capi.lib().gnn_peer_free(self._own)
         self._own = None
@@ -124,7 +125,7 @@ def probe(device, group=None) -> bool:
     dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
     if ok.item() < 1:  # some rank could not allocate or map: no rank pushes
         if buf is not None:
-            buf.close()
+            buf.close(collective=False)  # the ranks that failed hold no buffer to close
         return False
     try:
         mine = torch.full((1, 4), float(rank + 1), dtype=torch.float32, device=device)
