@@ -10,7 +10,6 @@ MoNet  script/train/train_gmmconv_our.py:22-68
 from __future__ import annotations
 
 import torch
-import torch.nn.functional as F
 from torch import nn
 
 from .layers import EdgeConv, GATConv, GMMConv
@@ -51,14 +50,16 @@ class DGCNN(nn.Module):
         super().__init__()
         self.k = k
         dims = [input_dims] + list(feature_dims)
-        self.conv = nn.ModuleList([EdgeConv(dims[i], dims[i + 1]) for i in range(len(feature_dims))])
+        # LeakyReLU(0.2) follows every layer; it runs inside the aggregation kernels
+        self.conv = nn.ModuleList([EdgeConv(dims[i], dims[i + 1], negative_slope=0.2)
+                                   for i in range(len(feature_dims))])
         self.proj_output = nn.Linear(dims[-1], output_classes)
 
     def forward(self, x, src_ind):
         batch, n_points, _ = x.shape
         h = x.reshape(batch * n_points, -1)
         for conv in self.conv:
-            h = F.leaky_relu(conv(self.k, src_ind, h), 0.2)
+            h = conv(self.k, src_ind, h)
         h = h.view(batch, n_points, -1).max(dim=1).values
         return self.proj_output(h)
 

@@ -240,6 +240,19 @@ int gnn_edgeconv_fwd(int k, const int* src_ind /*[n*k]*/, const float* h_src /*[
 int gnn_edgeconv_bwd(const float* grad_out /*[n,F]*/, const int* max_idx /*[n,F]*/, int64_t n,
                      int64_t n_src, int F, float* grad_src /*[n_src,F]*/, cudaStream_t stream);
 
+/* The same pair with the LeakyReLU(slope > 0) the DGCNN model applies to every EdgeConv
+ * output (script/train/train_edgeconv_our.py:44-52) folded in, saving one read and one
+ * write of [n,F] in each direction: the forward stores leaky(max) (max_idx unchanged, the
+ * activation being monotone), the backward applies LeakyReLU' by the sign of `out`, writes
+ * the result as grad_dst (the gradient of h_dst) and scatters it into grad_src. */
+int gnn_edgeconv_fwd_act(int k, const int* src_ind, const float* h_src, const float* h_dst,
+                         int64_t n, int F, float slope, float* out, int* max_idx,
+                         cudaStream_t stream);
+int gnn_edgeconv_bwd_act(const float* grad_out /*[n,F]*/, const float* out /*[n,F]*/, float slope,
+                         const int* max_idx, int64_t n, int64_t n_src, int F,
+                         float* grad_src /*[n_src,F]*/, float* grad_dst /*[n,F]*/,
+                         cudaStream_t stream);
+
 /* ---- fused GMMConv ------------------------------------------------------------------
  * gnn_gmm_fwd replaces gmm.gmmconv (src/fused_gmmconv/gmmconv.cc,
  * gmmconv.cu:48-80,201-219):

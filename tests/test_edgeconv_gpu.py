@@ -70,3 +70,29 @@ def test_edgeconv_backward_scatter(cuda):
     g = torch.randn(n, F, generator=gen)
     got = edgeconv_backward(g.to(cuda), idx.to(cuda))
     assert_close(got, ref.edgeconv_backward(g, idx), "grad_src", scale_atol=True)
+
+
+@pytest.mark.parametrize("n,k,F", [(64, 20, 64), (33, 5, 7), (30, 33, 8), (17, 20, 100)])
+@pytest.mark.parametrize("ties", [False, True])
+def test_edgeconv_leaky_forward_and_backward(cuda, n, k, F, ties):
+    """LeakyReLU folded into the kernels: the output is bitwise leaky(max) of the plain forward
+    (same arg-max), the backward equals autograd through the oracle's max followed by
+    torch's leaky_relu."""
+    from ae_mlsys_gnn_b200.operators.fused_edgeconv import edgeconv_forward, fused_edgeconv_op
+
+    slope = 0.2
+    src, h_src, h_dst = _case(n, k, F, n * 77 + k, ties)
+    h_src = h_src - 1.0  # both signs of the maximum occur
+    out, idx = edgeconv_forward(k, src.to(cuda), h_src.to(cuda), h_dst.to(cuda), slope)
+    eo, ei = ref.edgeconv_forward(k, src, h_src, h_dst)
+    assert torch.equal(idx.cpu(), ei)
+    assert torch.equal(out.cpu(), torch.nn.functional.leaky_relu(eo, slope))
+
+    hs = h_src.to(cuda).requires_grad_(True)
+    hd = h_dst.to(cuda).requires_grad_(True)
+    gen = torch.Generator().manual_seed(5)
+    gout = torch.randn(n, F, generator=gen)
+    fused_edgeconv_op(k, src.to(cuda), hs, hd, slope).backward(gout.to(cuda))
+    g_pre = torch.where(eo > 0, gout, gout * slope)
+    assert torch.equal(hd.grad.cpu(), g_pre)
+    assert_close(hs.grad, ref.edgeconv_backward(g_pre, ei), "grad_src", scale_atol=True)
