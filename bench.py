@@ -504,11 +504,19 @@ def gpu_reference_leg(dev, seed: int):
 # one workload on the GPU(s)
 # ----------------------------------------------------------------------------------------
 
-def traffic_from_profile(key: str, workload: str):
-    """DRAM bytes per launch measured once with ncu (profiles/traffic.json), or None."""
+def traffic_from_profile(key: str, workload: str, launch_bytes: float | None = None):
+    """DRAM bytes per launch measured once with ncu on the whole graph (profiles/traffic.json), or
+    None.  ``launch_bytes``: algorithmic bytes of the launch in question; when the capture records the
+    algorithmic bytes of the captured launch and they differ (a rank's block of a partitioned run),
+    the measured traffic is scaled by their ratio, i.e. the captured DRAM-to-algorithmic ratio is
+    assumed to carry over."""
     try:
-        t = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))
-        return t.get(workload, {}).get(key)
+        t = json.load(open(os.path.join(ROOT, "profiles", "traffic.json"))).get(workload, {})
+        dram = t.get(key)
+        full = t.get("_algorithmic_bytes", {}).get(key)
+        if dram and launch_bytes and full and abs(launch_bytes - full) > 0.02 * full:
+            return dram * launch_bytes / full
+        return dram
     except Exception:
         return None
 
@@ -644,7 +652,7 @@ def barrier(world):
     torch.cuda.synchronize()
 
 
-def timed_epochs(w: Workload, steps: int, warmup: int, sampler=None):
+def timed_epochs(w: Workload, steps: int, warmup: int, sampler=None, timeline_path=None):
     """Warm-up, then `steps` epochs bracketed by barrier + synchronize, one CUDA-event pair per
     step; small workloads get an L2 flush (256 MB write) between steps, outside the pairs.
     Returns (ms per step as the max over ranks, per-entry-point summary, launch counts, clocks)."""
@@ -674,6 +682,16 @@ def timed_epochs(w: Workload, steps: int, warmup: int, sampler=None):
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
     per = ledger.summary()
+    if timeline_path:  # the last timed step as a list of library calls on the device's clock
+        a0, b0 = ev[-1]
+        span = a0.elapsed_time(b0)
+        calls = []
+        for (name, s, t), key in zip(ledger.timer.records, ledger.keys):
+            at = a0.elapsed_time(s)
+            if 0.0 <= at <= span:
+                calls.append({"key": key, "t_ms": round(at, 4), "ms": round(s.elapsed_time(t), 4)})
+        with open(timeline_path, "w") as f:
+            json.dump({"step_ms": span, "calls": calls}, f)
     for key, nbytes in ledger.link_bytes.items():  # NVLink side of the exchange kernels
         if key in per and per[key]["ms"] > 0:
             per[key]["link_bytes"] = nbytes
@@ -711,13 +729,17 @@ def roofline_of(per: dict, steps: int, workload: str):
     launch_ms = p["ms"] / p["calls"]
     alg = p["bytes"] / p["calls"]
     alg_gbs = alg / (launch_ms * 1e-3) / 1e9 if launch_ms > 0 else 0.0
-    traffic = traffic_from_profile(key, workload)
+    traffic = traffic_from_profile(key, workload, alg)
+    scaled = traffic is not None and traffic != traffic_from_profile(key, workload)
     roof = {"bound": "hbm", "kernel": key, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
             "launch_ms": launch_ms, "traffic": traffic, "bytes_per_launch_algorithmic": alg,
             "achieved_algorithmic": alg_gbs, "frac_algorithmic": alg_gbs / peak}
     if traffic:
         roof["achieved"] = traffic / (launch_ms * 1e-3) / 1e9
         roof["basis"] = "measured DRAM bytes per launch (ncu, profiles/traffic.json) / CUDA-event time"
+        if scaled:
+            roof["basis"] += ("; the capture is of the whole graph on one GPU, scaled to this rank's block by"
+                              " algorithmic bytes")
     else:  # no capture of this kernel and shape: only the algorithmic figure exists
         roof["achieved"] = alg_gbs
         roof["basis"] = "algorithmic bytes / CUDA-event time (no DRAM capture for this kernel and shape)"
@@ -731,7 +753,7 @@ def roofline_of(per: dict, steps: int, workload: str):
             e["nvlink_gbs"] = v["link_bytes"] / (v["ms"] * 1e-3) / 1e9
         if v["bytes"] > 0 and v["ms"] > 0:
             e["gbs_algorithmic"] = v["bytes"] / (v["ms"] * 1e-3) / 1e9
-            t = traffic_from_profile(k, workload)
+            t = traffic_from_profile(k, workload, v["bytes"] / v["calls"])
             if t:
                 e["gbs_dram"] = t * v["calls"] / (v["ms"] * 1e-3) / 1e9
         entries[k] = e
@@ -785,6 +807,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-models", action="store_true", help="skip the sub-records of the other configurations")
     ap.add_argument("--no-gpu-reference", action="store_true", help="skip timing the reference's CUDA operators")
+    ap.add_argument("--timeline", default=None, metavar="PATH",
+                    help="rank 0 writes the last timed step as a JSON list of library calls (start, duration)")
     args = ap.parse_args()
     wl = dict(WORKLOADS[args.workload], name=args.workload)
     if args.warmup < 3 and args.impl == "b200":
@@ -813,7 +837,8 @@ def main():
     _capi.lib()
     w = Workload(wl, dev, args.seed, world, rank)
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    ms_per_step, per, counts, clocks = timed_epochs(w, args.steps, args.warmup, sampler)
+    ms_per_step, per, counts, clocks = timed_epochs(w, args.steps, args.warmup, sampler,
+                                                    args.timeline if rank == 0 else None)
     launches = count_launches(counts, 0)
 
     # ---- end to end: host buffers in, loss out, through the public API -------------------
@@ -822,6 +847,18 @@ def main():
         e2e = run_e2e(args, w)
         dense.check_status(dev)
     roof = roofline_of(per, args.steps, wl["name"])
+    per_rank = None
+    if world > 1:  # how even the partition is: every rank's share of rows, halo, sends and kernel time
+        part = w.part
+        mine = torch.tensor([part.n_local, int(part.row_ptr[-1].item()), part.fwd.n_halo,
+                             sum(part.fwd.send_splits), sum(v["ms"] for v in per.values()) / args.steps,
+                             sum(v["ms"] for k, v in per.items() if k.startswith("gnn_halo_push")) / args.steps],
+                            dtype=torch.float64, device=dev)
+        rows = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(rows, mine)
+        per_rank = [{"rows": int(r[0]), "edges": int(r[1]), "halo_rows": int(r[2]), "rows_sent": int(r[3]),
+                     "entry_points_ms": round(float(r[4]), 3), "halo_push_ms": round(float(r[5]), 3)}
+                    for r in rows]
     setup_ms = w.setup_ms
     exchange = w.exchange
     if hasattr(w.model, "close"):
@@ -853,6 +890,8 @@ def main():
             "cublas_fallback_calls": fallbacks, "roofline": roof, "cpu_baseline": cpu,
             "models": models, "gpu_reference": gpu_ref,
         }
+        if per_rank is not None:
+            line["per_rank"] = per_rank
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
