@@ -66,6 +66,8 @@ PROTOTYPES = {
                            _PTR, _PTR, _PTR],
     "gnn_edgeconv_fwd": [_INT, _PTR, _PTR, _PTR, _I64, _INT, _PTR, _PTR, _PTR],
     "gnn_edgeconv_bwd": [_PTR, _PTR, _I64, _I64, _INT, _PTR, _PTR],
+    "gnn_gmm_sum_fwd": [_PTR, _PTR, _PTR, _I64, _INT, _INT, _PTR, _PTR],
+    "gnn_gmm_sum_bwd": [_PTR, _I64, _INT, _INT, _PTR, _PTR],
     "gnn_edgeconv_fwd_act": [_INT, _PTR, _PTR, _PTR, _I64, _INT, _F32, _PTR, _PTR, _PTR],
     "gnn_edgeconv_bwd_act": [_PTR, _PTR, _F32, _PTR, _I64, _I64, _INT, _PTR, _PTR, _PTR],
     "gnn_gmm_fwd_workspace_bytes": [_I64, _INT, _INT, _SZP],
@@ -164,7 +166,7 @@ KERNELS_PER_CALL = {
     "gnn_gemm_tf32x3": 2, "gnn_gemm_tf32x3_scores": 2, "gnn_gemm_tf32x3_tn": 2,
     "gnn_gat_bwd_col_edges": 2, "gnn_gat_bwd_pack": 1, "gnn_gat_bwd_pack_elu": 1, "gnn_gat_bwd_row_sum": 2, "gnn_invert_permutation": 1,
     "gnn_gat_edge_alpha": 1, "gnn_edgeconv_fwd": 1, "gnn_edgeconv_bwd": 1, "gnn_edgeconv_fwd_act": 1,
-    "gnn_edgeconv_bwd_act": 1, "gnn_gmm_fwd": 2,
+    "gnn_edgeconv_bwd_act": 1, "gnn_gmm_fwd": 2, "gnn_gmm_sum_fwd": 1, "gnn_gmm_sum_bwd": 1,
     "gnn_gaussian_fwd": 1, "gnn_gaussian_bwd": 2, "gnn_mhspmm": 2, "gnn_mhsddmm": 1,
     "gnn_sddmm_coo": 1, "gnn_mhtranspose": 1, "gnn_u_add_v_fwd": 1, "gnn_u_add_v_bwd": 1,
     "gnn_edge_softmax_fwd": 1, "gnn_edge_softmax_bwd": 1, "gnn_knn_graph": 1, "gnn_halo_push": 1,

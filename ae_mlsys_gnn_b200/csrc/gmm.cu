@@ -215,3 +215,85 @@ extern "C" int gnn_gaussian_bwd(const float* pseudo, const float* mu, const floa
   gaussian_bwd_reduce_kernel<<<(K * 2 * D + 127) / 128, 128, 0, stream>>>(nb, K, D, partial, grad_mu, grad_inv_sigma);
   return check_launch("gnn_gaussian_bwd");
 }
+
+// ---- the layer's tail: sum over the K kernels, residual, bias (layers/gmmconv_layer.py:69-75) ----
+namespace {
+
+// One thread per VW consecutive output floats: out[n,f] = ((sum_k x[n,k,f]) + res[n,f]) + bias[f].
+template <int VW>
+__global__ void kernels_sum_fwd_kernel(int64_t total, int K, int F, const float* __restrict__ x,
+                                       const float* __restrict__ res, const float* __restrict__ bias,
+                                       float* __restrict__ out) {
+  const int64_t t = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VW;
+  if (t >= total) return;
+  const int64_t n = t / F;
+  const int f = (int)(t - n * F);
+  const float* xr = x + (size_t)n * K * F + f;
+  float acc[VW];
+#pragma unroll
+  for (int i = 0; i < VW; ++i) acc[i] = 0.f;
+  for (int k = 0; k < K; ++k) {
+    if constexpr (VW == 4) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(xr + (size_t)k * F));
+      acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+    } else {
+      acc[0] += __ldg(xr + (size_t)k * F);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VW; ++i) {
+    if (res) acc[i] += __ldg(res + t + i);
+    if (bias) acc[i] += __ldg(bias + f + i);
+  }
+  if constexpr (VW == 4) *reinterpret_cast<float4*>(out + t) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  else out[t] = acc[0];
+}
+
+// grad_x[n,k,:] = grad_out[n,:] for every k.
+template <int VW>
+__global__ void kernels_sum_bwd_kernel(int64_t total, int K, int F, const float* __restrict__ grad_out,
+                                       float* __restrict__ grad_x) {
+  const int64_t t = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VW;
+  if (t >= total) return;
+  const int64_t n = t / F;
+  const int f = (int)(t - n * F);
+  float* gx = grad_x + (size_t)n * K * F + f;
+  if constexpr (VW == 4) {
+    const float4 g = __ldg(reinterpret_cast<const float4*>(grad_out + t));
+    for (int k = 0; k < K; ++k) *reinterpret_cast<float4*>(gx + (size_t)k * F) = g;
+  } else {
+    const float g = __ldg(grad_out + t);
+    for (int k = 0; k < K; ++k) gx[(size_t)k * F] = g;
+  }
+}
+
+}  // namespace
+
+extern "C" int gnn_gmm_sum_fwd(const float* x, const float* residual, const float* bias, int64_t n,
+                               int K, int F, float* out, cudaStream_t stream) {
+  if (n < 0 || K <= 0 || F <= 0) return bad("gnn_gmm_sum_fwd: bad size");
+  if (n == 0) return GNN_OK;
+  if (!x || !out) return bad("gnn_gmm_sum_fwd: null pointer");
+  const int64_t total = n * F;
+  const bool vec = F % 4 == 0 && aligned16(x) && aligned16(out) && (!residual || aligned16(residual)) &&
+                   (!bias || aligned16(bias));
+  if (vec)
+    kernels_sum_fwd_kernel<4><<<(unsigned)((total / 4 + 255) / 256), 256, 0, stream>>>(total, K, F, x, residual, bias, out);
+  else
+    kernels_sum_fwd_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(total, K, F, x, residual, bias, out);
+  return check_launch("gnn_gmm_sum_fwd");
+}
+
+extern "C" int gnn_gmm_sum_bwd(const float* grad_out, int64_t n, int K, int F, float* grad_x,
+                               cudaStream_t stream) {
+  if (n < 0 || K <= 0 || F <= 0) return bad("gnn_gmm_sum_bwd: bad size");
+  if (n == 0) return GNN_OK;
+  if (!grad_out || !grad_x) return bad("gnn_gmm_sum_bwd: null pointer");
+  const int64_t total = n * F;
+  const bool vec = F % 4 == 0 && aligned16(grad_out) && aligned16(grad_x);
+  if (vec)
+    kernels_sum_bwd_kernel<4><<<(unsigned)((total / 4 + 255) / 256), 256, 0, stream>>>(total, K, F, grad_out, grad_x);
+  else
+    kernels_sum_bwd_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(total, K, F, grad_out, grad_x);
+  return check_launch("gnn_gmm_sum_bwd");
+}

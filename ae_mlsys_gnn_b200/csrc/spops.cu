@@ -154,45 +154,139 @@ u_add_v_fwd_kernel(ChunkGeom g, int F, const float* __restrict__ row_val,
 
 // grad_row[s,f] = sum_{e in s} g[e,f];  grad_col[c,f] = sum_{e: idx[e]=c} g[e,f]
 // (src/u_add_v/u_add_v.cu:43-78; both outputs are zero-filled first, which the
-// reference forgets for grad_col).
+// reference forgets for grad_col).  The lanes walk a piece's (edge, feature) pairs in memory
+// order, so all 32 are busy whatever F is; grad_col is scattered with atomics (the signature
+// carries no transposed graph to gather over), grad_row is summed in registers and only the
+// pieces of rows cut by a chunk boundary meet through atomics.
 __global__ void __launch_bounds__(kThreadsPerCta)
 u_add_v_bwd_kernel(ChunkGeom g, int F, const float* __restrict__ grad,
                    float* __restrict__ grad_row, float* __restrict__ grad_col) {
   const int lane = threadIdx.x & 31;
   const int chunk_id = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
   if (chunk_id >= g.num_chunks) return;
+  const bool lanes_own_feature = F <= 32 && 32 % F == 0;  // lane l always sees feature l % F
   for_each_piece(g, chunk_id, [&](int s, int a, int b, bool first, bool last) {
-    for (int f = lane; f < F; f += 32) {
-      float acc = 0.f;
-      for (int e = a; e < b; ++e) {
-        const float v = __ldg(grad + (size_t)e * F + f);
-        acc += v;
-        atomicAdd(grad_col + (size_t)__ldg(g.idx + e) * F + f, v);
+    const int64_t total = (int64_t)(b - a) * F;
+    float acc = 0.f;
+    for (int64_t t = lane; t < total; t += 32) {
+      const int e = a + (int)(t / F);
+      const int f = (int)(t % F);
+      const float v = __ldg(grad + (size_t)a * F + t);
+      acc += v;
+      atomicAdd(grad_col + (size_t)__ldg(g.idx + e) * F + f, v);
+    }
+    if (lanes_own_feature) {
+      for (int o = 16; o >= F; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane < F) {
+        if (first && last) grad_row[(size_t)s * F + lane] = acc;
+        else atomicAdd(grad_row + (size_t)s * F + lane, acc);
       }
-      if (first && last) grad_row[(size_t)s * F + f] = acc;
-      else atomicAdd(grad_row + (size_t)s * F + f, acc);
+    } else {
+      for (int f = lane; f < F; f += 32) {
+        float r = 0.f;
+        for (int e = a; e < b; ++e) r += __ldg(grad + (size_t)e * F + f);
+        if (first && last) grad_row[(size_t)s * F + f] = r;
+        else atomicAdd(grad_row + (size_t)s * F + f, r);
+      }
     }
   });
 }
 
-// CSR edge softmax over (E,H) values, one warp per segment
-// (src/edge_softmax/edge_softmax.cu:7-60 forward, :63-98 backward).
+// CSR edge softmax over (E,H) values (src/edge_softmax/edge_softmax.cu:7-60 forward, :63-98
+// backward).  One warp per segment; a segment of kHeavySegment edges or more is left to all
+// the warps of its CTA together, so a hub does not hang on 32 lanes.  When H divides 32 the
+// threads walk the segment's E x H block in memory order (thread t always sees head t % H)
+// and the per-head reductions run across the threads of equal head; other H take one head
+// at a time.
+constexpr int kHeavySegment = 2048;
+
+template <bool BLOCK, class Op>
+__device__ __forceinline__ float group_reduce(float v, int stride, Op op, float* red) {
+  // combines the values of the threads whose index is equal modulo `stride` (a power of two
+  // <= 32): inside the warp by butterflies, across the warps of the CTA through `red`
+  for (int o = 16; o >= stride; o >>= 1) v = op(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if constexpr (BLOCK) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    __syncthreads();  // the previous use of `red` is over
+    if (lane < stride) red[w * 32 + lane] = v;
+    __syncthreads();
+    v = red[lane & (stride - 1)];
+    for (int k = 1; k < kWarpsPerCta; ++k) v = op(v, red[k * 32 + (lane & (stride - 1))]);
+  }
+  return v;
+}
+
+template <bool BLOCK>
+__device__ __forceinline__ void edge_softmax_fwd_segment(int a, int b, int H, const float* __restrict__ in,
+                                                         float* __restrict__ out, float* red) {
+  const int tid = BLOCK ? threadIdx.x : (threadIdx.x & 31);
+  const int nthr = BLOCK ? kThreadsPerCta : 32;
+  auto fmax2 = [](float x, float y) { return fmaxf(x, y); };
+  auto add2 = [](float x, float y) { return x + y; };
+  if (H <= 32 && 32 % H == 0) {
+    const float* x = in + (size_t)a * H;
+    float* y = out + (size_t)a * H;
+    const int64_t total = (int64_t)(b - a) * H;
+    float m = kNegBig;
+    for (int64_t t = tid; t < total; t += nthr) m = fmaxf(m, __ldg(x + t));
+    m = group_reduce<BLOCK>(m, H, fmax2, red);
+    float sum = 0.f;
+    for (int64_t t = tid; t < total; t += nthr) sum += expf(__ldg(x + t) - m);
+    sum = group_reduce<BLOCK>(sum, H, add2, red);
+    for (int64_t t = tid; t < total; t += nthr) y[t] = expf(__ldg(x + t) - m) / sum;
+  } else {
+    for (int h = 0; h < H; ++h) {
+      float m = kNegBig;
+      for (int e = a + tid; e < b; e += nthr) m = fmaxf(m, __ldg(in + (size_t)e * H + h));
+      m = group_reduce<BLOCK>(m, 1, fmax2, red);
+      float sum = 0.f;
+      for (int e = a + tid; e < b; e += nthr) sum += expf(__ldg(in + (size_t)e * H + h) - m);
+      sum = group_reduce<BLOCK>(sum, 1, add2, red);
+      for (int e = a + tid; e < b; e += nthr)
+        out[(size_t)e * H + h] = expf(__ldg(in + (size_t)e * H + h) - m) / sum;
+    }
+  }
+}
+
+template <bool BLOCK>
+__device__ __forceinline__ void edge_softmax_bwd_segment(int a, int b, int H, const float* __restrict__ y,
+                                                         const float* __restrict__ gy, float* __restrict__ gx,
+                                                         float* red) {
+  const int tid = BLOCK ? threadIdx.x : (threadIdx.x & 31);
+  const int nthr = BLOCK ? kThreadsPerCta : 32;
+  auto add2 = [](float x, float y) { return x + y; };
+  if (H <= 32 && 32 % H == 0) {
+    const size_t off = (size_t)a * H;
+    const int64_t total = (int64_t)(b - a) * H;
+    float dot = 0.f;
+    for (int64_t t = tid; t < total; t += nthr) dot = fmaf(__ldg(y + off + t), __ldg(gy + off + t), dot);
+    dot = group_reduce<BLOCK>(dot, H, add2, red);
+    for (int64_t t = tid; t < total; t += nthr) gx[off + t] = __ldg(y + off + t) * (__ldg(gy + off + t) - dot);
+  } else {
+    for (int h = 0; h < H; ++h) {
+      float dot = 0.f;
+      for (int e = a + tid; e < b; e += nthr)
+        dot = fmaf(__ldg(y + (size_t)e * H + h), __ldg(gy + (size_t)e * H + h), dot);
+      dot = group_reduce<BLOCK>(dot, 1, add2, red);
+      for (int e = a + tid; e < b; e += nthr)
+        gx[(size_t)e * H + h] = __ldg(y + (size_t)e * H + h) * (__ldg(gy + (size_t)e * H + h) - dot);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreadsPerCta)
 edge_softmax_fwd_kernel(const int* __restrict__ ptr, int nseg, int H,
                         const float* __restrict__ in, float* __restrict__ out) {
-  const int lane = threadIdx.x & 31;
-  const int s = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
-  if (s >= nseg) return;
-  const int a = __ldg(ptr + s), b = __ldg(ptr + s + 1);
-  for (int h = 0; h < H; ++h) {
-    float m = kNegBig;
-    for (int e = a + lane; e < b; e += 32) m = fmaxf(m, __ldg(in + (size_t)e * H + h));
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int e = a + lane; e < b; e += 32) sum += expf(__ldg(in + (size_t)e * H + h) - m);
-    sum = warp_sum(sum);
-    for (int e = a + lane; e < b; e += 32)
-      out[(size_t)e * H + h] = expf(__ldg(in + (size_t)e * H + h) - m) / sum;
+  __shared__ float red[kWarpsPerCta * 32];
+  const int s0 = blockIdx.x * kWarpsPerCta;
+  const int s = s0 + (threadIdx.x >> 5);
+  if (s < nseg) {
+    const int a = __ldg(ptr + s), b = __ldg(ptr + s + 1);
+    if (b - a < kHeavySegment) edge_softmax_fwd_segment<false>(a, b, H, in, out, red);
+  }
+  for (int k = 0; k < kWarpsPerCta && s0 + k < nseg; ++k) {  // uniform over the CTA
+    const int a = __ldg(ptr + s0 + k), b = __ldg(ptr + s0 + k + 1);
+    if (b - a >= kHeavySegment) edge_softmax_fwd_segment<true>(a, b, H, in, out, red);
   }
 }
 
@@ -200,17 +294,16 @@ __global__ void __launch_bounds__(kThreadsPerCta)
 edge_softmax_bwd_kernel(const int* __restrict__ ptr, int nseg, int H,
                         const float* __restrict__ y, const float* __restrict__ gy,
                         float* __restrict__ gx) {
-  const int lane = threadIdx.x & 31;
-  const int s = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
-  if (s >= nseg) return;
-  const int a = __ldg(ptr + s), b = __ldg(ptr + s + 1);
-  for (int h = 0; h < H; ++h) {
-    float dot = 0.f;
-    for (int e = a + lane; e < b; e += 32)
-      dot = fmaf(__ldg(y + (size_t)e * H + h), __ldg(gy + (size_t)e * H + h), dot);
-    dot = warp_sum(dot);
-    for (int e = a + lane; e < b; e += 32)
-      gx[(size_t)e * H + h] = __ldg(y + (size_t)e * H + h) * (__ldg(gy + (size_t)e * H + h) - dot);
+  __shared__ float red[kWarpsPerCta * 32];
+  const int s0 = blockIdx.x * kWarpsPerCta;
+  const int s = s0 + (threadIdx.x >> 5);
+  if (s < nseg) {
+    const int a = __ldg(ptr + s), b = __ldg(ptr + s + 1);
+    if (b - a < kHeavySegment) edge_softmax_bwd_segment<false>(a, b, H, y, gy, gx, red);
+  }
+  for (int k = 0; k < kWarpsPerCta && s0 + k < nseg; ++k) {
+    const int a = __ldg(ptr + s0 + k), b = __ldg(ptr + s0 + k + 1);
+    if (b - a >= kHeavySegment) edge_softmax_bwd_segment<true>(a, b, H, y, gy, gx, red);
   }
 }
 

@@ -39,7 +39,9 @@ class GAT(nn.Module):
         h = inputs
         for layer in self.gat_layers[:-1]:
             h = layer(row_ptr, col_ind, col_ptr, row_ind, h, save_memory).flatten(1)
-        return self.gat_layers[-1](row_ptr, col_ind, col_ptr, row_ind, h, save_memory).mean(1)
+        out = self.gat_layers[-1](row_ptr, col_ind, col_ptr, row_ind, h, save_memory)
+        # the mean over one output head is the head itself: a view, not a pass over N x F
+        return out.squeeze(1) if out.shape[1] == 1 else out.mean(1)
 
 
 class DGCNN(nn.Module):

@@ -139,6 +139,54 @@ class GaussianFunction(torch.autograd.Function):
         return gaussian_bp(pseudo, mu, sigma, grad_out.contiguous())
 
 
+class KernelSumFunction(torch.autograd.Function):
+    """out = x.sum(1) (+ residual) (+ bias) in one pass (gnn_gmm_sum_fwd); the backward of x is
+    one broadcast store (gnn_gmm_sum_bwd)."""
+
+    @staticmethod
+    def forward(ctx, x, residual, bias):
+        x = x.contiguous()
+        capi.require(x, F32, "x", 3)
+        dev = x.device
+        n, K, F = x.shape
+        if residual is not None:
+            residual = residual.contiguous()
+            capi.require(residual, F32, "residual", 2, dev)
+            if residual.shape != (n, F):
+                raise ValueError("residual must be (n, F)")
+        if bias is not None:
+            bias = bias.contiguous()
+            capi.require(bias, F32, "bias", 1, dev)
+            if bias.shape != (F,):
+                raise ValueError("bias must be (F,)")
+        out = torch.empty((n, F), dtype=F32, device=dev)
+        with torch.cuda.device(dev):
+            capi.call("gnn_gmm_sum_fwd", capi.ptr(x), capi.ptr(residual), capi.ptr(bias), n, K, F,
+                      capi.ptr(out), capi.stream_ptr(dev))
+        ctx.shape = (n, K, F)
+        ctx.has = (residual is not None, bias is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        grad_out = grad_out.contiguous()
+        n, K, F = ctx.shape
+        grad_x = None
+        if ctx.needs_input_grad[0]:
+            grad_x = torch.empty((n, K, F), dtype=F32, device=grad_out.device)
+            with torch.cuda.device(grad_out.device):
+                capi.call("gnn_gmm_sum_bwd", capi.ptr(grad_out), n, K, F, capi.ptr(grad_x),
+                          capi.stream_ptr(grad_out.device))
+        grad_res = grad_out if ctx.has[0] and ctx.needs_input_grad[1] else None
+        grad_bias = grad_out.sum(0) if ctx.has[1] and ctx.needs_input_grad[2] else None
+        return grad_x, grad_res, grad_bias
+
+
+def kernel_sum(x, residual=None, bias=None):
+    """(n,K,F) -> (n,F): the sum over the K mixture kernels plus the optional residual and bias."""
+    return KernelSumFunction.apply(x, residual, bias)
+
+
 def GmmConvFuse(rowptr, colind, colptr, rowind, permute, node_feat, pseudo, mu, sigma):
     return GmmFuseFunction.apply(rowptr, colind, colptr, rowind, permute, node_feat, pseudo, mu, sigma)
 
@@ -155,5 +203,5 @@ def GaussianCp(pseudo, mu, sigma):
     return GaussianFunction.apply(pseudo, mu, sigma)
 
 
-__all__ = ["GmmConvFuse", "GmmConvFuseEb", "GmmConvStash", "GaussianCp", "gmmconv", "gaussian",
+__all__ = ["kernel_sum", "GmmConvFuse", "GmmConvFuseEb", "GmmConvStash", "GaussianCp", "gmmconv", "gaussian",
            "gaussian_bp", "mhtranspose_forward"]

@@ -268,6 +268,16 @@ int gnn_gmm_fwd(const int* ptr, const int* idx, int64_t n_seg, int64_t nnz,
                 const float* inv_sigma /*[K,D]*/, int K, int D, int F,
                 float* out /*[n_seg,K,F]*/, void* workspace, size_t workspace_bytes,
                 cudaStream_t stream);
+/* The tail of the GMMConv layer as one pass (layers/gmmconv_layer.py:69-75, where it is a
+ * framework sum over the kernel axis plus up to two additions):
+ *   out[n,f] = sum_k x[n,k,f] + residual[n,f] + bias[f]      (residual, bias: NULL = absent)
+ * and its backward for x, grad_x[n,k,:] = grad_out[n,:] (the gradients of residual and bias
+ * are grad_out itself and its column sum, left to the caller). */
+int gnn_gmm_sum_fwd(const float* x /*[n,K,F]*/, const float* residual /*[n,F] or NULL*/,
+                    const float* bias /*[F] or NULL*/, int64_t n, int K, int F,
+                    float* out /*[n,F]*/, cudaStream_t stream);
+int gnn_gmm_sum_bwd(const float* grad_out /*[n,F]*/, int64_t n, int K, int F,
+                    float* grad_x /*[n,K,F]*/, cudaStream_t stream);
 /* gmm.Gaussian (gmmconv.cu:34-46,186-199). */
 int gnn_gaussian_fwd(const float* pseudo, const float* mu, const float* inv_sigma, int64_t E,
                      int K, int D, float* out /*[E,K]*/, cudaStream_t stream);

@@ -92,3 +92,36 @@ def test_gmm_layer(cuda):
     eo = ref.gmm_forward(g.row_ptr, g.col_ind, nf, pseudo, w["mu"], w["inv_sigma"]).sum(1)
     eo = eo + x.double() @ w["res_fc.weight"].T + w["bias"]
     assert_close(out, eo, "GMMConv layer")
+
+
+@pytest.mark.parametrize("n,K,F", [(300, 3, 16), (257, 2, 7), (64, 8, 64), (1, 1, 3), (0, 3, 16)])
+@pytest.mark.parametrize("with_res,with_bias", [(True, True), (False, True), (True, False), (False, False)])
+def test_kernel_sum(cuda, n, K, F, with_res, with_bias):
+    """The layer's tail (sum over kernels + residual + bias) and its gradients against torch."""
+    from ae_mlsys_gnn_b200.operators.fused_gmmconv import kernel_sum
+
+    gen = torch.Generator().manual_seed(n * 31 + K)
+    x = torch.randn(n, K, F, generator=gen)
+    res = torch.randn(n, F, generator=gen) if with_res else None
+    bias = torch.randn(F, generator=gen) if with_bias else None
+    gout = torch.randn(n, F, generator=gen)
+
+    def run(dev, dtype):
+        leaves = [t.to(dev, dtype).requires_grad_(True) if t is not None else None for t in (x, res, bias)]
+        if dev == "cpu":
+            out = leaves[0].sum(1)
+            if leaves[1] is not None:
+                out = out + leaves[1]
+            if leaves[2] is not None:
+                out = out + leaves[2]
+        else:
+            out = kernel_sum(*leaves)
+        out.backward(gout.to(dev, dtype))
+        return out, [t.grad if t is not None else None for t in leaves]
+
+    out, grads = run(cuda, torch.float32)
+    eo, egrads = run("cpu", torch.float64)
+    assert_close(out, eo, "kernel_sum")
+    for name, a, b in zip(("x", "residual", "bias"), grads, egrads):
+        if b is not None:
+            assert_close(a, b, f"grad {name}", scale_atol=True)

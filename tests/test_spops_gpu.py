@@ -33,8 +33,33 @@ def test_edge_softmax(cuda, name, H):
     assert_close(hd.grad, hr.grad, "edge_softmax grad", scale_atol=True)
 
 
+@pytest.mark.parametrize("H", [1, 4, 3, 8])
+def test_edge_softmax_heavy_segments(cuda, H):
+    """Segments long enough for the whole-CTA path (two in one CTA's group of rows, one at the
+    very end), next to short ones; two runs are bit-identical."""
+    from ae_mlsys_gnn_b200.operators.edge_softmax import csr_edge_softmax
+    from tests.util import graph_from_degrees
+
+    g = graph_from_degrees([3] * 10 + [5000] + [2] * 3 + [2048] + [7] * 20 + [0, 2047, 2500], n_cols=6000, seed=8)
+    gen = torch.Generator().manual_seed(3)
+    h = torch.randn(g.nnz, H, generator=gen) * 3
+    gout = torch.randn(g.nnz, H, generator=gen)
+    hd = h.to(cuda).requires_grad_(True)
+    out = csr_edge_softmax(g.row_ptr.to(cuda), hd)
+    out.backward(gout.to(cuda))
+    hr = h.double().requires_grad_(True)
+    eo = ref.edge_softmax(g.row_ptr, hr)
+    eo.backward(gout.double())
+    assert_close(out, eo, "edge_softmax")
+    assert_close(hd.grad, hr.grad, "edge_softmax grad", scale_atol=True)
+    hd2 = h.to(cuda).requires_grad_(True)
+    out2 = csr_edge_softmax(g.row_ptr.to(cuda), hd2)
+    out2.backward(gout.to(cuda))
+    assert torch.equal(out, out2) and torch.equal(hd.grad, hd2.grad)
+
+
 @pytest.mark.parametrize("name", ["tiny", "empty_rows", "hub", "random_200"])
-@pytest.mark.parametrize("F", [1, 4, 33])
+@pytest.mark.parametrize("F", [1, 4, 33, 32, 8])
 def test_u_add_v(cuda, name, F):
     from ae_mlsys_gnn_b200.operators.u_add_v import u_add_v_op
 
