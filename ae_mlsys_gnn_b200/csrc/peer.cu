@@ -51,31 +51,38 @@ struct PushParams {
   int64_t n_own;
   int64_t row_floats;
   int world;
+  int n_groups;             // destination ranks with rows to receive
+  int group[kMaxPeers];     // their ranks
+  int64_t group_max;        // rows of the largest group
 };
 
 // One thread per 16-byte unit (VEC) or per float; consecutive threads take consecutive units
-// of a row, so a warp writes 512 contiguous bytes of the destination.
+// of a row, so a warp writes 512 contiguous bytes of the destination.  The rows are visited in
+// slots that cycle through the destination ranks (slot s: rank group[s % n_groups], its row
+// s / n_groups), so at every moment a sender's stores are spread over all its receivers and
+// no receiver has all the senders of the node storing into it at once; a slot past the end
+// of a shorter group is skipped.  The rank's own rows follow.
 template <bool VEC>
 __global__ void __launch_bounds__(256)
 halo_push_kernel(PushParams p) {
   const int64_t upr = VEC ? p.row_floats / 4 : p.row_floats;  // units per row
-  const int64_t n_send = p.send_off[p.world];
-  const int64_t total = (n_send + p.n_own) * upr;
+  const int64_t n_slots = p.group_max * p.n_groups;
+  const int64_t total = (n_slots + p.n_own) * upr;
   for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < total;
        u += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = u / upr;
-    const int64_t col = u - row * upr;
+    const int64_t slot = u / upr;
+    const int64_t col = u - slot * upr;
     const float* src;
     float* dst;
-    if (row < n_send) {
-      int q = 0;
-#pragma unroll
-      for (int k = 1; k < kMaxPeers; ++k)
-        if (k < p.world && row >= p.send_off[k]) q = k;
-      src = p.x + (size_t)__ldg(p.send_idx + row) * p.row_floats;
-      dst = p.dst[q] + (size_t)(row - p.send_off[q]) * p.row_floats;
+    if (slot < n_slots) {
+      const int64_t i = slot / p.n_groups;
+      const int q = p.group[(int)(slot - i * p.n_groups)];
+      const int64_t beg = p.send_off[q];
+      if (i >= p.send_off[q + 1] - beg) continue;
+      src = p.x + (size_t)__ldg(p.send_idx + beg + i) * p.row_floats;
+      dst = p.dst[q] + (size_t)i * p.row_floats;
     } else {
-      const int64_t r = row - n_send;
+      const int64_t r = slot - n_slots;
       src = p.x + (size_t)r * p.row_floats;
       dst = p.own_dst + (size_t)r * p.row_floats;
     }
@@ -150,7 +157,18 @@ extern "C" int gnn_halo_push(const float* x, int64_t row_floats, const int* send
   const int64_t n_send = send_off[world];
   if (n_send > 0 && (!send_idx || !x)) return bad("gnn_halo_push: null pointer");
   if (p.n_own > 0 && !x) return bad("gnn_halo_push: null pointer");
-  const int64_t units = (n_send + p.n_own) * (vec ? row_floats / 4 : row_floats);
+  p.n_groups = 0;
+  p.group_max = 0;
+  for (int q = 0; q < kMaxPeers; ++q) p.group[q] = 0;
+  for (int q = 0; q < world; ++q) {
+    const int64_t cnt = send_off[q + 1] - send_off[q];
+    if (cnt > 0) {
+      p.group[p.n_groups++] = q;
+      if (cnt > p.group_max) p.group_max = cnt;
+    }
+  }
+  if (p.n_groups == 0) p.n_groups = 1;  // no rows to send: zero slots, the divisor stays valid
+  const int64_t units = (p.group_max * p.n_groups + p.n_own) * (vec ? row_floats / 4 : row_floats);
   if (units == 0) return GNN_OK;
   int64_t blocks = (units + 255) / 256;
   const int64_t cap = 148LL * 8 * 4;  // grid-stride beyond a few waves
