@@ -467,14 +467,16 @@ class HaloGATConv(_GATBase):
             with torch.no_grad():
                 (x_ext,) = exch.exchange((self.key, "fwd_x"), [feat.detach()], part.fwd, n)
             h_ext = feat.new_empty((x_ext.shape[0], H, Fo))
-            h = dense.project(feat, self.W, out=dense.OutRows(h_ext, 0)).view(-1, H, Fo)
+            with dense.side_weight_grads(part.world > 1):  # X^T G fills the next exchange of the backward
+                h = dense.project(feat, self.W, out=dense.OutRows(h_ext, 0)).view(-1, H, Fo)
             if x_ext.shape[0] > n:
                 with torch.no_grad():
                     dense.project(x_ext[n:], self.W.detach(), out=dense.OutRows(h_ext, n))
             ac_ext = None  # only the scores of the halo are still to be exchanged
         else:
             h_ext, ac_ext = exch.open((self.key, "fwd"), [(H, Fo), (H,)], part.fwd, n, feat.device)
-            h = dense.project(feat, self.W, out=dense.OutRows(h_ext, 0)).view(-1, H, Fo)
+            with dense.side_weight_grads(part.world > 1):
+                h = dense.project(feat, self.W, out=dense.OutRows(h_ext, 0)).view(-1, H, Fo)
         return HaloGATFunction.apply(h, self.attn_l, self.attn_r, part, self.negative_slope,
                                      self.kernels, exch, self.key, self.activation, h_ext, ac_ext)
 

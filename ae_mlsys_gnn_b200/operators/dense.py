@@ -27,6 +27,47 @@ _status: dict[int, torch.Tensor] = {}
 _fallbacks = {"calls": 0}
 
 
+# ---- weight gradients off the critical path -------------------------------------------------
+# The weight gradient of a projection (X^T G) is needed only when the optimizer runs, while
+# grad_x is what the rest of the backward pass waits for.  Inside ``side_weight_grads()`` the
+# projections record that their weight-gradient GEMM may run on a second stream: the backward
+# then enqueues it there, after grad_x, and the stream that ran the backward waits for all of
+# them when the backward pass ends (an engine callback), so callers see ordinary semantics.
+# Used by the partitioned model, where the GEMM fills the time in which the next layer's halo
+# exchange keeps the SMs nearly idle.
+_side = {"on": False, "streams": {}, "pending": [], "queued": False}
+
+
+class side_weight_grads:
+    def __init__(self, on: bool = True):
+        self.on = on
+
+    def __enter__(self):
+        self.prev = _side["on"]
+        _side["on"] = self.on
+        return self
+
+    def __exit__(self, *exc):
+        _side["on"] = self.prev
+
+
+def _side_stream(dev: torch.device) -> "torch.cuda.Stream":
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    st = _side["streams"].get(idx)
+    if st is None:
+        st = torch.cuda.Stream(device=dev)
+        _side["streams"][idx] = st
+    return st
+
+
+def join_weight_grads() -> None:
+    """The current stream waits for every weight-gradient GEMM enqueued on the second stream."""
+    _side["queued"] = False
+    pending, _side["pending"] = _side["pending"], []
+    for dev, ev in pending:
+        torch.cuda.current_stream(dev).wait_event(ev)
+
+
 def fallback_calls() -> int:
     """Dense products that went to the framework GEMM instead of the tensor-core kernel so far."""
     return _fallbacks["calls"]
@@ -161,6 +202,7 @@ class _MatmulFunction(torch.autograd.Function):
         w = w.contiguous()
         ctx.save_for_backward(x, w)
         ctx.w_is_out_by_in = w_is_out_by_in
+        ctx.side = _side["on"] and x.is_cuda
         return gemm_any_k(x, w, w_is_out_by_in, out)
 
     @staticmethod
@@ -177,11 +219,29 @@ class _MatmulFunction(torch.autograd.Function):
                 _note_fallback()
                 gx = g @ (w if ctx.w_is_out_by_in else w.t())
         if ctx.needs_input_grad[1]:
-            if enabled and x.shape[0] >= TN_MIN_ROWS and x.data_ptr() % 16 == 0 and g.data_ptr() % 16 == 0:
-                gw = gemm_tn(g, x) if ctx.w_is_out_by_in else gemm_tn(x, g)
-            else:
+            def weight_grad():
+                if enabled and x.shape[0] >= TN_MIN_ROWS and x.data_ptr() % 16 == 0 and g.data_ptr() % 16 == 0:
+                    return gemm_tn(g, x) if ctx.w_is_out_by_in else gemm_tn(x, g)
                 _note_fallback()
-                gw = (g.t() @ x) if ctx.w_is_out_by_in else (x.t() @ g)
+                return (g.t() @ x) if ctx.w_is_out_by_in else (x.t() @ g)
+
+            if ctx.side:
+                dev = g.device
+                main, side = torch.cuda.current_stream(dev), _side_stream(dev)
+                side.wait_stream(main)  # x, g (and grad_x, enqueued first) are in stream order before it
+                with torch.cuda.stream(side):
+                    gw = weight_grad()
+                    ev = torch.cuda.Event()
+                    ev.record(side)
+                x.record_stream(side)
+                g.record_stream(side)
+                gw.record_stream(main)
+                _side["pending"].append((dev, ev))
+                if not _side["queued"]:  # once per backward pass: join when the pass ends
+                    _side["queued"] = True
+                    torch.autograd.Variable._execution_engine.queue_callback(join_weight_grads)
+            else:
+                gw = weight_grad()
         return gx, gw, None, None
 
 

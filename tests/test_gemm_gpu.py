@@ -151,3 +151,32 @@ def test_gemm_scores_epilogue(cuda, M, K, H, F):
     h = out.double().view(M, H, F)
     assert_close(sl, (h * al.double()).sum(-1), "score_l", scale_atol=True)
     assert_close(sr, (h * ar.double()).sum(-1), "score_r", scale_atol=True)
+
+
+def test_weight_gradient_on_second_stream(cuda):
+    """Two stacked projections whose weight-gradient GEMMs run on the second stream: the
+    gradients read right after backward() (no explicit synchronisation by the caller) equal
+    those of the in-order path bit for bit, over several passes that recycle the memory."""
+    from ae_mlsys_gnn_b200.operators import dense
+
+    gen = torch.Generator().manual_seed(11)
+    x = torch.randn(20000, 96, generator=gen).to(cuda)
+    w1 = torch.randn(96, 256, generator=gen).to(cuda)
+    w2 = torch.randn(256, 64, generator=gen).to(cuda)
+    g = torch.randn(20000, 64, generator=gen).to(cuda)
+
+    def grads(side):
+        a, b = w1.clone().requires_grad_(True), w2.clone().requires_grad_(True)
+        xi = x.clone().requires_grad_(True)
+        with dense.side_weight_grads(side):
+            y = dense.project(torch.tanh(dense.project(xi, a)), b)
+        y.backward(g)
+        return a.grad.clone(), b.grad.clone(), xi.grad.clone()
+
+    ref = grads(False)
+    for _ in range(4):
+        got = grads(True)
+        for r, t in zip(ref, got):
+            assert torch.equal(r, t)
+    dense.check_status()
+    assert_close(ref[1], (torch.tanh(x.double() @ w1.double())).t() @ g.double(), "grad_w2", scale_atol=True)
