@@ -107,6 +107,7 @@ PROTOTYPES = {
     "gnn_peer_open": [_PTR, C.POINTER(C.c_void_p)],
     "gnn_peer_close": [_PTR],
     "gnn_halo_push": [_PTR, _I64, _PTR, _PTR, _PTR, _INT, _PTR, _I64, _PTR],
+    "gnn_halo_push_ranges": [_PTR, _I64, _PTR, _PTR, _PTR, _PTR, _INT, _PTR, _I64, _PTR],
 }
 _RESTYPES = {"gnn_last_error_string": C.c_char_p}
 
@@ -169,7 +170,7 @@ KERNELS_PER_CALL = {
     "gnn_edgeconv_bwd_act": 1, "gnn_gmm_fwd": 2, "gnn_gmm_sum_fwd": 1, "gnn_gmm_sum_bwd": 1,
     "gnn_gaussian_fwd": 1, "gnn_gaussian_bwd": 2, "gnn_mhspmm": 2, "gnn_mhsddmm": 1,
     "gnn_sddmm_coo": 1, "gnn_mhtranspose": 1, "gnn_u_add_v_fwd": 1, "gnn_u_add_v_bwd": 1,
-    "gnn_edge_softmax_fwd": 1, "gnn_edge_softmax_bwd": 1, "gnn_knn_graph": 1, "gnn_halo_push": 1,
+    "gnn_edge_softmax_fwd": 1, "gnn_edge_softmax_bwd": 1, "gnn_knn_graph": 1, "gnn_halo_push": 1, "gnn_halo_push_ranges": 1,
 }
 
 

@@ -44,8 +44,9 @@ int cuda_fail(const char* what, cudaError_t e) {
 
 struct PushParams {
   const float* x;           // [*, row_floats] local per-node tensor
-  const int* send_idx;      // [send_off[world]] local row ids, grouped by destination rank
-  int64_t send_off[kMaxPeers + 1];
+  const int* send_idx;      // local row ids, grouped by destination rank
+  int64_t send_beg[kMaxPeers];  // rank q's rows are send_idx[send_beg[q] .. send_beg[q] + send_cnt[q])
+  int64_t send_cnt[kMaxPeers];
   float* dst[kMaxPeers];    // receiver q's buffer, already advanced to where this rank's rows go
   float* own_dst;           // this rank's own buffer (rows 0..n_own-1), may be null
   int64_t n_own;
@@ -77,9 +78,8 @@ halo_push_kernel(PushParams p) {
     if (slot < n_slots) {
       const int64_t i = slot / p.n_groups;
       const int q = p.group[(int)(slot - i * p.n_groups)];
-      const int64_t beg = p.send_off[q];
-      if (i >= p.send_off[q + 1] - beg) continue;
-      src = p.x + (size_t)__ldg(p.send_idx + beg + i) * p.row_floats;
+      if (i >= p.send_cnt[q]) continue;
+      src = p.x + (size_t)__ldg(p.send_idx + p.send_beg[q] + i) * p.row_floats;
       dst = p.dst[q] + (size_t)i * p.row_floats;
     } else {
       const int64_t r = slot - n_slots;
@@ -136,37 +136,35 @@ extern "C" int gnn_peer_close(void* ptr) {
   return e == cudaSuccess ? GNN_OK : cuda_fail("gnn_peer_close", e);
 }
 
-extern "C" int gnn_halo_push(const float* x, int64_t row_floats, const int* send_idx, const int64_t* send_off,
-                             float* const* dst, int world, float* own_dst, int64_t n_own, cudaStream_t stream) {
+extern "C" int gnn_halo_push_ranges(const float* x, int64_t row_floats, const int* send_idx,
+                                    const int64_t* send_beg, const int64_t* send_cnt, float* const* dst,
+                                    int world, float* own_dst, int64_t n_own, cudaStream_t stream) {
   if (world < 1 || world > kMaxPeers) return bad("gnn_halo_push: world must be in [1, GNN_MAX_PEERS]");
-  if (row_floats <= 0 || n_own < 0 || !send_off || !dst) return bad("gnn_halo_push: bad argument");
+  if (row_floats <= 0 || n_own < 0 || !send_beg || !send_cnt || !dst) return bad("gnn_halo_push: bad argument");
   PushParams p;
   p.x = x; p.send_idx = send_idx; p.own_dst = own_dst; p.n_own = own_dst ? n_own : 0;
   p.row_floats = row_floats; p.world = world;
   bool vec = row_floats % 4 == 0 && aligned16(x) && (!own_dst || aligned16(own_dst));
-  for (int q = 0; q <= kMaxPeers; ++q) p.send_off[q] = send_off[q < world ? q : world];
-  for (int q = 0; q < kMaxPeers; ++q) {
-    p.dst[q] = q < world ? dst[q] : nullptr;
-    if (q < world) {
-      const int64_t cnt = send_off[q + 1] - send_off[q];
-      if (cnt < 0) return bad("gnn_halo_push: send_off must ascend");
-      if (cnt > 0 && !dst[q]) return bad("gnn_halo_push: rows for a rank without a destination pointer");
-      if (cnt > 0 && !aligned16(dst[q])) vec = false;
-    }
-  }
-  const int64_t n_send = send_off[world];
-  if (n_send > 0 && (!send_idx || !x)) return bad("gnn_halo_push: null pointer");
-  if (p.n_own > 0 && !x) return bad("gnn_halo_push: null pointer");
   p.n_groups = 0;
   p.group_max = 0;
-  for (int q = 0; q < kMaxPeers; ++q) p.group[q] = 0;
-  for (int q = 0; q < world; ++q) {
-    const int64_t cnt = send_off[q + 1] - send_off[q];
-    if (cnt > 0) {
-      p.group[p.n_groups++] = q;
-      if (cnt > p.group_max) p.group_max = cnt;
-    }
+  int64_t n_send = 0;
+  for (int q = 0; q < kMaxPeers; ++q) {
+    p.group[q] = 0;
+    p.dst[q] = q < world ? dst[q] : nullptr;
+    p.send_beg[q] = q < world ? send_beg[q] : 0;
+    p.send_cnt[q] = q < world ? send_cnt[q] : 0;
+    if (q >= world) continue;
+    const int64_t cnt = send_cnt[q];
+    if (cnt < 0 || send_beg[q] < 0) return bad("gnn_halo_push: negative range");
+    if (cnt == 0) continue;
+    if (!dst[q]) return bad("gnn_halo_push: rows for a rank without a destination pointer");
+    if (!aligned16(dst[q])) vec = false;
+    p.group[p.n_groups++] = q;
+    if (cnt > p.group_max) p.group_max = cnt;
+    n_send += cnt;
   }
+  if (n_send > 0 && (!send_idx || !x)) return bad("gnn_halo_push: null pointer");
+  if (p.n_own > 0 && !x) return bad("gnn_halo_push: null pointer");
   if (p.n_groups == 0) p.n_groups = 1;  // no rows to send: zero slots, the divisor stays valid
   const int64_t units = (p.group_max * p.n_groups + p.n_own) * (vec ? row_floats / 4 : row_floats);
   if (units == 0) return GNN_OK;
@@ -176,4 +174,17 @@ extern "C" int gnn_halo_push(const float* x, int64_t row_floats, const int* send
   if (vec) halo_push_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(p);
   else halo_push_kernel<false><<<(unsigned)blocks, 256, 0, stream>>>(p);
   return check_launch("gnn_halo_push");
+}
+
+extern "C" int gnn_halo_push(const float* x, int64_t row_floats, const int* send_idx, const int64_t* send_off,
+                             float* const* dst, int world, float* own_dst, int64_t n_own, cudaStream_t stream) {
+  if (world < 1 || world > kMaxPeers) return bad("gnn_halo_push: world must be in [1, GNN_MAX_PEERS]");
+  if (!send_off) return bad("gnn_halo_push: bad argument");
+  int64_t beg[kMaxPeers], cnt[kMaxPeers];
+  for (int q = 0; q < world; ++q) {
+    beg[q] = send_off[q];
+    cnt[q] = send_off[q + 1] - send_off[q];
+    if (cnt[q] < 0) return bad("gnn_halo_push: send_off must ascend");
+  }
+  return gnn_halo_push_ranges(x, row_floats, send_idx, beg, cnt, dst, world, own_dst, n_own, stream);
 }

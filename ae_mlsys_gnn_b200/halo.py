@@ -33,6 +33,7 @@ from __future__ import annotations
 
 import dataclasses
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -61,10 +62,32 @@ class ExchangePlan:
     # graph, so all ranks agree on whether the collective of this plan is issued at all: a rank
     # with nothing to send or receive itself (an empty block, only isolated nodes) still joins.
     active: bool = True
+    # host copy of send_idx and the ranges already looked up in it (for pushing a row block early)
+    send_host: object = None
+    range_cache: dict = dataclasses.field(default_factory=dict)
 
     @property
     def n_halo(self) -> int:
         return int(sum(self.recv_splits))
+
+    def ranges(self, lo: int, hi: int):
+        """For every destination rank q, (begin, count) of the part of its group of ``send_idx`` whose
+        rows lie in [lo, hi) -- the groups are ascending, so the part is contiguous."""
+        got = self.range_cache.get((lo, hi))
+        if got is None:
+            import numpy as np
+
+            if self.send_host is None:
+                self.send_host = self.send_idx.detach().cpu().numpy()
+            begs, cnts, pos = [], [], 0
+            for c in self.send_splits:
+                grp = self.send_host[pos: pos + c]
+                a, b = int(np.searchsorted(grp, lo, "left")), int(np.searchsorted(grp, hi, "left"))
+                begs.append(pos + a)
+                cnts.append(b - a)
+                pos += c
+            got = self.range_cache[(lo, hi)] = (begs, cnts)
+        return got
 
 
 @dataclass
@@ -297,7 +320,9 @@ class PeerStoreExchange(NcclExchange):
         self.n_locals = [part.bounds[q + 1] - part.bounds[q] for q in range(part.world)]
         self._slots = {}   # key -> [buffers of use 0, buffers of use 1, next use]
         self._open = {}    # key -> buffers handed out by the last open()
+        self._early = {}   # key -> indices of the tensors whose rows push_rows() has already moved
         self._flag = None
+        self._side = None
 
     # -- overridable pieces (a CPU stand-in for tests replaces them) -------------------------
     def _alloc(self, nbytes, device):
@@ -315,6 +340,26 @@ class PeerStoreExchange(NcclExchange):
         dst = [0 if q == self.rank or plan.send_splits[q] == 0
                else buf.ptrs[q] + (self.n_locals[q] + plan.dst_off[q]) * row_bytes for q in range(self.world)]
         halo_push(ext, plan.send_idx32, offs, dst, 0, 0)
+
+    def _push_rows(self, ext, plan, buf, row_bytes, lo, hi):
+        """The part of ``_push`` whose rows lie in [lo, hi)."""
+        from .peer import halo_push_ranges
+
+        begs, cnts = plan.ranges(lo, hi)
+        pos, dst = 0, []
+        for q, c in enumerate(plan.send_splits):
+            dst.append(0 if cnts[q] == 0 else
+                       buf.ptrs[q] + (self.n_locals[q] + plan.dst_off[q] + begs[q] - pos) * row_bytes)
+            pos += c
+        halo_push_ranges(ext, plan.send_idx32, begs, cnts, dst)
+
+    def _side_stream(self, device):
+        """(main, side) streams for pushes that overlap their producer; (None, None) where streams do not apply."""
+        if torch.device(device).type != "cuda":
+            return None, None
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=device)
+        return torch.cuda.current_stream(device), self._side
 
     def _complete(self, device):
         """Every rank's push kernels are complete before anything enqueued after this call runs."""
@@ -341,12 +386,35 @@ class PeerStoreExchange(NcclExchange):
         rows = n_local + plan.n_halo
         return [buf.view((rows,) + tuple(t), torch.float32) for buf, t in zip(bufs, tails)]
 
+    def push_rows(self, key, i: int, ext, plan: ExchangePlan, lo: int, hi: int):
+        """Moves the rows [lo, hi) of tensor ``i`` of the exchange point now, on a second stream that
+        waits for what the caller has enqueued so far: a producer that fills the tensor block by block
+        (a GEMM over row blocks) overlaps the transfer of one block with the computation of the next.
+        Every row of the tensor must be covered by such calls before ``push``, which then skips it."""
+        if not plan.active:
+            return
+        bufs, row_bytes = self._open[key]
+        main, side = self._side_stream(ext.device)
+        if side is not None:
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                self._push_rows(ext, plan, bufs[i], row_bytes[i], lo, hi)
+        else:
+            self._push_rows(ext, plan, bufs[i], row_bytes[i], lo, hi)
+        self._early.setdefault(key, set()).add(i)
+
     def push(self, key, exts, plan: ExchangePlan, n_local: int):
         if not plan.active:
             return
         bufs, row_bytes = self._open.pop(key)
-        for ext, buf, rb in zip(exts, bufs, row_bytes):
-            self._push(ext, plan, buf, rb, n_local)
+        early = self._early.pop(key, ())
+        for i, (ext, buf, rb) in enumerate(zip(exts, bufs, row_bytes)):
+            if i not in early:
+                self._push(ext, plan, buf, rb, n_local)
+        if early:
+            main, side = self._side_stream(exts[0].device)
+            if side is not None:
+                main.wait_stream(side)
         self._complete(exts[0].device)
 
     def close(self):
@@ -445,10 +513,14 @@ class HaloGATConv(_GATBase):
     default; e.g. 100 -> 512) the narrow inputs of the halo are exchanged and projected on the
     receiving rank instead of exchanging the wide projected rows."""
 
+    OVERLAP_MIN_ROWS = 16384  # per block: below this a block's GEMM no longer fills the GPU
+    OVERLAP_MIN_WIDTH = 128   # floats per row: narrow rows travel in no time
+
     def __init__(self, in_feats, out_feats, num_heads, negative_slope=0.2, kernels=_CudaKernels,
-                 recompute_projection="auto", activation=None, key=0):
+                 recompute_projection="auto", activation=None, key=0, overlap_blocks=4):
         super().__init__(in_feats, out_feats, num_heads, negative_slope)
         self.kernels = kernels
+        self.overlap_blocks = int(os.environ.get("GNN_B200_OVERLAP_BLOCKS", overlap_blocks))
         self.recompute_projection = recompute_projection
         self.activation = activation
         self.key = key
@@ -475,8 +547,21 @@ class HaloGATConv(_GATBase):
             ac_ext = None  # only the scores of the halo are still to be exchanged
         else:
             h_ext, ac_ext = exch.open((self.key, "fwd"), [(H, Fo), (H,)], part.fwd, n, feat.device)
+            # wide rows: the projection runs block by block and every finished block of rows starts
+            # travelling to the ranks that need it while the next block is computed
+            blocks = after = None
+            if (self.overlap_blocks > 1 and hasattr(exch, "push_rows") and part.fwd.active
+                    and n >= self.overlap_blocks * self.OVERLAP_MIN_ROWS and H * Fo >= self.OVERLAP_MIN_WIDTH):
+                step = -(-n // self.overlap_blocks)
+                step = -(-step // 128) * 128  # whole GEMM tiles
+                blocks = [(lo, min(lo + step, n)) for lo in range(0, n, step)]
+                key = (self.key, "fwd")
+
+                def after(lo, hi):
+                    exch.push_rows(key, 0, h_ext, part.fwd, lo, hi)
             with dense.side_weight_grads(part.world > 1):
-                h = dense.project(feat, self.W, out=dense.OutRows(h_ext, 0)).view(-1, H, Fo)
+                h = dense.project(feat, self.W, out=dense.OutRows(h_ext, 0), row_blocks=blocks,
+                                  after_block=after).view(-1, H, Fo)
         return HaloGATFunction.apply(h, self.attn_l, self.attn_r, part, self.negative_slope,
                                      self.kernels, exch, self.key, self.activation, h_ext, ac_ext)
 

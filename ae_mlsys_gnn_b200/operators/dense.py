@@ -197,13 +197,22 @@ TN_MIN_ROWS = 4096
 
 class _MatmulFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, w_is_out_by_in, out=None):
+    def forward(ctx, x, w, w_is_out_by_in, out=None, row_blocks=None, after_block=None):
         x = x.contiguous()
         w = w.contiguous()
         ctx.save_for_backward(x, w)
         ctx.w_is_out_by_in = w_is_out_by_in
         ctx.side = _side["on"] and x.is_cuda
-        return gemm_any_k(x, w, w_is_out_by_in, out)
+        if not row_blocks or out is None:
+            return gemm_any_k(x, w, w_is_out_by_in, out)
+        # one product per block of rows, each written to its rows of ``out``; ``after_block(lo, hi)``
+        # runs once a block is enqueued (e.g. to start moving those rows elsewhere)
+        n_out = w.shape[0] if w_is_out_by_in else w.shape[1]
+        for lo, hi in row_blocks:
+            gemm_any_k(x[lo:hi], w, w_is_out_by_in, OutRows(out.base, out.start + lo))
+            if after_block is not None:
+                after_block(lo, hi)
+        return out.rows(x.shape[0], n_out)
 
     @staticmethod
     def backward(ctx, g):
@@ -242,25 +251,30 @@ class _MatmulFunction(torch.autograd.Function):
                     torch.autograd.Variable._execution_engine.queue_callback(join_weight_grads)
             else:
                 gw = weight_grad()
-        return gx, gw, None, None
+        return gx, gw, None, None, None, None
 
 
-def matmul_tf32x3(x, w, out=None):
+def matmul_tf32x3(x, w, out=None, row_blocks=None, after_block=None):
     """x (M,K) @ w (K,N)."""
-    return _MatmulFunction.apply(x, w, False, out)
+    return _MatmulFunction.apply(x, w, False, out, row_blocks, after_block)
 
 
-def project(x, w, out: "OutRows | None" = None):
+def project(x, w, out: "OutRows | None" = None, row_blocks=None, after_block=None):
     """x @ w, on the tensor cores for CUDA fp32 matrices.  ``out``: rows of an existing buffer to
-    write the product into (the returned tensor is then that view)."""
+    write the product into (the returned tensor is then that view).  ``row_blocks`` (list of
+    (lo, hi) covering the rows, needs ``out``): the product is enqueued block by block and
+    ``after_block(lo, hi)`` is called after each, so that a consumer of finished rows (a transfer)
+    can start while the next block is computed; the backward is that of the whole product."""
     if x.dim() == 2 and supported(x.shape[0], w.shape[1], w.shape[0], x):
-        return matmul_tf32x3(x, w, out)
+        return matmul_tf32x3(x, w, out, row_blocks, after_block)
     _note_fallback()
     res = torch.matmul(x, w)
-    if out is None:
-        return res
-    dst = out.rows(res.shape[0], res.shape[1])
-    dst.copy_(res.detach())
+    if out is not None:
+        dst = out.rows(res.shape[0], res.shape[1])
+        dst.copy_(res.detach())
+    if row_blocks and after_block is not None:
+        for lo, hi in row_blocks:
+            after_block(lo, hi)
     return res
 
 

@@ -111,6 +111,26 @@ def halo_push(x: torch.Tensor, send_idx: torch.Tensor, send_off: list, dst_ptrs:
                   world, own_dst_ptr if own_dst_ptr else None, int(n_own), capi.stream_ptr(dev))
 
 
+def halo_push_ranges(x: torch.Tensor, send_idx: torch.Tensor, begs: list, cnts: list, dst_ptrs: list) -> None:
+    """``halo_push`` for part of a send list: rank q receives rows ``send_idx[begs[q] : begs[q] + cnts[q]]``
+    of ``x`` at ``dst_ptrs[q]`` onwards (the caller advances the pointer to where the range lands)."""
+    capi.require(x, torch.float32, "x")
+    dev = x.device
+    world = len(dst_ptrs)
+    row = 1
+    for s in x.shape[1:]:
+        row *= int(s)
+    if sum(int(c) for c in cnts) == 0:
+        return
+    capi.require(send_idx, torch.int32, "send_idx", 1, dev)
+    beg = (C.c_int64 * world)(*[int(v) for v in begs])
+    cnt = (C.c_int64 * world)(*[int(v) for v in cnts])
+    dst = (C.c_void_p * world)(*[C.c_void_p(int(p)) if p else C.c_void_p(None) for p in dst_ptrs])
+    with torch.cuda.device(dev):
+        capi.call("gnn_halo_push_ranges", capi.ptr(x), row, capi.ptr(send_idx), beg, cnt, dst, world, None, 0,
+                  capi.stream_ptr(dev))
+
+
 def probe(device, group=None) -> bool:
     """Whether peer-mapped buffers work between the ranks of ``group`` on this node: every rank
     stores one row into every other rank's buffer and checks what it received.  Collective; all

@@ -444,6 +444,13 @@ int gnn_peer_open(const unsigned char* handle, void** ptr);
 int gnn_peer_close(void* ptr);
 int gnn_halo_push(const float* x, int64_t row_floats, const int* send_idx, const int64_t* send_off,
                   float* const* dst, int world, float* own_dst, int64_t n_own, cudaStream_t stream);
+/* The same with an explicit range per rank, for pushing part of a send list (the rows a
+ * producer has finished so far): rank q gets rows send_idx[send_beg[q] .. send_beg[q] +
+ * send_cnt[q]) at dst[q] + j * row_floats, j counting from 0 inside the range.  send_beg,
+ * send_cnt and dst are HOST arrays of `world` entries. */
+int gnn_halo_push_ranges(const float* x, int64_t row_floats, const int* send_idx,
+                         const int64_t* send_beg, const int64_t* send_cnt, float* const* dst,
+                         int world, float* own_dst, int64_t n_own, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -180,3 +180,28 @@ def test_weight_gradient_on_second_stream(cuda):
             assert torch.equal(r, t)
     dense.check_status()
     assert_close(ref[1], (torch.tanh(x.double() @ w1.double())).t() @ g.double(), "grad_w2", scale_atol=True)
+
+
+def test_projection_by_row_blocks(cuda):
+    """The block-wise projection writes the same bits as the one-shot product, calls the hook
+    once per block in order, and keeps the gradients of the whole product."""
+    from ae_mlsys_gnn_b200.operators import dense
+
+    gen = torch.Generator().manual_seed(12)
+    M, K, N = 50000, 96, 512
+    x = torch.randn(M, K, generator=gen).to(cuda)
+    w = torch.randn(K, N, generator=gen).to(cuda)
+    g = torch.randn(M, N, generator=gen).to(cuda)
+    whole = dense.project(x, w)
+    buf = torch.zeros(M + 100, N, device=cuda)
+    seen = []
+    blocks = [(0, 16384), (16384, 32768), (32768, 49152), (49152, M)]
+    xi, wi = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    out = dense.project(xi, wi, out=dense.OutRows(buf, 0), row_blocks=blocks, after_block=lambda lo, hi: seen.append((lo, hi)))
+    assert seen == blocks
+    assert torch.equal(out, whole) and torch.equal(buf[:M], whole) and bool((buf[M:] == 0).all())
+    out.backward(g)
+    xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    dense.project(xr, wr).backward(g)
+    assert torch.equal(xi.grad, xr.grad) and torch.equal(wi.grad, wr.grad)
+    dense.check_status()

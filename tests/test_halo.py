@@ -116,20 +116,37 @@ class SharedMemoryExchange:
                         pos += cnt
                 pools[self.rank][buf.off: buf.off + n_local * row] = xf[:n_local].reshape(-1)
 
+            def _push_rows(self, x, plan, buf, row_bytes, lo, hi):
+                self.block_pushes = getattr(self, "block_pushes", 0) + 1
+                row = row_bytes // 4
+                xf = x.reshape(x.shape[0], row)
+                begs, cnts = plan.ranges(lo, hi)
+                pos = 0
+                for q, total in enumerate(plan.send_splits):
+                    if cnts[q]:
+                        start = buf.off + (self.n_locals[q] + plan.dst_off[q] + begs[q] - pos) * row
+                        rows = plan.send_idx[begs[q]: begs[q] + cnts[q]].long()
+                        assert bool(((rows >= lo) & (rows < hi)).all())
+                        pools[q][start: start + cnts[q] * row] = xf[rows].reshape(-1)
+                    pos += total
+                pools[self.rank][buf.off + lo * row: buf.off + hi * row] = xf[lo:hi].reshape(-1)
+
             def _complete(self, device):
                 dist.barrier()
 
         return _Exchange(part, group, small_group)
 
 
-def _worker(rank, world, port, results, recompute, graph="powerlaw", pools=None):
+def _worker(rank, world, port, results, recompute, graph="powerlaw", pools=None, overlap=False):
     import os
 
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from ae_mlsys_gnn_b200.halo import HaloGAT, build_halo_partition, halo_exchange, halo_return_sum
+        from ae_mlsys_gnn_b200.halo import HaloGAT, HaloGATConv, build_halo_partition, halo_exchange, halo_return_sum
 
+        if overlap:  # small blocks of rows are pushed while the projection of the next block "runs"
+            HaloGATConv.OVERLAP_MIN_ROWS, HaloGATConv.OVERLAP_MIN_WIDTH = 8, 1
         torch.manual_seed(0)
         g = _graph(graph)
         cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)
@@ -152,6 +169,8 @@ def _worker(rank, world, port, results, recompute, graph="powerlaw", pools=None)
             out = model(part, part.local_slice(x))
             loss = model.loss(part, out, part.local_slice(y))
             loss.backward()
+        if overlap and part.fwd.active and part.n_local >= 32:
+            assert model.exchanger(part).block_pushes > 0, "the block-wise push was not exercised"
         model.all_reduce_grads(world)
         total = loss.detach().clone()
         dist.all_reduce(total)
@@ -170,11 +189,12 @@ def _worker(rank, world, port, results, recompute, graph="powerlaw", pools=None)
 
 
 @pytest.mark.timeout(300)
-@pytest.mark.parametrize("world,recompute,graph,peer", [
-    (2, False, "powerlaw", False), (3, True, "powerlaw", False), (8, "auto", "powerlaw", False),
-    (4, False, "star", False),      # ranks with empty blocks still join every collective
-    (2, False, "powerlaw", True), (3, True, "powerlaw", True), (4, "auto", "star", True)])
-def test_halo_gat_matches_single(world, recompute, graph, peer):
+@pytest.mark.parametrize("world,recompute,graph,peer,overlap", [
+    (2, False, "powerlaw", False, False), (3, True, "powerlaw", False, False), (8, "auto", "powerlaw", False, False),
+    (4, False, "star", False, False),      # ranks with empty blocks still join every collective
+    (2, False, "powerlaw", True, False), (3, True, "powerlaw", True, False), (4, "auto", "star", True, False),
+    (2, False, "powerlaw", True, True), (3, False, "powerlaw", True, True), (4, False, "star", True, True)])
+def test_halo_gat_matches_single(world, recompute, graph, peer, overlap):
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
@@ -182,7 +202,7 @@ def test_halo_gat_matches_single(world, recompute, graph, peer):
     mgr = mp.Manager()
     results = mgr.dict()
     pools = [torch.zeros(1 << 20).share_memory_() for _ in range(world)] if peer else None
-    mp.spawn(_worker, args=(world, port, results, recompute, graph, pools), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, results, recompute, graph, pools, overlap), nprocs=world, join=True)
 
     g = _graph(graph)
     cp, ri, _ = ref.csr2csc(g.row_ptr, g.col_ind)

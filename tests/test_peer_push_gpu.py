@@ -35,3 +35,22 @@ def test_halo_push_rows(cuda, width, groups, with_own):
     if with_own:
         assert torch.equal(own[1:1 + n_own], x[:n_own])
     assert bool((own[0] == -7.0).all()) and bool((own[-1] == -7.0).all())
+
+
+def test_halo_push_ranges(cuda):
+    """Part of a send list per destination (what a block-wise producer pushes early): exactly the
+    rows of the ranges arrive, at the start of the given destinations."""
+    from ae_mlsys_gnn_b200.peer import halo_push_ranges
+
+    gen = torch.Generator().manual_seed(5)
+    n, width = 900, 128
+    x = torch.randn(n, width, generator=gen).to(cuda)
+    send_idx = torch.randint(0, n, (700,), generator=gen, dtype=torch.int32).to(cuda)
+    begs, cnts = [10, 0, 300, 650], [90, 0, 200, 50]
+    bufs = [torch.full((c + 2, width), -7.0, device=cuda) for c in cnts]
+    dst = [b[1:].data_ptr() if c else 0 for b, c in zip(bufs, cnts)]
+    halo_push_ranges(x, send_idx, begs, cnts, dst)
+    torch.cuda.synchronize()
+    for b, beg, c in zip(bufs, begs, cnts):
+        assert torch.equal(b[1:1 + c], x[send_idx[beg: beg + c].long()])
+        assert bool((b[0] == -7.0).all()) and bool((b[-1] == -7.0).all())
