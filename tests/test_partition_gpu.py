@@ -37,6 +37,12 @@ def _worker(rank, world, port, results, exchange="gather"):
         g, x, y = _inputs()
         g = g.to(dev)
         cp, ri, _ = csr2csc(g.row_ptr, g.col_ind)
+        blocks = exchange == "peer-blocks"  # projections by row blocks, finished blocks pushed early
+        if blocks:
+            from ae_mlsys_gnn_b200.halo import HaloGATConv
+
+            HaloGATConv.OVERLAP_MIN_ROWS, HaloGATConv.OVERLAP_MIN_WIDTH = 128, 1
+            exchange = "peer"
         if exchange in ("halo", "peer"):
             from ae_mlsys_gnn_b200.halo import HaloGAT, build_halo_partition
 
@@ -74,7 +80,7 @@ def _worker(rank, world, port, results, exchange="gather"):
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("exchange", ["gather", "halo", "peer"])
+@pytest.mark.parametrize("exchange", ["gather", "halo", "peer", "peer-blocks"])
 @pytest.mark.parametrize("world", [2, 4])
 def test_partitioned_gat_matches_single_gpu(cuda, world, exchange):
     if torch.cuda.device_count() < world:
