@@ -183,6 +183,21 @@ void launch_row(const GatBwdRowParams& p, cudaStream_t stream) {
 template <int HP, int Q, bool VEC, bool ACC, bool EDGES>
 void launch_col_main(const GatBwdColParams& p, cudaStream_t stream) {
   const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
+  if constexpr (VEC && Q >= 3 && Q <= HP) {  // the widest tiles (rows of more than 256 floats): rows in flight in shared memory
+    static const bool ring = [] {
+      const char* e = getenv("GNN_B200_COL_RING");
+      return e ? atoi(e) != 0 : true;
+    }();
+    if (ring && p.width == 128 * Q && p.F == 128) {
+      auto kernel = gat_bwd_col_kernel<HP, Q, VEC, 1, ACC, EDGES, true>;
+      static const cudaError_t attr = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                           (int)col_ring_bytes<Q>());
+      if (attr == cudaSuccess) {
+        kernel<<<blocks, kThreadsPerCta, col_ring_bytes<Q>(), stream>>>(p);
+        return;
+      }
+    }
+  }
   if constexpr (VEC) {
     if (p.width == 128 * Q) {  // every slot fully used: heads are aligned with the tile slots
       if constexpr (Q <= HP) {

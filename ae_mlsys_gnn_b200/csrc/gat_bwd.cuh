@@ -264,9 +264,29 @@ constexpr bool kColPipelined = VEC && Q <= 2;  // 128-bit tiles of at most 8 reg
 
 // (Two CTAs per SM are requested only for the pipelined narrow tiles; the widest tile gets
 // there by itself, and with the explicit limit its gather loop is scheduled into spills.)
-template <int HP, int Q, bool VEC, int HPS = 0, bool ACC = false, bool EDGES = false>
-__global__ void __launch_bounds__(kThreadsPerCta, kColPipelined<Q, VEC> ? 2 : 0)
+// RING (wide 128-bit tiles): the gathered rows travel through a ring in shared memory instead
+// of registers.  Every lane copies the 16-byte units it will read itself with cp.async
+// (groups of U rows, kColRingRows rows per warp), so rows stay in flight while earlier ones
+// are consumed, waiting costs one cp.async.wait_group, and no lane ever reads another lane's
+// copy: no barrier of any kind.  The plain loop holds a row in registers from request to use,
+// which limits a warp to U rows in flight and leaves none while it computes.
+constexpr int kColRingRows = 6;
+template <int Q>
+constexpr size_t col_ring_bytes() { return (size_t)kWarpsPerCta * kColRingRows * Q * 32 * sizeof(float4); }
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int HP, int Q, bool VEC, int HPS = 0, bool ACC = false, bool EDGES = false, bool RING = false>
+__global__ void __launch_bounds__(kThreadsPerCta, (kColPipelined<Q, VEC> || RING) ? 2 : 0)
 gat_bwd_col_kernel(GatBwdColParams p) {
+  static_assert(!RING || VEC, "the ring moves 16-byte units");
+  extern __shared__ __align__(16) unsigned char col_ring_smem[];
   static_assert(HPS == 0 || Q * HPS <= HP, "slot-aligned heads need Q * HPS <= HP");
   constexpr int VW = VEC ? 4 : 1;
   constexpr int U0 = Unroll<Q, VEC>::U;
@@ -373,6 +393,68 @@ gat_bwd_col_kernel(GatBwdColParams p) {
             process(vb, jj + U);
           }
         }
+      } else if constexpr (RING) {
+        constexpr int G = kColRingRows / U;  // groups of U rows the ring holds
+        static_assert(G >= 2 && G * U == kColRingRows, "ring rows must be a multiple of the group");
+        float4* const ring = reinterpret_cast<float4*>(col_ring_smem) + (size_t)wib * (kColRingRows * Q * 32) + lane;
+        auto issue = [&](int g) {  // rows [g*U, g*U + U) of this batch into ring slot g % G
+          if (g * U < nbr) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const float4* row = reinterpret_cast<const float4*>(p.gout + (size_t)cs[g * U + u] * p.ld_gout) + lane;
+              float4* dst = ring + ((g % G) * U + u) * (Q * 32);
+#pragma unroll
+              for (int q = 0; q < Q; ++q)
+                if (t.valid[q]) cp_async_16(dst + q * 32, row + q * 32);
+            }
+          }
+          cp_async_commit();  // (an empty group keeps the count of pending groups uniform)
+        };
+#pragma unroll
+        for (int g = 0; g < G - 1; ++g) issue(g);
+#pragma unroll 1
+        for (int g = 0; g * U < nbr; ++g) {
+          issue(g + G - 1);       // its slot was consumed in the previous iteration
+          cp_async_wait<G - 1>();  // all but the newest G-1 groups have landed: group g is there
+          const int jj = g * U;
+          float v[U][Q][VW];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+#pragma unroll
+            for (int q = 0; q < Q; ++q) {
+              float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (t.valid[q]) x = ring[((g % G) * U + u) * (Q * 32) + q * 32];
+              v[u][q][0] = x.x; v[u][q][1] = x.y; v[u][q][2] = x.z; v[u][q][3] = x.w;
+            }
+          }
+          float pv[V];
+#pragma unroll
+          for (int i = 0; i < V; ++i) pv[i] = 0.f;
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+#pragma unroll
+            for (int q = 0; q < Q; ++q) {
+              const float wq = ws[(jj + u) * HP + (HPS > 0 ? q * HPS + lane_head : t.head[q])];
+              float d = 0.f;
+#pragma unroll
+              for (int i = 0; i < VW; ++i) {
+                acc[q][i] = fmaf(wq, v[u][q][i], acc[q][i]);
+                d = fmaf(fq[q][i], v[u][q][i], d);
+              }
+              if constexpr (HPS > 0) {
+#pragma unroll
+                for (int k = 0; k < HPS; ++k) pv[u * HP + q * HPS + k] = (lane_head == k) ? d : 0.f;
+              } else {
+#pragma unroll
+                for (int h = 0; h < HP; ++h)
+                  if (t.head[q] == h) pv[u * HP + h] += d;
+              }
+            }
+          }
+          warp_multi_sum<V>(pv, lane);
+          if ((lane & (32 / V - 1)) == 0) gs[jj * HP + lane / (32 / V)] = pv[0];
+        }
+        cp_async_wait<0>();  // only empty groups can be pending here
       } else
       // (the wide tiles keep the plain loop, written out: their register allocation is at
       // the two-CTA limit and changes with the form of this loop)
