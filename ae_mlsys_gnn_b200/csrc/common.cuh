@@ -147,6 +147,25 @@ struct RowTile {
 };
 
 // ---------------------------------------------------------------------------
+// Ring of gathered rows in shared memory (wide 128-bit tiles).  Every lane copies the 16-byte
+// units of a row that it will read itself with cp.async (groups of U rows, kGatherRingRows rows
+// per warp), so rows stay in flight while earlier ones are consumed, waiting costs one
+// cp.async.wait_group, and no lane ever reads another lane's copy: no barrier of any kind.
+// A loop that holds a row in registers from request to use is limited to the rows its
+// registers can hold, and has none in flight while it computes.
+constexpr int kGatherRingRows = 6;
+template <int Q>
+constexpr size_t gather_ring_bytes() { return (size_t)kWarpsPerCta * kGatherRingRows * Q * 32 * sizeof(float4); }
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// ---------------------------------------------------------------------------
 // Edge-chunk traversal.  The nnz positions of a segment array (CSR rows or CSC
 // columns) are cut into chunks of `chunk` consecutive positions, one warp per
 // chunk, so every warp moves the same number of gathered rows whatever the

@@ -191,9 +191,9 @@ void launch_col_main(const GatBwdColParams& p, cudaStream_t stream) {
     if (ring && p.width == 128 * Q && p.F == 128) {
       auto kernel = gat_bwd_col_kernel<HP, Q, VEC, 1, ACC, EDGES, true>;
       static const cudaError_t attr = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                           (int)col_ring_bytes<Q>());
+                                                           (int)gather_ring_bytes<Q>());
       if (attr == cudaSuccess) {
-        kernel<<<blocks, kThreadsPerCta, col_ring_bytes<Q>(), stream>>>(p);
+        kernel<<<blocks, kThreadsPerCta, gather_ring_bytes<Q>(), stream>>>(p);
         return;
       }
     }

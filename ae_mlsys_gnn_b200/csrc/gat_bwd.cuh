@@ -264,24 +264,7 @@ constexpr bool kColPipelined = VEC && Q <= 2;  // 128-bit tiles of at most 8 reg
 
 // (Two CTAs per SM are requested only for the pipelined narrow tiles; the widest tile gets
 // there by itself, and with the explicit limit its gather loop is scheduled into spills.)
-// RING (wide 128-bit tiles): the gathered rows travel through a ring in shared memory instead
-// of registers.  Every lane copies the 16-byte units it will read itself with cp.async
-// (groups of U rows, kColRingRows rows per warp), so rows stay in flight while earlier ones
-// are consumed, waiting costs one cp.async.wait_group, and no lane ever reads another lane's
-// copy: no barrier of any kind.  The plain loop holds a row in registers from request to use,
-// which limits a warp to U rows in flight and leaves none while it computes.
-constexpr int kColRingRows = 6;
-template <int Q>
-constexpr size_t col_ring_bytes() { return (size_t)kWarpsPerCta * kColRingRows * Q * 32 * sizeof(float4); }
-
-__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
+// RING: the gathered rows travel through the per-lane cp.async ring described in common.cuh.
 template <int HP, int Q, bool VEC, int HPS = 0, bool ACC = false, bool EDGES = false, bool RING = false>
 __global__ void __launch_bounds__(kThreadsPerCta, (kColPipelined<Q, VEC> || RING) ? 2 : 0)
 gat_bwd_col_kernel(GatBwdColParams p) {
@@ -394,9 +377,9 @@ gat_bwd_col_kernel(GatBwdColParams p) {
           }
         }
       } else if constexpr (RING) {
-        constexpr int G = kColRingRows / U;  // groups of U rows the ring holds
-        static_assert(G >= 2 && G * U == kColRingRows, "ring rows must be a multiple of the group");
-        float4* const ring = reinterpret_cast<float4*>(col_ring_smem) + (size_t)wib * (kColRingRows * Q * 32) + lane;
+        constexpr int G = kGatherRingRows / U;  // groups of U rows the ring holds
+        static_assert(G >= 2 && G * U == kGatherRingRows, "ring rows must be a multiple of the group");
+        float4* const ring = reinterpret_cast<float4*>(col_ring_smem) + (size_t)wib * (kGatherRingRows * Q * 32) + lane;
         auto issue = [&](int g) {  // rows [g*U, g*U + U) of this batch into ring slot g % G
           if (g * U < nbr) {
 #pragma unroll
