@@ -281,14 +281,12 @@ __device__ __forceinline__ void finish_segment(const WGatherParams& p, const Pol
 
 // ----- main kernel ----------------------------------------------------------
 
-template <template <int> class Policy, int HP, int Q, bool VEC, class Tile = RowTile<Q, VEC>, bool RING = false>
-__global__ void __launch_bounds__(kThreadsPerCta, RING ? 2 : 0)
+template <template <int> class Policy, int HP, int Q, bool VEC, class Tile = RowTile<Q, VEC>>
+__global__ void __launch_bounds__(kThreadsPerCta)
 wgather_kernel(WGatherParams p, Policy<HP> pol) {
   constexpr int VW = Tile::VW;
   constexpr int U = Q * VW >= 16 ? 2 : (Q * VW >= 8 ? 4 : 8);
   constexpr bool SOFTMAX = Policy<HP>::kSoftmax;
-  static_assert(!RING || (VEC && std::is_same<Tile, RowTile<Q, VEC>>::value), "the ring moves 16-byte units of fp32 rows");
-  extern __shared__ __align__(16) unsigned char gather_ring_smem[];
   __shared__ int cs_all[kWarpsPerCta][32];
   __shared__ float ws_all[kWarpsPerCta][32 * HP];
 
@@ -387,54 +385,16 @@ wgather_kernel(WGatherParams p, Policy<HP> pol) {
           }
         }
       };
-      if constexpr (RING) {
-        constexpr int G = kGatherRingRows / U;  // groups of U rows the ring holds
-        static_assert(G >= 2 && G * U == kGatherRingRows, "ring rows must be a multiple of the group");
-        float4* const ring = reinterpret_cast<float4*>(gather_ring_smem) + (size_t)wib * (kGatherRingRows * Q * 32) + lane;
-        auto issue = [&](int g) {  // rows [g*U, g*U + U) of this batch into ring slot g % G
-          if (g * U < nbr) {
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-              const float4* row = reinterpret_cast<const float4*>(p.feat + (size_t)cs[g * U + u] * p.ld_feat) + lane;
-              float4* dst = ring + ((g % G) * U + u) * (Q * 32);
-#pragma unroll
-              for (int q = 0; q < Q; ++q)
-                if (t.valid[q]) cp_async_16(dst + q * 32, row + q * 32);
-            }
-          }
-          cp_async_commit();  // (an empty group keeps the count of pending groups uniform)
-        };
-#pragma unroll
-        for (int g = 0; g < G - 1; ++g) issue(g);
+      float va[U][Q][VW], vb[U][Q][VW];
+      load_rows(va, 0);
 #pragma unroll 1
-        for (int g = 0; g * U < nbr; ++g) {
-          issue(g + G - 1);        // its slot was consumed in the previous iteration
-          cp_async_wait<G - 1>();  // all but the newest G-1 groups have landed: group g is there
-          float v[U][Q][VW];
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-#pragma unroll
-            for (int q = 0; q < Q; ++q) {
-              float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (t.valid[q]) x = ring[((g % G) * U + u) * (Q * 32) + q * 32];
-              v[u][q][0] = x.x; v[u][q][1] = x.y; v[u][q][2] = x.z; v[u][q][3] = x.w;
-            }
-          }
-          accumulate(v, g * U);
-        }
-        cp_async_wait<0>();  // only empty groups can be pending here
-      } else {
-        float va[U][Q][VW], vb[U][Q][VW];
-        load_rows(va, 0);
-#pragma unroll 1
-        for (int jj = 0; jj < nbr; jj += 2 * U) {
-          const bool more = jj + U < nbr;
-          if (more) load_rows(vb, jj + U);
-          accumulate(va, jj);
-          if (more) {
-            if (jj + 2 * U < nbr) load_rows(va, jj + 2 * U);
-            accumulate(vb, jj + U);
-          }
+      for (int jj = 0; jj < nbr; jj += 2 * U) {
+        const bool more = jj + U < nbr;
+        if (more) load_rows(vb, jj + U);
+        accumulate(va, jj);
+        if (more) {
+          if (jj + 2 * U < nbr) load_rows(va, jj + 2 * U);
+          accumulate(vb, jj + U);
         }
       }
     }
@@ -655,24 +615,7 @@ inline void launch_wgather(const WGatherParams& p, const Policy<HP>& pol,
                            cudaStream_t stream) {
   if (p.g.num_chunks > 0) {
     const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
-    bool launched = false;
-    // rows of more than 256 floats, fp32, 128-bit tile: rows in flight in shared memory
-    if constexpr (VEC && Q >= 3 && std::is_same<Tile, RowTile<Q, VEC>>::value) {
-      static const bool ring = [] {
-        const char* e = getenv("GNN_B200_FWD_RING");
-        return e ? atoi(e) != 0 : true;
-      }();
-      if (ring) {
-        auto kernel = wgather_kernel<Policy, HP, Q, VEC, Tile, true>;
-        static const cudaError_t attr = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                             (int)gather_ring_bytes<Q>());
-        if (attr == cudaSuccess) {
-          kernel<<<blocks, kThreadsPerCta, gather_ring_bytes<Q>(), stream>>>(p, pol);
-          launched = true;
-        }
-      }
-    }
-    if (!launched) wgather_kernel<Policy, HP, Q, VEC, Tile><<<blocks, kThreadsPerCta, 0, stream>>>(p, pol);
+    wgather_kernel<Policy, HP, Q, VEC, Tile><<<blocks, kThreadsPerCta, 0, stream>>>(p, pol);
   }
   launch_wgather_fixup<Policy, HP, Q, VEC, Tile>(p, pol, stream);
 }
