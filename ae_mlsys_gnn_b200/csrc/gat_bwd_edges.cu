@@ -18,7 +18,7 @@
 //
 // Replaces, for callers that keep `out`, the row pass that stands in for the reference's
 // mhspmm_backward_kernel + mhsddmm (src/fused_gat/fused_gat_SM.cu:560-607, :656-732).
-#include "common.cuh"
+#include "wgather.cuh"
 
 using namespace gnn;
 
@@ -86,6 +86,54 @@ pack_kernel(int64_t n_rows, const float* __restrict__ out, const float* __restri
       rp[2 * H + h] = empty ? 0.f : 1.f / sum;
       rp[3 * H + h] = empty ? 0.f : acc;
     }
+  }
+}
+
+// The same for rows of up to 512 floats read with 128-bit loads: the whole row of both
+// matrices is requested at once (2 Q loads per lane in flight instead of two per head), the
+// per-head sums come out of one combined butterfly, and the lanes that end up holding a head's
+// sum write that head's record side by side.
+template <int HP, int Q, bool ELU>
+__global__ void __launch_bounds__(kThreadsPerCta)
+pack_tile_kernel(int64_t n_rows, const float* __restrict__ out, const float* __restrict__ gout,
+                 const float* __restrict__ attn_row, const float* __restrict__ edge_max,
+                 const float* __restrict__ edge_sum, int H, int F, float alpha, float* __restrict__ grad_pre,
+                 float* __restrict__ rowpack) {
+  const int lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  RowTile<Q, true> t;
+  t.init(lane, H * F, F, H);
+  float ov[Q][4], gv[Q][4];
+  t.load(out + (size_t)r * H * F, lane, ov);
+  t.load(gout + (size_t)r * H * F, lane, gv);
+  float pv[HP];
+#pragma unroll
+  for (int h = 0; h < HP; ++h) pv[h] = 0.f;
+#pragma unroll
+  for (int q = 0; q < Q; ++q) {
+    float d = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (ELU) gv[q][i] *= ov[q][i] > 0.f ? 1.f : alpha * expf(ov[q][i]);
+      d = fmaf(ov[q][i], gv[q][i], d);
+    }
+#pragma unroll
+    for (int h = 0; h < HP; ++h)
+      if (t.head[q] == h && t.valid[q]) pv[h] += d;
+  }
+  if constexpr (ELU) t.store(grad_pre + (size_t)r * H * F, lane, gv);
+  warp_multi_sum<HP>(pv, lane);  // head h on lanes [h*32/HP, (h+1)*32/HP)
+  constexpr int LPH = 32 / HP;
+  const int h = lane / LPH;
+  if ((lane & (LPH - 1)) == 0 && h < H) {
+    float* rp = rowpack + (size_t)r * 4 * H;
+    const float sum = __ldg(edge_sum + (size_t)r * H + h);
+    const bool empty = !(sum > 0.f);  // a row without edges: same record as the two-pass backward writes
+    rp[h] = __ldg(attn_row + (size_t)r * H + h);
+    rp[H + h] = empty ? kNegBig : __ldg(edge_max + (size_t)r * H + h);
+    rp[2 * H + h] = empty ? 0.f : 1.f / sum;
+    rp[3 * H + h] = empty ? 0.f : pv[0];
   }
 }
 
@@ -250,6 +298,18 @@ int launch_pack(const char* what, int64_t n_rows, const float* out, const float*
   const unsigned blocks = (unsigned)((n_rows + kWarpsPerCta - 1) / kWarpsPerCta);
   const bool vec = aligned16(out) && aligned16(grad_out) && (!elu || aligned16(grad_pre)) &&
                    ((int64_t)H * F) % 4 == 0;
+  if (vec && F % 4 == 0 && H <= 8 && (int64_t)H * F <= 512) {
+    const bool ok = dispatch_tile(next_pow2(H), H * F, true, [&](auto hp, auto q, auto) {
+      constexpr int HP = decltype(hp)::value, Q = decltype(q)::value;
+      if (elu)
+        pack_tile_kernel<HP, Q, true><<<blocks, kThreadsPerCta, 0, stream>>>(n_rows, out, grad_out, attn_row, edge_max,
+                                                                           edge_sum, H, F, alpha, grad_pre, rowpack);
+      else
+        pack_tile_kernel<HP, Q, false><<<blocks, kThreadsPerCta, 0, stream>>>(n_rows, out, grad_out, attn_row, edge_max,
+                                                                            edge_sum, H, F, alpha, grad_pre, rowpack);
+    });
+    if (ok) return check_launch(what);
+  }
 #define GNN_PACK(V, E)                                                                                     \
   pack_kernel<V, E><<<blocks, kThreadsPerCta, 0, stream>>>(n_rows, out, grad_out, attn_row, edge_max,       \
                                                           edge_sum, H, F, alpha, grad_pre, rowpack)
