@@ -190,9 +190,17 @@ void launch_col_main(const GatBwdColParams& p, cudaStream_t stream) {
     }();
     if (ring && p.width == 128 * Q && p.F == 128) {
       auto kernel = gat_bwd_col_kernel<HP, Q, VEC, 1, ACC, EDGES, true>;
-      static const cudaError_t attr = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                           (int)gather_ring_bytes<Q>());
-      if (attr == cudaSuccess) {
+      // more than 48 KB of dynamic shared memory needs this opt-in once per device and kernel
+      static bool opted[64] = {};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      bool ready = dev >= 0 && dev < 64 && opted[dev];
+      if (!ready && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)gather_ring_bytes<Q>()) == cudaSuccess) {
+        ready = true;
+        if (dev >= 0 && dev < 64) opted[dev] = true;
+      }
+      if (ready) {
         kernel<<<blocks, kThreadsPerCta, gather_ring_bytes<Q>(), stream>>>(p);
         return;
       }
