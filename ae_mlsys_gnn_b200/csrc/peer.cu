@@ -20,6 +20,7 @@
 // kernel has completed, so the caller orders "all ranks' push kernels are complete" before
 // the consumer with a collective on the same stream (a one-element all-reduce).
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include "../../include/gnn_b200.h"
 #include "common.cuh"
@@ -199,7 +200,14 @@ extern "C" int gnn_halo_push_ranges(const float* x, int64_t row_floats, const in
   while (lpr < 32 && lpr < upr) lpr <<= 1;
   const int64_t warps = (slots + 32 / lpr - 1) / (32 / lpr);
   int64_t blocks = (warps + 7) / 8;
-  const int64_t cap = 148LL * 8 * 4;  // grid-stride beyond a few waves
+  // grid-stride beyond a few waves (GNN_B200_PUSH_BLOCKS_PER_SM, 1..32: measured at 2, 4 and 32
+  // blocks per SM the transfer time does not depend on it)
+  static const int per_sm = [] {
+    const char* e = getenv("GNN_B200_PUSH_BLOCKS_PER_SM");
+    const int v = e ? atoi(e) : 32;
+    return v < 1 ? 1 : (v > 32 ? 32 : v);
+  }();
+  const int64_t cap = 148LL * per_sm;
   if (blocks > cap) blocks = cap;
   if (vec) halo_push_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(p, lpr);
   else halo_push_kernel<false><<<(unsigned)blocks, 256, 0, stream>>>(p, lpr);
