@@ -20,6 +20,7 @@
 // kernel has completed, so the caller orders "all ranks' push kernels are complete" before
 // the consumer with a collective on the same stream (a one-element all-reduce).
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include "../../include/gnn_b200.h"
 #include "common.cuh"
@@ -57,39 +58,65 @@ struct PushParams {
   int64_t group_max;        // rows of the largest group
 };
 
-// One thread per 16-byte unit (VEC) or per float; consecutive threads take consecutive units
-// of a row, so a warp writes 512 contiguous bytes of the destination.  The rows are visited in
-// slots that cycle through the destination ranks (slot s: rank group[s % n_groups], its row
-// s / n_groups), so at every moment a sender's stores are spread over all its receivers and
-// no receiver has all the senders of the node storing into it at once; a slot past the end
-// of a shorter group is skipped.  The rank's own rows follow.
+// LPR lanes per row (a power of two, 32 for rows of 32 units or more; a unit is 16 bytes with
+// VEC, else one float), so a warp moves 32 / LPR rows at a time and consecutive lanes write
+// consecutive units: 512 contiguous bytes of the destination per warp instruction for wide rows.
+// The rows are visited in slots that cycle through the destination ranks (slot s: rank
+// group[s % n_groups], its row s / n_groups), so at every moment a sender's stores are spread
+// over all its receivers and no receiver has all the senders of the node storing into it at
+// once; a slot past the end of a shorter group is skipped.  The rank's own rows follow.
+// The per-rank tables are copied to shared memory first: indexing kernel parameters with a
+// run-time index would send every access through local memory.
 template <bool VEC>
 __global__ void __launch_bounds__(256)
-halo_push_kernel(PushParams p) {
-  const int64_t upr = VEC ? p.row_floats / 4 : p.row_floats;  // units per row
+halo_push_kernel(PushParams p, int lpr) {
+  __shared__ int64_t s_beg[kMaxPeers], s_cnt[kMaxPeers];
+  __shared__ float* s_dst[kMaxPeers];
+  __shared__ int s_group[kMaxPeers];
+  if (threadIdx.x < kMaxPeers) {
+    s_beg[threadIdx.x] = p.send_beg[threadIdx.x];
+    s_cnt[threadIdx.x] = p.send_cnt[threadIdx.x];
+    s_dst[threadIdx.x] = p.dst[threadIdx.x];
+    s_group[threadIdx.x] = p.group[threadIdx.x];
+  }
+  __syncthreads();
+  const int upr = (int)(VEC ? p.row_floats / 4 : p.row_floats);  // units per row
+  const int rpw = 32 / lpr;                                       // rows per warp and step
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / lpr, off = lane % lpr;
   const int64_t n_slots = p.group_max * p.n_groups;
-  const int64_t total = (n_slots + p.n_own) * upr;
-  for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < total;
-       u += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t slot = u / upr;
-    const int64_t col = u - slot * upr;
+  const int64_t total = n_slots + p.n_own;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t base = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * rpw; base < total;
+       base += warps * rpw) {
+    const int64_t slot = base + sub;
+    if (slot >= total) continue;
     const float* src;
     float* dst;
     if (slot < n_slots) {
       const int64_t i = slot / p.n_groups;
-      const int q = p.group[(int)(slot - i * p.n_groups)];
-      if (i >= p.send_cnt[q]) continue;
-      src = p.x + (size_t)__ldg(p.send_idx + p.send_beg[q] + i) * p.row_floats;
-      dst = p.dst[q] + (size_t)i * p.row_floats;
+      const int q = s_group[(int)(slot - i * p.n_groups)];
+      if (i >= s_cnt[q]) continue;
+      src = p.x + (size_t)__ldg(p.send_idx + s_beg[q] + i) * p.row_floats;
+      dst = s_dst[q] + (size_t)i * p.row_floats;
     } else {
       const int64_t r = slot - n_slots;
       src = p.x + (size_t)r * p.row_floats;
       dst = p.own_dst + (size_t)r * p.row_floats;
     }
-    if (VEC)
-      reinterpret_cast<float4*>(dst)[col] = __ldg(reinterpret_cast<const float4*>(src) + col);
-    else
-      dst[col] = __ldg(src + col);
+    if (VEC) {
+      const float4* s4 = reinterpret_cast<const float4*>(src);
+      float4* d4 = reinterpret_cast<float4*>(dst);
+      // up to four units per lane requested before the first is stored
+      int u = off;
+      for (; u + 3 * lpr < upr; u += 4 * lpr) {
+        const float4 a = __ldg(s4 + u), b = __ldg(s4 + u + lpr), c = __ldg(s4 + u + 2 * lpr), d = __ldg(s4 + u + 3 * lpr);
+        d4[u] = a; d4[u + lpr] = b; d4[u + 2 * lpr] = c; d4[u + 3 * lpr] = d;
+      }
+      for (; u < upr; u += lpr) d4[u] = __ldg(s4 + u);
+    } else {
+      for (int u = off; u < upr; u += lpr) dst[u] = __ldg(src + u);
+    }
   }
 }
 
@@ -166,13 +193,24 @@ extern "C" int gnn_halo_push_ranges(const float* x, int64_t row_floats, const in
   if (n_send > 0 && (!send_idx || !x)) return bad("gnn_halo_push: null pointer");
   if (p.n_own > 0 && !x) return bad("gnn_halo_push: null pointer");
   if (p.n_groups == 0) p.n_groups = 1;  // no rows to send: zero slots, the divisor stays valid
-  const int64_t units = (p.group_max * p.n_groups + p.n_own) * (vec ? row_floats / 4 : row_floats);
-  if (units == 0) return GNN_OK;
-  int64_t blocks = (units + 255) / 256;
-  const int64_t cap = 148LL * 8 * 4;  // grid-stride beyond a few waves
+  const int64_t slots = p.group_max * p.n_groups + p.n_own;
+  if (slots == 0) return GNN_OK;
+  const int64_t upr = vec ? row_floats / 4 : row_floats;
+  int lpr = 1;
+  while (lpr < 32 && lpr < upr) lpr <<= 1;
+  const int64_t warps = (slots + 32 / lpr - 1) / (32 / lpr);
+  int64_t blocks = (warps + 7) / 8;
+  // grid-stride beyond a few waves (GNN_B200_PUSH_BLOCKS_PER_SM, 1..32: measured at 2, 4 and 32
+  // blocks per SM the transfer time does not depend on it)
+  static const int per_sm = [] {
+    const char* e = getenv("GNN_B200_PUSH_BLOCKS_PER_SM");
+    const int v = e ? atoi(e) : 32;
+    return v < 1 ? 1 : (v > 32 ? 32 : v);
+  }();
+  const int64_t cap = 148LL * per_sm;
   if (blocks > cap) blocks = cap;
-  if (vec) halo_push_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(p);
-  else halo_push_kernel<false><<<(unsigned)blocks, 256, 0, stream>>>(p);
+  if (vec) halo_push_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(p, lpr);
+  else halo_push_kernel<false><<<(unsigned)blocks, 256, 0, stream>>>(p, lpr);
   return check_launch("gnn_halo_push");
 }
 

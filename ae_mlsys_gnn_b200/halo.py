@@ -517,10 +517,14 @@ class HaloGATConv(_GATBase):
     OVERLAP_MIN_WIDTH = 128   # floats per row: narrow rows travel in no time
 
     def __init__(self, in_feats, out_feats, num_heads, negative_slope=0.2, kernels=_CudaKernels,
-                 recompute_projection="auto", activation=None, key=0, overlap_blocks=4):
+                 recompute_projection="auto", activation=None, key=0, overlap_blocks=1, side_weight_grads=False):
         super().__init__(in_feats, out_feats, num_heads, negative_slope)
         self.kernels = kernels
+        # Both options move work beside the main stream (see forward); measured on 2 and 4 GPUs they
+        # change the epoch by less than the run-to-run spread, because a GEMM and a push kernel that
+        # run at the same time slow each other down by about what the overlap hides: off by default.
         self.overlap_blocks = int(os.environ.get("GNN_B200_OVERLAP_BLOCKS", overlap_blocks))
+        self.side_weight_grads = bool(int(os.environ.get("GNN_B200_SIDE_WEIGHT_GRADS", int(side_weight_grads))))
         self.recompute_projection = recompute_projection
         self.activation = activation
         self.key = key
@@ -539,7 +543,7 @@ class HaloGATConv(_GATBase):
             with torch.no_grad():
                 (x_ext,) = exch.exchange((self.key, "fwd_x"), [feat.detach()], part.fwd, n)
             h_ext = feat.new_empty((x_ext.shape[0], H, Fo))
-            with dense.side_weight_grads(part.world > 1):  # X^T G fills the next exchange of the backward
+            with dense.side_weight_grads(self.side_weight_grads and part.world > 1):  # X^T G beside the next exchange
                 h = dense.project(feat, self.W, out=dense.OutRows(h_ext, 0)).view(-1, H, Fo)
             if x_ext.shape[0] > n:
                 with torch.no_grad():
@@ -559,7 +563,7 @@ class HaloGATConv(_GATBase):
 
                 def after(lo, hi):
                     exch.push_rows(key, 0, h_ext, part.fwd, lo, hi)
-            with dense.side_weight_grads(part.world > 1):
+            with dense.side_weight_grads(self.side_weight_grads and part.world > 1):
                 h = dense.project(feat, self.W, out=dense.OutRows(h_ext, 0), row_blocks=blocks,
                                   after_block=after).view(-1, H, Fo)
         return HaloGATFunction.apply(h, self.attn_l, self.attn_r, part, self.negative_slope,

@@ -164,6 +164,8 @@ def _worker(rank, world, port, results, recompute, graph="powerlaw", pools=None,
         model = HaloGAT(12, [8], [2], 5, 1, kernels=OracleKernels, exchange=exchange)
         for layer in model.gat_layers:
             layer.recompute_projection = recompute
+            if overlap:
+                layer.overlap_blocks = 4
         for _ in range(3 if pools is not None else 1):  # several steps: both buffers of every exchange point
             model.zero_grad()
             out = model(part, part.local_slice(x))

@@ -48,6 +48,9 @@ def _worker(rank, world, port, results, exchange="gather"):
 
             part = build_halo_partition(g.row_ptr, g.col_ind, cp, ri, rank, world)
             model = HaloGAT(20, [16, 16], [4, 4], 6, 1, exchange="peer" if exchange == "peer" else "nccl").to(dev)
+            if blocks:  # both kinds of work beside the main stream
+                for layer in model.gat_layers:
+                    layer.overlap_blocks, layer.side_weight_grads = 4, True
             max_n = max(part.bounds[r + 1] - part.bounds[r] for r in range(world))
         else:
             part = build_partition(g.row_ptr, g.col_ind, cp, ri, rank, world, pieces=1 if world == 2 else 3)
