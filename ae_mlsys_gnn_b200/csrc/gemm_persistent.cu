@@ -51,20 +51,13 @@ constexpr int kNumBars = 3 * kMaxStages + 2 * kAccBufs;
 // mode.  BN = 256 (B given as split hi/lo, K-major: the projection weights): the B tile is
 // 256 rows, two stages of 96 KB, all 512 tensor-memory columns; per multiply-add it reads 2/3 of
 // the shared-memory bytes of the 128-wide tile, which is what bounds this kernel.
-template <int BN, bool BRES = false>
+template <int BN>
 struct Geom {
-  // BRES ("weights resident"): for a reduction of at most kResKb blocks of 32 the B tiles of the
-  // CTA's column tile (hi and lo, all K blocks) are loaded once and stay in shared memory; the
-  // stages then hold only A.  Without it every 128-row tile fetches the same weight tile from
-  // L2 again, which is what bounds short reductions (K = 100, 48).
-  static constexpr int kResKb = BRES ? (BN == 128 ? 4 : 2) : 0;
-  static constexpr int kStages = BRES ? 3 : (BN == 128 ? 3 : 2);
+  static constexpr int kStages = BN == 128 ? 3 : 2;
   static constexpr int kBTileBytes = BN * BK * 4;
-  static constexpr int kStageBytes = BRES ? 2 * kTileBytes : 2 * kTileBytes + 2 * kBTileBytes;  // A0, A1[, B0, B1]
-  static constexpr int kResBytes = kResKb * 2 * kBTileBytes;
+  static constexpr int kStageBytes = 2 * kTileBytes + 2 * kBTileBytes;  // A0, A1, B0, B1
   static constexpr int kTmemCols = kAccBufs * BN;
-  static constexpr size_t kSmemBytes =
-      (size_t)kResBytes + (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 8 * (kNumBars + 1) + 16;
+  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 8 * kNumBars + 16;
 };
 // The tensor core adds into its fp32 accumulator with truncation: a chain of n MMAs comes
 // out low by about n * 2^-26 of its value (measured: -4e-4 after 25,000 MMAs).  After this
@@ -242,20 +235,18 @@ __device__ __forceinline__ TileCoord decode_tile(const Params& p, int tile) {
   return t;
 }
 
-template <int BN, bool BRES = false>
+template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
                        const __grid_constant__ CUtensorMap map_b0, const __grid_constant__ CUtensorMap map_b1,
                        Params p) {
-  using G = Geom<BN, BRES>;
-  constexpr int kStages = G::kStages;
-  constexpr int kStageBytes = G::kStageBytes;
-  constexpr int kBTileBytes = G::kBTileBytes;
-  constexpr int kTmemCols = G::kTmemCols;
+  constexpr int kStages = Geom<BN>::kStages;
+  constexpr int kStageBytes = Geom<BN>::kStageBytes;
+  constexpr int kBTileBytes = Geom<BN>::kBTileBytes;
+  constexpr int kTmemCols = Geom<BN>::kTmemCols;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
-  const uint32_t res_base = (raw_addr + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
-  const uint32_t base = res_base + G::kResBytes;           // stages follow the resident weights (if any)
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
   uint8_t* const base_ptr = smem_raw + (base - raw_addr);
   const uint32_t bars = base + kStages * kStageBytes;
   auto full_bar = [&](int s) { return bars + 8u * s; };                       // TMA -> converters
@@ -263,9 +254,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
   auto empty_bar = [&](int s) { return bars + 8u * (2 * kStages + s); };      // MMA -> TMA
   auto acc_full_bar = [&](int b) { return bars + 8u * (3 * kMaxStages + b); };   // MMA -> epilogue
   auto acc_empty_bar = [&](int b) { return bars + 8u * (3 * kMaxStages + kAccBufs + b); };  // epilogue -> MMA
-  const uint32_t res_bar = bars + 8u * kNumBars;                                 // TMA -> MMA: resident weights
-  const uint32_t tmem_slot = bars + 8u * (kNumBars + 1);
-  uint32_t* const tmem_slot_ptr = reinterpret_cast<uint32_t*>(base_ptr + kStages * kStageBytes + 8 * (kNumBars + 1));
+  const uint32_t tmem_slot = bars + 8u * kNumBars;
+  uint32_t* const tmem_slot_ptr = reinterpret_cast<uint32_t*>(base_ptr + kStages * kStageBytes + 8 * kNumBars);
 
   __shared__ volatile int s_failed;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -281,7 +271,6 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
       mbar_init(acc_full_bar(b), 1);
       mbar_init(acc_empty_bar(b), 4);
     }
-    mbar_init(res_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -296,17 +285,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      const uint32_t tx = operand_tx_bytes(p.a_mode, kTileBytes) + (BRES ? 0u : operand_tx_bytes(p.b_mode, kBTileBytes));
-      if constexpr (BRES) {
-        // the grid is a multiple of tiles_n, so every tile of this CTA has the same column tile:
-        // its weights (all K blocks, hi and lo) are loaded once
-        if ((int)blockIdx.x < p.num_tiles) {
-          const TileCoord t0 = decode_tile<BN>(p, blockIdx.x);
-          mbar_expect_tx(res_bar, (uint32_t)p.total_kb * operand_tx_bytes(p.b_mode, kBTileBytes));
-          for (int kb = 0; kb < p.total_kb; ++kb)
-            load_operand(p.b_mode, res_base + kb * 2 * kBTileBytes, &map_b0, &map_b1, t0.n0, kb, res_bar, kBTileBytes);
-        }
-      }
+      const uint32_t tx = operand_tx_bytes(p.a_mode, kTileBytes) + operand_tx_bytes(p.b_mode, kBTileBytes);
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < p.num_tiles && !s_failed; tile += gridDim.x) {
         const TileCoord t = decode_tile<BN>(p, tile);
@@ -317,9 +296,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
           const uint32_t st = base + s * kStageBytes;
           mbar_expect_tx(full_bar(s), tx);
           load_operand(p.a_mode, st, &map_a0, &map_a1, t.m0, t.kb_begin + kb, full_bar(s));
-          if constexpr (!BRES)
-            load_operand(p.b_mode, st + 2 * kTileBytes, &map_b0, &map_b1, t.n0, t.kb_begin + kb, full_bar(s),
-                         kBTileBytes);
+          load_operand(p.b_mode, st + 2 * kTileBytes, &map_b0, &map_b1, t.n0, t.kb_begin + kb, full_bar(s),
+                       kBTileBytes);
         }
       }
     }
@@ -331,9 +309,6 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
       const uint64_t b_step = b_mn ? (1024 >> 4) : (32 >> 4);
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      if constexpr (BRES) {
-        if ((int)blockIdx.x < p.num_tiles && !mbar_wait(res_bar, 0, &s_failed)) { s_failed = 1; ok = false; }
-      }
       for (int tile = blockIdx.x; tile < p.num_tiles && ok && !s_failed; tile += gridDim.x) {
         const TileCoord t = decode_tile<BN>(p, tile);
         int n_mma = min(BN, p.N - t.n0);
@@ -354,9 +329,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
             const uint32_t st = base + s * kStageBytes;
             const uint64_t a_hi = operand_desc(st, a_mn);
             const uint64_t a_lo = operand_desc(st + kTileBytes, a_mn);
-            const uint32_t bst = BRES ? res_base + (uint32_t)kb * 2u * kBTileBytes : st + 2 * kTileBytes;
-            const uint64_t b_hi = operand_desc(bst, b_mn);
-            const uint64_t b_lo = operand_desc(bst + kBTileBytes, b_mn);
+            const uint64_t b_hi = operand_desc(st + 2 * kTileBytes, b_mn);
+            const uint64_t b_lo = operand_desc(st + 2 * kTileBytes + kBTileBytes, b_mn);
 #pragma unroll
             for (int k = 0; k < BK / 8; ++k) {
               const uint64_t da = a_step * k, db = b_step * k;
@@ -383,7 +357,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
         if (!mbar_wait(full_bar(s), (it / kStages) & 1, &s_failed)) { s_failed = 1; ok = false; break; }
         uint8_t* st = base_ptr + s * kStageBytes;
         if (conv_a) convert_tile(st, st + kTileBytes, tid);
-        if constexpr (BN == 128 && !BRES) {  // the 256-wide tile and resident weights take B already split
+        if constexpr (BN == 128) {  // the 256-wide tile takes B already split
           if (conv_b) convert_tile(st + 2 * kTileBytes, st + 3 * kTileBytes, tid);
         }
         // the tensor core reads shared memory through the async proxy
@@ -504,7 +478,6 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
         mbar_wait(full_bar(s), 0, nullptr, kDrainCycles);
         mbar_wait(full_bar(s), 1, nullptr, kDrainCycles);
       }
-      if constexpr (BRES) mbar_wait(res_bar, 0, nullptr, kDrainCycles);
     }
     __syncthreads();
   }
@@ -585,7 +558,7 @@ bool encode_operand(const GemmOperand& o, int64_t K, CUtensorMap* m0, CUtensorMa
   return false;
 }
 
-template <int BN, bool BRES = false>
+template <int BN>
 int launch_instance(const CUtensorMap& ma0, const CUtensorMap& ma1, const CUtensorMap& mb0, const CUtensorMap& mb1,
                     Params p, int64_t b_rows, int splits, cudaStream_t stream) {
   static bool attr_set = false;  // per process and instantiation; the attribute is per device
@@ -593,8 +566,8 @@ int launch_instance(const CUtensorMap& ma0, const CUtensorMap& ma1, const CUtens
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set || attr_dev != dev) {
-    if (cudaFuncSetAttribute(gemm_persistent_kernel<BN, BRES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)Geom<BN, BRES>::kSmemBytes) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_persistent_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)Geom<BN>::kSmemBytes) != cudaSuccess) {
       set_last_error("gnn_gemm_tf32x3: cannot reserve dynamic shared memory");
       return GNN_ERR_CUDA;
     }
@@ -611,9 +584,8 @@ int launch_instance(const CUtensorMap& ma0, const CUtensorMap& ma1, const CUtens
     return GNN_ERR_INVALID_ARG;
   }
   p.num_tiles = (int)tiles;
-  int grid = (int)(tiles < sms ? tiles : sms);
-  if (BRES) grid = grid / p.tiles_n * p.tiles_n;  // a CTA then keeps one column tile (tile % tiles_n) for good
-  gemm_persistent_kernel<BN, BRES><<<grid, kThreads, Geom<BN, BRES>::kSmemBytes, stream>>>(ma0, ma1, mb0, mb1, p);
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  gemm_persistent_kernel<BN><<<grid, kThreads, Geom<BN>::kSmemBytes, stream>>>(ma0, ma1, mb0, mb1, p);
   return GNN_OK;
 }
 
@@ -654,23 +626,11 @@ int launch_gemm_persistent(const GemmOperand& a, const GemmOperand& b, int64_t K
   }();
   const bool wide = wide_ok && b.mode == kKMajorSplit && a.mode == kKMajorRaw && splits == 1 && b.rows >= 256 &&
                     p.total_kb <= kChainKb;
-  // short reductions keep the weights of the column tile in shared memory (GNN_B200_GEMM_RESIDENT=0: off)
-  static const bool res_ok = [] {
-    const char* e = getenv("GNN_B200_GEMM_RESIDENT");
-    return !(e && e[0] == '0');
-  }();
-  const bool presplit = b.mode == kKMajorSplit && a.mode == kKMajorRaw && splits == 1;
-  const bool res256 = res_ok && wide && p.total_kb <= Geom<256, true>::kResKb;
-  const bool res128 = res_ok && presplit && !res256 && p.total_kb <= Geom<128, true>::kResKb &&
-                      p.tiles_m >= 148;  // enough row tiles for every CTA to reuse its weights
-  const bool box256 = res256 || (wide && !res128);
   CUtensorMap ma0, ma1, mb0, mb1;
-  if (!encode_operand(a, K, &ma0, &ma1) || !encode_operand(b, K, &mb0, &mb1, box256 ? 256 : BM)) {
+  if (!encode_operand(a, K, &ma0, &ma1) || !encode_operand(b, K, &mb0, &mb1, wide ? 256 : BM)) {
     set_last_error("gnn_gemm_tf32x3: cuTensorMapEncodeTiled failed");
     return GNN_ERR_CUDA;
   }
-  if (res256) return launch_instance<256, true>(ma0, ma1, mb0, mb1, p, b.rows, splits, stream);
-  if (res128) return launch_instance<128, true>(ma0, ma1, mb0, mb1, p, b.rows, splits, stream);
   return wide ? launch_instance<256>(ma0, ma1, mb0, mb1, p, b.rows, splits, stream)
               : launch_instance<128>(ma0, ma1, mb0, mb1, p, b.rows, splits, stream);
 }
