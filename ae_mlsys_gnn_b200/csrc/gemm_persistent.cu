@@ -46,6 +46,10 @@ constexpr int kThreads = 32 * 10;
 constexpr int kAccBufs = 2;
 constexpr int kMaxStages = 3;
 constexpr int kNumBars = 3 * kMaxStages + 2 * kAccBufs;
+// Epilogue staging: a 32 x 32 fp32 block per epilogue warp (4 KB), through which the rows a
+// thread holds are turned into stores that cover whole 128-byte lines.
+constexpr int kEpiStageBytes = 4 * 32 * 32 * 4;
+constexpr int kEpiStageOffset = (8 * kNumBars + 16 + 127) / 128 * 128;  // after the barriers and the TMEM slot, 128-byte aligned
 
 // Geometry of one instantiation.  BN = 128: three stages, 256 tensor-memory columns, any operand
 // mode.  BN = 256 (B given as split hi/lo, K-major: the projection weights): the B tile is
@@ -57,7 +61,8 @@ struct Geom {
   static constexpr int kBTileBytes = BN * BK * 4;
   static constexpr int kStageBytes = 2 * kTileBytes + 2 * kBTileBytes;  // A0, A1, B0, B1
   static constexpr int kTmemCols = kAccBufs * BN;
-  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 8 * kNumBars + 16;
+  static constexpr size_t kSmemBytes =
+      (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + kEpiStageOffset + kEpiStageBytes;
 };
 // The tensor core adds into its fp32 accumulator with truncation: a chain of n MMAs comes
 // out low by about n * 2^-26 of its value (measured: -4e-4 after 25,000 MMAs).  After this
@@ -256,6 +261,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
   auto acc_empty_bar = [&](int b) { return bars + 8u * (3 * kMaxStages + kAccBufs + b); };  // epilogue -> MMA
   const uint32_t tmem_slot = bars + 8u * kNumBars;
   uint32_t* const tmem_slot_ptr = reinterpret_cast<uint32_t*>(base_ptr + kStages * kStageBytes + 8 * kNumBars);
+  float4* const epi_stage = reinterpret_cast<float4*>(base_ptr + kStages * kStageBytes + kEpiStageOffset);
 
   __shared__ volatile int s_failed;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -443,7 +449,30 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_
               dl = dr = 0.f;
             }
           }
-          if (last && row < p.M) {
+          // A thread holds 32 consecutive floats of ONE row, so storing them directly makes every
+          // warp instruction touch 32 different lines, 16 bytes each.  Full chunks of aligned
+          // outputs go through the warp's staging block instead (written row-wise with the
+          // 16-byte units of row r rotated by r mod 8, read back four rows at a time, both
+          // conflict-free): every store instruction then covers four whole 128-byte lines.
+          const bool staged = last && p.N - col0 >= 32 && (p.ldc & 3) == 0 && ((uintptr_t)Cout & 15) == 0;  // warp-uniform
+          if (staged) {
+            float4* const stg = epi_stage + lg * 256;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              stg[lane * 8 + (j ^ (lane & 7))] =
+                  make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                              __uint_as_float(r[4 * j + 3]));
+            __syncwarp();
+            const int u = lane & 7;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3);
+              const float4 v = stg[rr * 8 + (u ^ (rr & 7))];
+              const int grow = t.m0 + lg * 32 + rr;
+              if (grow < p.M) *reinterpret_cast<float4*>(Cout + (size_t)grow * p.ldc + col0 + u * 4) = v;
+            }
+            __syncwarp();  // the block is rewritten by the next chunk
+          } else if (last && row < p.M) {
             float* crow = Cout + (size_t)row * p.ldc + col0;
             const int ncols = min(32, p.N - col0);
             if (ncols == 32 && ((uintptr_t)crow & 15) == 0) {
