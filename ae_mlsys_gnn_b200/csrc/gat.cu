@@ -17,18 +17,27 @@ bool narrow_shape(const HeadPlan& pl, int H, int64_t width) {
     const char* e = getenv("GNN_B200_NARROW");
     return !(e && e[0] == '0');
   }();
-  return enabled && pl.fused && !pl.vec && H == 1 && width <= 64;
+  return enabled && pl.fused && H == 1 && width <= 64;
 }
 
-// Calls fn(integral_constant<LPR>, integral_constant<Q>) for the sub-warp tile covering `width`.
-template <class Fn>
+// Calls fn(integral_constant<LPR>, integral_constant<Q>, bool_constant<VEC>) for the sub-warp tile covering
+// `width` floats: VEC (rows of whole 16-byte units) gives every lane four consecutive floats.
+template <bool VEC, class Fn>
 void dispatch_narrow(int width, Fn&& fn) {
   using std::integral_constant;
-  if (width <= 8) fn(integral_constant<int, 8>{}, integral_constant<int, 1>{});
-  else if (width <= 16) fn(integral_constant<int, 16>{}, integral_constant<int, 1>{});
-  else if (width <= 32) fn(integral_constant<int, 16>{}, integral_constant<int, 2>{});
-  else if (width <= 48) fn(integral_constant<int, 16>{}, integral_constant<int, 3>{});
-  else fn(integral_constant<int, 16>{}, integral_constant<int, 4>{});
+  if constexpr (VEC) {
+    using V = std::bool_constant<true>;
+    if (width <= 16) fn(integral_constant<int, 4>{}, integral_constant<int, 4>{}, V{});
+    else if (width <= 32) fn(integral_constant<int, 8>{}, integral_constant<int, 4>{}, V{});
+    else fn(integral_constant<int, 16>{}, integral_constant<int, 4>{}, V{});
+  } else {
+    using V = std::bool_constant<false>;
+    if (width <= 8) fn(integral_constant<int, 8>{}, integral_constant<int, 1>{}, V{});
+    else if (width <= 16) fn(integral_constant<int, 16>{}, integral_constant<int, 1>{}, V{});
+    else if (width <= 32) fn(integral_constant<int, 16>{}, integral_constant<int, 2>{}, V{});
+    else if (width <= 48) fn(integral_constant<int, 16>{}, integral_constant<int, 3>{}, V{});
+    else fn(integral_constant<int, 16>{}, integral_constant<int, 4>{}, V{});
+  }
 }
 
 int bad(const char* msg) {
@@ -121,12 +130,12 @@ extern "C" int gnn_gat_fwd_part(const int* row_ptr, const int* col_ind, int64_t 
         pol.slope = negative_slope;
         pol.seg_max = edge_max + (pl.fused ? 0 : h);
         pol.seg_sum = edge_sum + (pl.fused ? 0 : h);
-        if constexpr (HP == 1 && !decltype(v)::value) {
+        if constexpr (HP == 1) {
           if (narrow) {  // sub-warp main kernel; the merge kernel of the general tile reads its slots
             if (p.g.num_chunks > 0) {
               const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
-              dispatch_narrow(w, [&](auto lpr, auto nq) {
-                gat_fwd_narrow_kernel<decltype(lpr)::value, decltype(nq)::value>
+              dispatch_narrow<decltype(v)::value>(w, [&](auto lpr, auto nq, auto nv) {
+                gat_fwd_narrow_kernel<decltype(lpr)::value, decltype(nq)::value, decltype(nv)::value>
                     <<<blocks, kThreadsPerCta, 0, stream>>>(p, pol);
               });
             }
@@ -219,11 +228,11 @@ void launch_col_main(const GatBwdColParams& p, cudaStream_t stream) {
   gat_bwd_col_kernel<HP, Q, VEC, 0, ACC, EDGES><<<blocks, kThreadsPerCta, 0, stream>>>(p);
 }
 
-template <bool ACC, bool EDGES>
+template <bool ACC, bool EDGES, bool VEC>
 void launch_col_narrow(const GatBwdColParams& p, cudaStream_t stream) {
   const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
-  dispatch_narrow(p.width, [&](auto lpr, auto nq) {
-    gat_bwd_col_narrow_kernel<decltype(lpr)::value, decltype(nq)::value, ACC, EDGES>
+  dispatch_narrow<VEC>(p.width, [&](auto lpr, auto nq, auto nv) {
+    gat_bwd_col_narrow_kernel<decltype(lpr)::value, decltype(nq)::value, ACC, EDGES, decltype(nv)::value>
         <<<blocks, kThreadsPerCta, 0, stream>>>(p);
   });
 }
@@ -232,11 +241,11 @@ template <int HP, int Q, bool VEC>
 void launch_col(const GatBwdColParams& p, cudaStream_t stream, bool narrow = false) {
   if (p.g.num_chunks > 0 && narrow) {
     if (p.edge_grad) {
-      if (p.accumulate) launch_col_narrow<true, true>(p, stream);
-      else launch_col_narrow<false, true>(p, stream);
+      if (p.accumulate) launch_col_narrow<true, true, VEC>(p, stream);
+      else launch_col_narrow<false, true, VEC>(p, stream);
     } else {
-      if (p.accumulate) launch_col_narrow<true, false>(p, stream);
-      else launch_col_narrow<false, false>(p, stream);
+      if (p.accumulate) launch_col_narrow<true, false, VEC>(p, stream);
+      else launch_col_narrow<false, false, VEC>(p, stream);
     }
   } else if (p.g.num_chunks > 0) {
     if (p.edge_grad) {

@@ -26,21 +26,43 @@
 
 namespace gnn {
 
-template <int LPR, int Q>
+// VEC (rows of a multiple of 4 floats, 16-byte aligned): lane i owns the four consecutive floats
+// 4i .. 4i+3 (Q == 4) and moves them with one 128-bit access; otherwise it owns floats
+// i, i+LPR, ... and moves them one by one.
+template <int LPR, int Q, bool VEC = false>
 struct SubTile {
+  static_assert(!VEC || Q == 4, "a 128-bit unit is four floats");
   static constexpr int R = 32 / LPR;
   int sub;       // lane inside the sub-warp
   int grp;       // sub-warp index
   bool valid[Q];
+  __device__ __forceinline__ int elem(int q) const { return VEC ? sub * 4 + q : sub + LPR * q; }
   __device__ __forceinline__ void init(int lane, int width) {
     sub = lane & (LPR - 1);
     grp = lane / LPR;
 #pragma unroll
-    for (int q = 0; q < Q; ++q) valid[q] = sub + LPR * q < width;
+    for (int q = 0; q < Q; ++q) valid[q] = elem(q) < width;
   }
   __device__ __forceinline__ void load(const float* __restrict__ row, float (&v)[Q]) const {
+    if constexpr (VEC) {
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (valid[0]) x = __ldg(reinterpret_cast<const float4*>(row) + sub);
+      v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    } else {
 #pragma unroll
-    for (int q = 0; q < Q; ++q) v[q] = valid[q] ? __ldg(row + sub + LPR * q) : 0.f;
+      for (int q = 0; q < Q; ++q) v[q] = valid[q] ? __ldg(row + sub + LPR * q) : 0.f;
+    }
+  }
+  // the same with an ordinary load, for rows this kernel also writes
+  __device__ __forceinline__ void load_rw(const float* row, float (&v)[Q]) const {
+    if constexpr (VEC) {
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (valid[0]) x = *(reinterpret_cast<const float4*>(row) + sub);
+      v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    } else {
+#pragma unroll
+      for (int q = 0; q < Q; ++q) v[q] = valid[q] ? row[sub + LPR * q] : 0.f;
+    }
   }
   // Sum over the R sub-warps; every sub-warp ends with the total.
   __device__ __forceinline__ void reduce_groups(float (&v)[Q]) const {
@@ -59,9 +81,13 @@ struct SubTile {
   // so the merge kernels of the general tile read them unchanged.
   __device__ __forceinline__ void store(float* row, const float (&v)[Q]) const {
     if (grp == 0) {
+      if constexpr (VEC) {
+        if (valid[0]) reinterpret_cast<float4*>(row)[sub] = make_float4(v[0], v[1], v[2], v[3]);
+      } else {
 #pragma unroll
-      for (int q = 0; q < Q; ++q)
-        if (valid[q]) row[sub + LPR * q] = v[q];
+        for (int q = 0; q < Q; ++q)
+          if (valid[q]) row[sub + LPR * q] = v[q];
+      }
     }
   }
 };
@@ -73,10 +99,10 @@ struct NarrowUnroll { static constexpr int U = Q >= 3 ? 4 : 8; };
 // ---- forward ------------------------------------------------------------------------------
 // p.H == 1, p.width <= LPR * Q.  Writes out / seg_max / seg_sum (or scratch slots for the
 // pieces of split rows) exactly like wgather_kernel<GatSoftmaxPolicy, 1, ., false>.
-template <int LPR, int Q>
+template <int LPR, int Q, bool VEC = false>
 __global__ void __launch_bounds__(kThreadsPerCta)
 gat_fwd_narrow_kernel(WGatherParams p, GatSoftmaxPolicy<1> pol) {
-  using Tile = SubTile<LPR, Q>;
+  using Tile = SubTile<LPR, Q, VEC>;
   constexpr int R = Tile::R;
   constexpr int U = NarrowUnroll<Q>::U;
   __shared__ int cs_all[kWarpsPerCta][32];
@@ -150,11 +176,10 @@ gat_fwd_narrow_kernel(WGatherParams p, GatSoftmaxPolicy<1> pol) {
         const float fo = expf(mo - M), fn = expf(m - M);
         ssum = so * fo + ssum * fn;
         m = M;
+        float old[Q];
+        t.load_rw(orow, old);
 #pragma unroll
-        for (int q = 0; q < Q; ++q) {
-          const float old = t.valid[q] ? orow[t.sub + LPR * q] : 0.f;
-          acc[q] = fmaf(old, fo, acc[q] * fn);
-        }
+        for (int q = 0; q < Q; ++q) acc[q] = fmaf(old[q], fo, acc[q] * fn);
       }
       if (p.finalize) {
         const float inv = 1.f / ssum;
@@ -180,10 +205,10 @@ gat_fwd_narrow_kernel(WGatherParams p, GatSoftmaxPolicy<1> pol) {
 // ---- backward column pass -------------------------------------------------------------------
 // p.H == 1, p.width <= LPR * Q; same outputs and scratch layout as
 // gat_bwd_col_kernel<1, ., false, 0, ACC, EDGES>.
-template <int LPR, int Q, bool ACC, bool EDGES>
+template <int LPR, int Q, bool ACC, bool EDGES, bool VEC = false>
 __global__ void __launch_bounds__(kThreadsPerCta)
 gat_bwd_col_narrow_kernel(GatBwdColParams p) {
-  using Tile = SubTile<LPR, Q>;
+  using Tile = SubTile<LPR, Q, VEC>;
   constexpr int R = Tile::R;
   constexpr int U = NarrowUnroll<Q>::U;
   __shared__ int cs_all[kWarpsPerCta][32];
@@ -259,9 +284,10 @@ gat_bwd_col_narrow_kernel(GatBwdColParams p) {
     if (first && last) {
       float* grow = p.grad_feat + (size_t)s * p.ld_gfeat;
       if constexpr (ACC) {
+        float old[Q];
+        t.load_rw(grow, old);
 #pragma unroll
-        for (int q = 0; q < Q; ++q)
-          if (t.valid[q]) acc[q] += grow[t.sub + LPR * q];
+        for (int q = 0; q < Q; ++q) acc[q] += old[q];
       }
       t.store(grow, acc);
       if (lane == 0) {

@@ -583,40 +583,62 @@ class FusedGATProjectedLayerFunction(torch.autograd.Function):
         H, F = attn_l.shape[1], attn_l.shape[2]
         feat, W = feat.contiguous(), W.contiguous()
         attn_l, attn_r = attn_l.contiguous(), attn_r.contiguous()
-        h2, attn_row, attn_col = dense.gemm_any_k(feat, W, False, scores=(attn_l.view(H, F), attn_r.view(H, F)))
-        h = h2.view(-1, H, F)
+        # One head whose width is not a multiple of 4 floats (the 47- / 41- / 7-wide output layers): the
+        # weights get zero columns up to the next multiple, so the projected rows, the aggregated rows and
+        # their gradients have a 16-byte pitch and the sparse kernels move them with 128-bit accesses; the
+        # extra columns are zero everywhere (a zero weight column, a zero gradient column) and are cut off
+        # at the node's boundary.  It also makes the input gradient's GEMM a K % 4 == 0 product.
+        pad = (-F) % 4 if H == 1 else 0
+        Fp = F + pad
+        Wp, alp, arp = W, attn_l.view(H, F), attn_r.view(H, F)
+        if pad:
+            Wp = torch.nn.functional.pad(W, (0, pad))
+            alp = torch.nn.functional.pad(alp, (0, pad))
+            arp = torch.nn.functional.pad(arp, (0, pad))
+        h2, attn_row, attn_col = dense.gemm_any_k(feat, Wp, False, scores=(alp, arp))
+        h = h2.view(-1, H, Fp)
         act = None
         if activation == "elu":
             out, act, edge_max, edge_sum = gat_forward_act(attn_row, attn_col, row_ptr, col_ind, negative_slope, h)
         else:
             out, edge_max, edge_sum = gat_forward(attn_row, attn_col, row_ptr, col_ind, negative_slope, h)
         ctx.save_for_backward(row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, h, attn_row,
-                              attn_col, attn_l, attn_r, out, feat, W)
+                              attn_col, alp, arp, out, feat, Wp)
         ctx.negative_slope = negative_slope
         ctx.activation = activation
-        return out if act is None else act
+        ctx.width = (F, pad)
+        res = out if act is None else act
+        return res[:, :, :F] if pad else res
 
     @staticmethod
     def backward(ctx, grad_out):
         from . import dense
 
-        (row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, h, attn_row, attn_col, attn_l,
-         attn_r, out, feat, W) = ctx.saved_tensors
+        (row_ptr, col_ind, col_ptr, row_ind, edge_max, edge_sum, h, attn_row, attn_col, alp,
+         arp, out, feat, Wp) = ctx.saved_tensors
+        F, pad = ctx.width
+        grad_out = torch.nn.functional.pad(grad_out, (0, pad)) if pad else grad_out.contiguous()
         grad_h, gar, gac = _backward(ctx.negative_slope, row_ptr, col_ind, col_ptr, row_ind,
                                      edge_max, edge_sum, h, attn_row, attn_col, out,
-                                     grad_out.contiguous(), ctx.activation)
-        gl, gr = gat_scores_backward(h, attn_l, attn_r, gar, gac, grad_h)
+                                     grad_out, ctx.activation)
+        H = h.shape[1]
+        gl, gr = gat_scores_backward(h, alp.view(1, H, -1), arp.view(1, H, -1), gar, gac, grad_h)
         g2 = grad_h.view(grad_h.shape[0], -1)
         grad_feat = grad_w = None
         if ctx.needs_input_grad[0]:
-            grad_feat = dense.gemm_any_k(g2, W, True)      # g (N, HF) @ W^T: W is (in, HF) = "N x K" of this product
+            grad_feat = dense.gemm_any_k(g2, Wp, True)      # g (N, HF) @ W^T: W is (in, HF) = "N x K" of this product
         if ctx.needs_input_grad[1]:
             if feat.shape[0] >= dense.TN_MIN_ROWS and feat.data_ptr() % 16 == 0 and g2.data_ptr() % 16 == 0:
                 grad_w = dense.gemm_tn(feat, g2)
             else:
                 dense._note_fallback()
                 grad_w = feat.t() @ g2
-        return (grad_feat, grad_w, gl.view_as(attn_l), gr.view_as(attn_r), None, None, None, None, None, None)
+            if pad:
+                grad_w = grad_w[:, :F].contiguous()
+        gl, gr = gl.reshape(1, H, -1), gr.reshape(1, H, -1)
+        if pad:
+            gl, gr = gl[:, :, :F].contiguous(), gr[:, :, :F].contiguous()
+        return (grad_feat, grad_w, gl, gr, None, None, None, None, None, None)
 
 
 def projected_layer_supported(feat, W, H, F):
