@@ -232,6 +232,17 @@ template <bool ACC, bool EDGES, bool VEC>
 void launch_col_narrow(const GatBwdColParams& p, cudaStream_t stream) {
   const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
   dispatch_narrow<VEC>(p.width, [&](auto lpr, auto nq, auto nv) {
+    if constexpr (decltype(nv)::value) {
+      static const bool ring = [] {
+        const char* e = getenv("GNN_B200_NARROW_RING");
+        return e ? atoi(e) != 0 : true;
+      }();
+      if (ring) {  // 32 KB of dynamic shared memory: within the default limit, no opt-in needed
+        gat_bwd_col_narrow_kernel<decltype(lpr)::value, decltype(nq)::value, ACC, EDGES, true, true>
+            <<<blocks, kThreadsPerCta, kNarrowRingBytes, stream>>>(p);
+        return;
+      }
+    }
     gat_bwd_col_narrow_kernel<decltype(lpr)::value, decltype(nq)::value, ACC, EDGES, decltype(nv)::value>
         <<<blocks, kThreadsPerCta, 0, stream>>>(p);
   });
