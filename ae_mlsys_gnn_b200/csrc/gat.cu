@@ -20,16 +20,6 @@ bool narrow_shape(const HeadPlan& pl, int H, int64_t width) {
   return enabled && pl.fused && H == 1 && width <= 64;
 }
 
-// The sub-warp kernels for rows of whole 16-byte units keep their rows in flight in shared memory
-// (GNN_B200_NARROW_RING=0: in registers).
-bool narrow_ring() {
-  static const bool on = [] {
-    const char* e = getenv("GNN_B200_NARROW_RING");
-    return e ? atoi(e) != 0 : true;
-  }();
-  return on;
-}
-
 // Calls fn(integral_constant<LPR>, integral_constant<Q>, bool_constant<VEC>) for the sub-warp tile covering
 // `width` floats: VEC (rows of whole 16-byte units) gives every lane four consecutive floats.
 template <bool VEC, class Fn>
@@ -145,13 +135,6 @@ extern "C" int gnn_gat_fwd_part(const int* row_ptr, const int* col_ind, int64_t 
             if (p.g.num_chunks > 0) {
               const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
               dispatch_narrow<decltype(v)::value>(w, [&](auto lpr, auto nq, auto nv) {
-                if constexpr (decltype(nv)::value) {
-                  if (narrow_ring()) {
-                    gat_fwd_narrow_kernel<decltype(lpr)::value, decltype(nq)::value, true, true>
-                        <<<blocks, kThreadsPerCta, kNarrowRingBytes, stream>>>(p, pol);
-                    return;
-                  }
-                }
                 gat_fwd_narrow_kernel<decltype(lpr)::value, decltype(nq)::value, decltype(nv)::value>
                     <<<blocks, kThreadsPerCta, 0, stream>>>(p, pol);
               });
@@ -250,7 +233,11 @@ void launch_col_narrow(const GatBwdColParams& p, cudaStream_t stream) {
   const int blocks = (p.g.num_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
   dispatch_narrow<VEC>(p.width, [&](auto lpr, auto nq, auto nv) {
     if constexpr (decltype(nv)::value) {
-      if (narrow_ring()) {  // 32 KB of dynamic shared memory: within the default limit, no opt-in needed
+      static const bool ring = [] {
+        const char* e = getenv("GNN_B200_NARROW_RING");
+        return e ? atoi(e) != 0 : true;
+      }();
+      if (ring) {  // 32 KB of dynamic shared memory: within the default limit, no opt-in needed
         gat_bwd_col_narrow_kernel<decltype(lpr)::value, decltype(nq)::value, ACC, EDGES, true, true>
             <<<blocks, kThreadsPerCta, kNarrowRingBytes, stream>>>(p);
         return;

@@ -96,23 +96,15 @@ struct SubTile {
 template <int Q>
 struct NarrowUnroll { static constexpr int U = Q >= 3 ? 4 : 8; };
 
-// RING (VEC only): the lane's 16-byte unit of each gathered row goes through a ring of
-// kNarrowRingSlots slots per lane in shared memory (cp.async, groups of two rows), as in the wide
-// tile: rows stay in flight while earlier ones are reduced.
-constexpr int kNarrowRingSlots = 8;
-constexpr size_t kNarrowRingBytes = (size_t)kWarpsPerCta * kNarrowRingSlots * 32 * sizeof(float4);
-
 // ---- forward ------------------------------------------------------------------------------
 // p.H == 1, p.width <= LPR * Q.  Writes out / seg_max / seg_sum (or scratch slots for the
 // pieces of split rows) exactly like wgather_kernel<GatSoftmaxPolicy, 1, ., false>.
-template <int LPR, int Q, bool VEC = false, bool RING = false>
+template <int LPR, int Q, bool VEC = false>
 __global__ void __launch_bounds__(kThreadsPerCta)
 gat_fwd_narrow_kernel(WGatherParams p, GatSoftmaxPolicy<1> pol) {
-  static_assert(!RING || VEC, "the ring moves 16-byte units");
   using Tile = SubTile<LPR, Q, VEC>;
   constexpr int R = Tile::R;
-  constexpr int U = RING ? 2 : NarrowUnroll<Q>::U;
-  extern __shared__ __align__(16) unsigned char narrow_ring_smem[];
+  constexpr int U = NarrowUnroll<Q>::U;
   __shared__ int cs_all[kWarpsPerCta][32];
   __shared__ float ws_all[kWarpsPerCta][32];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
@@ -157,55 +149,21 @@ gat_fwd_narrow_kernel(WGatherParams p, GatSoftmaxPolicy<1> pol) {
       ws[lane] = w;
       __syncwarp();
       const int nb = min(32, b - base);
-      [[maybe_unused]] float4* const ring =
-          reinterpret_cast<float4*>(narrow_ring_smem) + (size_t)wib * (kNarrowRingSlots * 32) + lane;
-      constexpr int G = kNarrowRingSlots / U;     // groups of U rows per lane the ring holds
-      [[maybe_unused]] auto issue = [&](int g) {  // rows jj = g*R*U of this batch, this sub-warp's share
-        const int jj = g * R * U;
-        if (jj < nb) {
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int j = jj + u * R + t.grp;
-            if (t.valid[0])
-              cp_async_16(ring + ((g % G) * U + u) * 32,
-                          reinterpret_cast<const float4*>(p.feat + (size_t)cs[j] * p.ld_feat) + t.sub);
-          }
-        }
-        cp_async_commit();
-      };
-      if constexpr (RING) {
-#pragma unroll
-        for (int g = 0; g < G - 1; ++g) issue(g);
-      }
 #pragma unroll 1
       for (int jj = 0; jj < nb; jj += R * U) {
         float v[U][Q];
         float wv[U];
-        if constexpr (RING) {
-          const int g = jj / (R * U);
-          issue(g + G - 1);
-          cp_async_wait<G - 1>();
 #pragma unroll
-          for (int u = 0; u < U; ++u) {
-            wv[u] = ws[jj + u * R + t.grp];
-            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (t.valid[0]) x = ring[((g % G) * U + u) * 32];
-            v[u][0] = x.x; v[u][1] = x.y; v[u][2] = x.z; v[u][3] = x.w;
-          }
-        } else {
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int j = jj + u * R + t.grp;  // < 32 always: R * U divides 32
-            wv[u] = ws[j];                     // 0 past the end of the batch
-            t.load(p.feat + (size_t)cs[j] * p.ld_feat, v[u]);
-          }
+        for (int u = 0; u < U; ++u) {
+          const int j = jj + u * R + t.grp;  // < 32 always: R * U divides 32
+          wv[u] = ws[j];                     // 0 past the end of the batch
+          t.load(p.feat + (size_t)cs[j] * p.ld_feat, v[u]);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u)
 #pragma unroll
           for (int q = 0; q < Q; ++q) acc[q] = fmaf(wv[u], v[u][q], acc[q]);
       }
-      if constexpr (RING) cp_async_wait<0>();  // only empty groups can be pending
     }
     t.reduce_groups(acc);
 
@@ -247,6 +205,12 @@ gat_fwd_narrow_kernel(WGatherParams p, GatSoftmaxPolicy<1> pol) {
 // ---- backward column pass -------------------------------------------------------------------
 // p.H == 1, p.width <= LPR * Q; same outputs and scratch layout as
 // gat_bwd_col_kernel<1, ., false, 0, ACC, EDGES>.
+// RING (VEC only): the lane's 16-byte unit of each gathered row goes through a ring of
+// kNarrowRingSlots slots per lane in shared memory (cp.async, groups of two rows), as in the wide
+// tile: rows stay in flight while earlier ones are reduced.
+constexpr int kNarrowRingSlots = 8;
+constexpr size_t kNarrowRingBytes = (size_t)kWarpsPerCta * kNarrowRingSlots * 32 * sizeof(float4);
+
 template <int LPR, int Q, bool ACC, bool EDGES, bool VEC = false, bool RING = false>
 __global__ void __launch_bounds__(kThreadsPerCta)
 gat_bwd_col_narrow_kernel(GatBwdColParams p) {
