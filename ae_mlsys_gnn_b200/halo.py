@@ -538,16 +538,29 @@ class HaloGATConv(_GATBase):
 
     def forward(self, part: HaloPartition, feat, exch):
         n, H, Fo = part.n_local, self.num_heads, self.out_feats
+        W, attn_l, attn_r = self.W, self.attn_l, self.attn_r
+        # One head of odd width (the 47-wide output layer): zero weight columns up to the next multiple of
+        # 4 floats give the projected rows, the rows that travel and their gradients a 16-byte pitch (128-bit
+        # accesses in the sparse kernels and in the push); the extra columns are zero and are cut off below.
+        pad = (-Fo) % 4 if H == 1 else 0
+        if pad:
+            W = F.pad(W, (0, pad))
+            attn_l, attn_r = F.pad(attn_l, (0, pad)), F.pad(attn_r, (0, pad))
+            Fo = Fo + pad
+        out = self._forward(part, feat, exch, W, attn_l, attn_r, n, H, Fo)
+        return out[:, :, : Fo - pad] if pad else out
+
+    def _forward(self, part, feat, exch, W, attn_l, attn_r, n, H, Fo):
         if self._recompute(part):
             # the narrow inputs travel first; both projections write into one [own | halo] tensor
             with torch.no_grad():
                 (x_ext,) = exch.exchange((self.key, "fwd_x"), [feat.detach()], part.fwd, n)
             h_ext = feat.new_empty((x_ext.shape[0], H, Fo))
             with dense.side_weight_grads(self.side_weight_grads and part.world > 1):  # X^T G beside the next exchange
-                h = dense.project(feat, self.W, out=dense.OutRows(h_ext, 0)).view(-1, H, Fo)
+                h = dense.project(feat, W, out=dense.OutRows(h_ext, 0)).view(-1, H, Fo)
             if x_ext.shape[0] > n:
                 with torch.no_grad():
-                    dense.project(x_ext[n:], self.W.detach(), out=dense.OutRows(h_ext, n))
+                    dense.project(x_ext[n:], W.detach(), out=dense.OutRows(h_ext, n))
             ac_ext = None  # only the scores of the halo are still to be exchanged
         else:
             h_ext, ac_ext = exch.open((self.key, "fwd"), [(H, Fo), (H,)], part.fwd, n, feat.device)
@@ -564,9 +577,9 @@ class HaloGATConv(_GATBase):
                 def after(lo, hi):
                     exch.push_rows(key, 0, h_ext, part.fwd, lo, hi)
             with dense.side_weight_grads(self.side_weight_grads and part.world > 1):
-                h = dense.project(feat, self.W, out=dense.OutRows(h_ext, 0), row_blocks=blocks,
+                h = dense.project(feat, W, out=dense.OutRows(h_ext, 0), row_blocks=blocks,
                                   after_block=after).view(-1, H, Fo)
-        return HaloGATFunction.apply(h, self.attn_l, self.attn_r, part, self.negative_slope,
+        return HaloGATFunction.apply(h, attn_l, attn_r, part, self.negative_slope,
                                      self.kernels, exch, self.key, self.activation, h_ext, ac_ext)
 
 
