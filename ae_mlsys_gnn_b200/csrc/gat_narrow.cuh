@@ -1,22 +1,25 @@
-// Fused GAT forward and backward column pass for one head with a narrow, unaligned feature
-// row (the 1 x 47 / 1 x 41 / 1 x 7 output layers: rows of 188 / 164 / 28 bytes, which rule
-// out 128-bit accesses).  Same mathematics, chunk traversal, scratch slots and merge kernels
-// as the general kernels (wgather.cuh, gat_bwd.cuh); what differs is the tiling of the warp:
+// Fused GAT forward and backward column pass for one head with a narrow feature row (at most 64
+// floats: the 1 x 47 / 1 x 41 / 1 x 7 output layers and their 16-byte-pitch forms 1 x 48 / 44 / 8).
+// Same mathematics, chunk traversal, scratch slots and merge kernels as the general kernels
+// (wgather.cuh, gat_bwd.cuh); what differs is the tiling of the warp:
 //
 //   general tile : 32 lanes share one gathered row (lane l owns floats l, l+32, ...).  With 47
 //                  floats half of the second load is idle and every edge costs its own
 //                  address arithmetic, weight fetch and (backward) 5-step warp reduction.
 //   here         : the warp is cut into R = 32/LPR sub-warps of LPR lanes; sub-warp g works
-//                  on edge j*R + g, lane i of it owns floats i, i+LPR, ... (Q of them).  One
-//                  warp instruction therefore serves R edges, the per-edge dot product of the
-//                  backward is a log2(LPR)-step reduction that R edges share, and R*U rows
-//                  are in flight per warp.
+//                  on edge j*R + g.  One warp instruction therefore serves R edges, the per-edge
+//                  dot product of the backward is a log2(LPR)-step reduction that R edges
+//                  share, and R*U rows are in flight per warp.  A lane owns floats i, i+LPR, ...
+//                  (rows that rule out 128-bit accesses: 188 / 164 / 28 bytes) or, for rows of
+//                  whole 16-byte units, the four consecutive floats 4i .. 4i+3.
 //
 // Measured on a 1 M-node / 42 M-edge R-MAT graph, 1 x 47: forward 1.90 -> 1.55 ms, column pass
-// with edge gradients about 3.9 -> 2.27 ms.  What bounds these kernels is the first-level cache's
+// with edge gradients about 3.9 -> 2.27 ms.  What bounds the scalar form is the first-level cache's
 // line look-ups (a 188-byte row starts anywhere in a 128-byte line, every 64-byte piece of it
 // costs one or two look-ups, and the 4-byte gather of the source's score another): holding all
-// 32 rows of a batch in flight with fewer resident warps was measured slower.
+// 32 rows of a batch in flight with fewer resident warps was measured slower.  On a 2.45 M-node /
+// 125 M-edge graph, 1 x 48 against 1 x 47: forward 4.65 -> 4.30 ms, column pass 7.04 -> 5.27 ms
+// (with its rows in the shared-memory ring below; the same ring made the forward slower).
 //
 // Replaces, for these shapes, fused_forward_kernel_small_f_sm and
 // mhspmm_backward_kernel_small_f + mhsddmm + fused_backward_kernel
