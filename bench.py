@@ -25,6 +25,10 @@ The line's extra records (single GPU, default workload):
                  extrapolated by edge count (flagged as such);
   gpu_reference  the reference's own CUDA operators (compiled unmodified into oracle/_ref)
                  timed per operator next to this library's on the same inputs.
+With N > 1: `per_rank` (rows, edges, halo rows, rows sent, entry-point and push time of every
+rank), the NVLink bytes and GB/s of the `gnn_halo_push[width]` entries, and the DRAM capture of
+the whole graph scaled to the rank's block by algorithmic bytes.  `--timeline PATH` writes one
+timed step of rank 0 as a list of library calls (start and duration on the device's clock).
 """
 from __future__ import annotations
 
